@@ -1,0 +1,518 @@
+// bf16 GEMM family on 5th-generation tensor cores (tcgen05), fp32 accumulation in
+// tensor memory, operands staged by TMA (plain tile loads, no cluster multicast).
+//
+// One persistent kernel template covers every contraction of the training step:
+//   NT  y = x W^T            (forward linears, grouped expert forward)
+//   NN  dx = dy W            (data gradients; W is read MN-major, no transpose copy)
+//   TN  dW (+)= dy^T x       (weight gradients, accumulated in fp32 or bf16 in place)
+// with a device-side tile table for grouped (per-expert) problems, a fused
+// SwiGLU epilogue for the gate/up projection and a K-concatenated form for
+// dx = dgate W1 + dup W3.
+//
+// Layout of one CTA (192 threads, one CTA per SM):
+//   warp 0       TMA producer (one elected lane)
+//   warp 1       tensor-memory allocation, MMA issue (one elected lane)
+//   warps 2..5   epilogue: tcgen05.ld the 128 x BN fp32 tile, convert, store
+// The accumulator is double-buffered in TMEM (2 x 256 columns), so the epilogue
+// of tile i overlaps the main loop of tile i+1.  Shared memory holds a 4-stage
+// ring of {A 128x64, B 256x64} bf16 tiles in the 128-byte-swizzled layout that
+// both TMA and the MMA descriptors understand.
+#include "ptx.cuh"
+
+namespace b2 {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;   // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;   // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int GROUP_M = 8;
+
+enum Epilogue : int {
+  EPI_STORE_BF16 = 0,   // D[M,N] bf16 = acc
+  EPI_ACC_F32 = 1,      // D[M,N] fp32 += acc   (beta selects += or =)
+  EPI_ACC_BF16 = 2,     // D[M,N] bf16 += acc
+  EPI_SWIGLU = 3,       // H[M,N/2] = silu(acc[:, :128]) * acc[:, 128:]; optional gate/up stores
+  EPI_STORE_F32 = 4,    // D[M,N] fp32 = acc
+};
+
+enum Schedule : int {
+  SCHED_FLAT = 0,       // tiles over (M, N); optional per-m-tile expert for B
+  SCHED_WGRAD = 1,      // tiles over (expert, M, N); K range = rows of the expert
+};
+
+struct GemmParams {
+  CUtensorMap map_a;
+  CUtensorMap map_b;
+  CUtensorMap map_b2;          // second B: up-projection (SwiGLU) or K-continuation (k >= k_split)
+  int M, N, K;                 // problem per expert for SCHED_WGRAD (K unused there)
+  int num_experts;             // >= 1
+  int b_expert_rows;           // rows of one expert in the B map (outer TMA coordinate pitch)
+  int k_split;                 // K index where map_b2 takes over (0 = unused)
+  const int* tile_expert;      // [m_tiles] expert of each m-tile, or null
+  const int* num_m_tiles;      // device scalar: live m-tiles, or null (= ceil(M/128))
+  const int* expert_offsets;   // [E] cumulative row ends (SCHED_WGRAD)
+  void* d;                     // output
+  void* d_gate;                // optional gate pre-activation (SwiGLU)
+  void* d_up;                  // optional up pre-activation (SwiGLU)
+  long long ldd;               // leading dimension of d (elements)
+  long long d_expert_stride;   // elements between experts in d (SCHED_WGRAD)
+  float beta;                  // 1 accumulate, 0 overwrite (EPI_ACC_*)
+  int* status;                 // device word; non-zero = a wait ran out
+};
+
+struct TileCoord {
+  int m_tile, n_tile, expert, k_begin, k_blocks;
+  bool valid;
+};
+
+template <int SCHED>
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, long long tile, int m_tiles, int n_tiles) {
+  TileCoord t;
+  t.valid = true;
+  if (SCHED == SCHED_WGRAD) {
+    const long long per_expert = static_cast<long long>(m_tiles) * n_tiles;
+    t.expert = static_cast<int>(tile / per_expert);
+    const int rest = static_cast<int>(tile - t.expert * per_expert);
+    const int group = rest / (GROUP_M * n_tiles);
+    const int first_m = group * GROUP_M;
+    const int rows_in_group = min(GROUP_M, m_tiles - first_m);
+    const int in_group = rest - group * GROUP_M * n_tiles;
+    t.m_tile = first_m + in_group % rows_in_group;
+    t.n_tile = in_group / rows_in_group;
+    const int begin = t.expert == 0 ? 0 : p.expert_offsets[t.expert - 1];
+    const int end = p.expert_offsets[t.expert];
+    t.k_begin = begin;
+    t.k_blocks = (end - begin + BK - 1) / BK;
+  } else {
+    const int group = static_cast<int>(tile / (GROUP_M * n_tiles));
+    const int first_m = group * GROUP_M;
+    const int rows_in_group = min(GROUP_M, m_tiles - first_m);
+    const int in_group = static_cast<int>(tile - static_cast<long long>(group) * GROUP_M * n_tiles);
+    t.m_tile = first_m + in_group % rows_in_group;
+    t.n_tile = in_group / rows_in_group;
+    t.expert = p.tile_expert ? p.tile_expert[t.m_tile] : 0;
+    t.k_begin = 0;
+    t.k_blocks = (p.K + BK - 1) / BK;
+  }
+  return t;
+}
+
+template <int A_MN, int B_MN, int EPI, int SCHED>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int m_tiles = p.num_m_tiles ? *p.num_m_tiles : (p.M + BM - 1) / BM;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const long long total_tiles = static_cast<long long>(m_tiles) * n_tiles * (SCHED == SCHED_WGRAD ? p.num_experts : 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&p.map_a);
+    tma_prefetch_desc(&p.map_b);
+    if (EPI == EPI_SWIGLU || p.k_split > 0) tma_prefetch_desc(&p.map_b2);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (long long tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        const TileCoord t = decode_tile<SCHED>(p, tile, m_tiles, n_tiles);
+        const int m0 = t.m_tile * BM;
+        const int n0 = t.n_tile * BN;
+        for (int kb = 0; kb < t.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            *abort_flag = 1;
+            atomicExch(p.status, 1);
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const int k0 = t.k_begin + kb * BK;
+          // ---- A
+          if (A_MN) {
+            // MN-major: two boxes of [64 (m) x 64 (k)]; inner coordinate = m, outer = k row
+            tma_load_2d(sa, &p.map_a, &full_bar[stage], m0, k0);
+            tma_load_2d(sa + 8192, &p.map_a, &full_bar[stage], m0 + 64, k0);
+          } else {
+            tma_load_2d(sa, &p.map_a, &full_bar[stage], k0, m0);
+          }
+          // ---- B
+          if (EPI == EPI_SWIGLU) {
+            // gate rows then up rows of the same 128 output features (K-major)
+            const int row = t.expert * p.b_expert_rows + t.n_tile * 128;
+            tma_load_2d(sb, &p.map_b, &full_bar[stage], k0, row);
+            tma_load_2d(sb + 16384, &p.map_b2, &full_bar[stage], k0, row);
+          } else if (B_MN) {
+            const bool second = p.k_split > 0 && k0 >= p.k_split;
+            const CUtensorMap* map = second ? &p.map_b2 : &p.map_b;
+            const int krow = (SCHED == SCHED_WGRAD ? 0 : t.expert * p.b_expert_rows) + (second ? k0 - p.k_split : k0);
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, map, &full_bar[stage], n0 + c * 64, krow);
+          } else {
+            tma_load_2d(sb, &p.map_b, &full_bar[stage], k0, t.expert * p.b_expert_rows + n0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (long long tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        const TileCoord t = decode_tile<SCHED>(p, tile, m_tiles, n_tiles);
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
+          *abort_flag = 1;
+          atomicExch(p.status, 2);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool failed = false;
+        for (int kb = 0; kb < t.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = A_MN ? umma_smem_desc(sa + k * 2048, 8192, 1024) : umma_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? umma_smem_desc(sb + k * 2048, 8192, 1024) : umma_smem_desc(sb + k * 32, 16, 1024);
+            umma_bf16_ss(d_tmem, da, db, idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty_bar[stage]);   // frees the stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (failed) {
+          *abort_flag = 1;
+          atomicExch(p.status, 3);
+          break;
+        }
+        umma_commit(&tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;                 // TMEM lane group this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (long long tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+      const TileCoord t = decode_tile<SCHED>(p, tile, m_tiles, n_tiles);
+      if (!mbar_wait(&tmem_full[acc], acc_phase)) {
+        *abort_flag = 1;
+        atomicExch(p.status, 4);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+      const long long row = static_cast<long long>(t.m_tile) * BM + row_in_tile;
+      const bool row_ok = row < p.M;
+      const bool empty_k = t.k_blocks == 0;   // an expert without rows contributes nothing
+      if (EPI == EPI_SWIGLU) {
+        __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(p.d);
+        const long long half_n = p.N / 2;
+        const long long col0 = static_cast<long long>(t.n_tile) * 128;
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(taddr + c, g);
+          tmem_ld_32x32(taddr + 128 + c, u);
+          tmem_ld_wait();
+          if (row_ok && col0 + c < half_n) {
+            uint32_t out[16], og[16], ou[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
+              const float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
+              const float h0 = g0 / (1.f + __expf(-g0)) * u0;
+              const float h1 = g1 / (1.f + __expf(-g1)) * u1;
+              out[i] = pack_bf16(h0, h1);
+              og[i] = pack_bf16(g0, g1);
+              ou[i] = pack_bf16(u0, u1);
+            }
+            const long long off = row * half_n + col0 + c;
+            uint4* dst = reinterpret_cast<uint4*>(h + off);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+            if (p.d_gate) {
+              uint4* dg = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.d_gate) + off);
+              uint4* du = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.d_up) + off);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                dg[i] = make_uint4(og[4 * i], og[4 * i + 1], og[4 * i + 2], og[4 * i + 3]);
+                du[i] = make_uint4(ou[4 * i], ou[4 * i + 1], ou[4 * i + 2], ou[4 * i + 3]);
+              }
+            }
+          }
+        }
+      } else {
+        const long long col_base = static_cast<long long>(t.n_tile) * BN;
+        const long long expert_off = SCHED == SCHED_WGRAD ? t.expert * p.d_expert_stride : 0;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          if (!empty_k) {
+            tmem_ld_32x32(taddr + c, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0;
+          }
+          const long long col = col_base + c;
+          if (!row_ok || col >= p.N) continue;   // N is a multiple of 32 (checked on the host)
+          const long long off = expert_off + row * p.ldd + col;
+          if (EPI == EPI_STORE_BF16) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.d) + off);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              dst[i] = make_uint4(pack_bf16(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
+                                  pack_bf16(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
+                                  pack_bf16(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
+                                  pack_bf16(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])));
+          } else if (EPI == EPI_ACC_F32 || EPI == EPI_STORE_F32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.d) + off);
+            const bool add = EPI == EPI_ACC_F32 && p.beta != 0.f;
+            float4 old[8];
+            if (add) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) old[i] = dst[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float4 r = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                     __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+              if (add) {
+                r.x += old[i].x; r.y += old[i].y; r.z += old[i].z; r.w += old[i].w;
+              }
+              dst[i] = r;
+            }
+          } else if (EPI == EPI_ACC_BF16) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.d) + off);
+            const bool add = p.beta != 0.f;
+            uint4 old[4];
+            if (add) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) old[i] = dst[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t o[4] = {old[i].x, old[i].y, old[i].z, old[i].w};
+              uint32_t r[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float a = __uint_as_float(v[8 * i + 2 * j]), b = __uint_as_float(v[8 * i + 2 * j + 1]);
+                if (add) {
+                  const __nv_bfloat162 prev = *reinterpret_cast<__nv_bfloat162*>(&o[j]);
+                  a += __low2float(prev);
+                  b += __high2float(prev);
+                }
+                r[j] = pack_bf16(a, b);
+              }
+              dst[i] = make_uint4(r[0], r[1], r[2], r[3]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor [outer, inner] with row pitch ``pitch_elems``; box = [box_outer, 64] elements, 128B swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long inner, long long outer, long long pitch_elems,
+                    int box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_outer)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+template <int A_MN, int B_MN, int EPI, int SCHED>
+static int launch(const GemmParams& p, int sms, cudaStream_t stream) {
+  auto kernel = gemm_tcgen05_kernel<A_MN, B_MN, EPI, SCHED>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess) return -3;
+    configured = true;
+  }
+  kernel<<<sms, GEMM_THREADS, GEMM_SMEM, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+static int sm_count() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return sms;
+}
+
+}  // namespace b2
+
+using namespace b2;
+
+// Arguments shared by the entry points below:
+//   a, b           bf16 operands; layouts per entry point
+//   lda, ldb       row pitch in elements
+//   tile_expert    optional int32 [ceil(M/128)] expert of each 128-row tile (grouped problems)
+//   num_m_tiles    optional device int32 scalar with the live tile count
+//   status         device int32 word, set non-zero if an in-kernel wait ran out
+extern "C" {
+
+// y[M,N] = a[M,K] * w[e][N,K]^T      (a K-major, w K-major)
+// epi: 0 bf16 store, 4 fp32 store.
+int b2_gemm_nt(const void* a, const void* w, void* d, int M, int N, int K, long long lda, long long ldw,
+               long long ldd, int num_experts, const int* tile_expert, const int* num_m_tiles, int epi, int* status,
+               cudaStream_t stream) {
+  if (N % 32 || K % 8) return -10;
+  GemmParams p{};
+  if (make_map(&p.map_a, a, K, M, lda, BM)) return -11;
+  if (make_map(&p.map_b, w, K, static_cast<long long>(num_experts) * N, ldw, BN)) return -12;
+  p.M = M; p.N = N; p.K = K; p.num_experts = num_experts; p.b_expert_rows = N; p.k_split = 0;
+  p.tile_expert = tile_expert; p.num_m_tiles = num_m_tiles; p.d = d; p.ldd = ldd; p.status = status; p.beta = 0.f;
+  if (epi == EPI_STORE_BF16) return launch<0, 0, EPI_STORE_BF16, SCHED_FLAT>(p, sm_count(), stream);
+  if (epi == EPI_STORE_F32) return launch<0, 0, EPI_STORE_F32, SCHED_FLAT>(p, sm_count(), stream);
+  return -13;
+}
+
+// h[M,F] = silu(a w1[e]^T) * (a w3[e]^T); optional gate/up pre-activations [M,F].
+int b2_gemm_swiglu(const void* a, const void* w1, const void* w3, void* h, void* gate, void* up, int M, int F, int K,
+                   long long lda, int num_experts, const int* tile_expert, const int* num_m_tiles, int* status,
+                   cudaStream_t stream) {
+  if (F % 128 || K % 8) return -10;
+  GemmParams p{};
+  if (make_map(&p.map_a, a, K, M, lda, BM)) return -11;
+  if (make_map(&p.map_b, w1, K, static_cast<long long>(num_experts) * F, K, 128)) return -12;
+  if (make_map(&p.map_b2, w3, K, static_cast<long long>(num_experts) * F, K, 128)) return -12;
+  p.M = M; p.N = 2 * F; p.K = K; p.num_experts = num_experts; p.b_expert_rows = F; p.k_split = 0;
+  p.tile_expert = tile_expert; p.num_m_tiles = num_m_tiles; p.d = h; p.d_gate = gate; p.d_up = up; p.ldd = F;
+  p.status = status;
+  return launch<0, 0, EPI_SWIGLU, SCHED_FLAT>(p, sm_count(), stream);
+}
+
+// dx[M,N] = a[M,K] * w[e][K,N]     (w MN-major: its rows are the reduction index).
+// If w2 is given, K = k_split + K2 and rows k >= k_split come from w2 (dx = dg W1 + du W3 in one pass).
+int b2_gemm_nn(const void* a, const void* w, const void* w2, void* d, int M, int N, int K, int k_split, long long lda,
+               long long ldw, long long ldd, int num_experts, const int* tile_expert, const int* num_m_tiles,
+               int* status, cudaStream_t stream) {
+  if (N % 32 || K % 64 || (w2 && k_split % 64)) return -10;
+  GemmParams p{};
+  const int rows = w2 ? k_split : K;
+  if (make_map(&p.map_a, a, K, M, lda, BM)) return -11;
+  if (make_map(&p.map_b, w, N, static_cast<long long>(num_experts) * rows, ldw, 64)) return -12;
+  if (w2 && make_map(&p.map_b2, w2, N, static_cast<long long>(num_experts) * (K - k_split), ldw, 64)) return -12;
+  p.M = M; p.N = N; p.K = K; p.num_experts = num_experts; p.b_expert_rows = rows; p.k_split = w2 ? k_split : 0;
+  p.tile_expert = tile_expert; p.num_m_tiles = num_m_tiles; p.d = d; p.ldd = ldd; p.status = status;
+  return launch<0, 1, EPI_STORE_BF16, SCHED_FLAT>(p, sm_count(), stream);
+}
+
+// dw[e][M,N] (+)= a[rows_e, M]^T * b[rows_e, N]   (both MN-major; rows_e from cumulative offsets, or all R rows
+// when expert_offsets is null).  out_kind: 1 fp32 (+= if beta), 2 bf16 (+= if beta).
+int b2_gemm_tn(const void* a, const void* b, void* d, int M, int N, int R, long long lda, long long ldb,
+               long long ldd, int num_experts, const int* expert_offsets, int out_kind, float beta, int* status,
+               cudaStream_t stream) {
+  if (N % 32 || M % 8) return -10;
+  GemmParams p{};
+  if (make_map(&p.map_a, a, M, R, lda, 64)) return -11;
+  if (make_map(&p.map_b, b, N, R, ldb, 64)) return -12;
+  p.M = M; p.N = N; p.K = R; p.num_experts = num_experts; p.b_expert_rows = 0; p.k_split = 0;
+  p.expert_offsets = expert_offsets; p.d = d; p.ldd = ldd; p.d_expert_stride = static_cast<long long>(M) * ldd;
+  p.beta = beta; p.status = status;
+  if (expert_offsets) {
+    if (out_kind == 1) return launch<1, 1, EPI_ACC_F32, SCHED_WGRAD>(p, sm_count(), stream);
+    if (out_kind == 2) return launch<1, 1, EPI_ACC_BF16, SCHED_WGRAD>(p, sm_count(), stream);
+  } else {
+    if (out_kind == 1) return launch<1, 1, EPI_ACC_F32, SCHED_FLAT>(p, sm_count(), stream);
+    if (out_kind == 2) return launch<1, 1, EPI_ACC_BF16, SCHED_FLAT>(p, sm_count(), stream);
+  }
+  return -13;
+}
+
+}  // extern "C"

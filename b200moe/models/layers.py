@@ -155,15 +155,22 @@ class MultiHeadLayerLL(nn.Module):
     def forward(self, x, token_positions=None, mask=None):
         batch, seq = x.shape[0], x.shape[1]
         hq, hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        fused_rope = False
         if self.qkv_weight is not None:
-            qkv = ops.linear(x, self.qkv_weight).view(batch, seq, hq + 2 * hkv, hd)
+            qkv = ops.linear(x.reshape(batch * seq, -1), self.qkv_weight)
+            if (self.use_rope and token_positions is None and mask is None and ops.use_native(qkv, "rope")
+                    and not ops.use_native(qkv, "attention")):
+                from ..ops.attention import rope_qk_
+                qkv = rope_qk_(qkv, seq, hq + 2 * hkv, hq + hkv, hd, self.RoPE.cos, self.RoPE.sin)
+                fused_rope = True
+            qkv = qkv.view(batch, seq, hq + 2 * hkv, hd)
             q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hkv], qkv[:, :, hq + hkv:]
         else:
             q = self.q_proj(x).view(batch, seq, hq, hd)
             k = self.k_proj(x).view(batch, seq, hkv, hd)
             v = self.v_proj(x).view(batch, seq, hkv, hd)
         cos = sin = None
-        if self.use_rope:
+        if self.use_rope and not fused_rope:
             cos, sin = self.RoPE.cos, self.RoPE.sin
             if token_positions is not None:
                 cos, sin = cos[token_positions], sin[token_positions]

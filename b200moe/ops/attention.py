@@ -32,6 +32,32 @@ class _RopeAttention(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
+class _RopeQK(torch.autograd.Function):
+    """Rotate the first ``heads`` heads of every token of a fused projection
+    ``[tokens, total_heads * hd]`` in place; the backward pass applies the
+    transpose rotation to the gradient."""
+
+    @staticmethod
+    def forward(ctx, qkv, seq, total, heads, hd, cos, sin):
+        _native().rope_inplace(qkv, 0, qkv.shape[0], seq, heads, hd, total * hd, cos, sin, 1.0)
+        ctx.mark_dirty(qkv)
+        ctx.meta = (seq, total, heads, hd, cos, sin)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, dqkv):
+        seq, total, heads, hd, cos, sin = ctx.meta
+        dqkv = dqkv.contiguous().clone()
+        _native().rope_inplace(dqkv, 0, dqkv.shape[0], seq, heads, hd, total * hd, cos, sin, -1.0)
+        return dqkv, None, None, None, None, None, None
+
+
+def rope_qk_(qkv2d, seq, total_heads, heads, head_dim, cos, sin):
+    """In-place RoPE on heads ``[0, heads)`` of a ``[tokens, total_heads*head_dim]``
+    tensor whose tokens are ``batch`` runs of ``seq`` positions."""
+    return _RopeQK.apply(qkv2d, seq, total_heads, heads, head_dim, cos, sin)
+
+
 def rope_attention(q, k, v, cos, sin):
     """Returns ``[B, S, Hq, head_dim]``.  ``cos``/``sin`` are ``[S_max, hd/2]``
     fp32 tables or ``None`` for no rotation."""

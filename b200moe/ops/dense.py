@@ -37,7 +37,7 @@ class _Linear(torch.autograd.Function):
         else:
             w = weight if weight.dtype == x.dtype else weight.to(x.dtype)
             y = x2d @ w.t()
-        return y.view(*x.shape[:-1], weight.shape[0])
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
     def backward(ctx, dy):

@@ -1,0 +1,109 @@
+"""The MoE block as native kernels with a hand-written backward pass.
+
+Forward:  plan (device counting sort) → gather rows into the padded
+expert-major buffer → grouped gate/up GEMM with the SwiGLU epilogue → grouped
+down GEMM → weighted combine.  Backward: the duals in reverse, with the three
+weight-gradient GEMMs accumulating into the experts' ``main_grad`` buffers.
+No step involves the host: tile counts, segment offsets and the tile→expert
+table stay on the device and the persistent GEMMs read them there.
+
+Replaces the reference's ``_dispatch_tokens`` / ``GroupedPositionWiseFFLayer`` /
+``_combine_tokens`` (implementation/layers.py:139-246) including its per-expert
+``nonzero`` loop and ``.cpu()`` split exchange.  With an expert-parallel context
+(``ep_ctx``) the gather and combine steps move rows between GPUs through peer
+memory (``b200moe.comm``).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import native
+
+ALIGN = 128
+
+
+def capacity_rows(slots: int, num_experts: int) -> int:
+    """Worst-case rows of the padded expert-major buffer."""
+    return (slots + num_experts * (ALIGN - 1) + ALIGN - 1) // ALIGN * ALIGN
+
+
+def _wgrad(dy, x, param, offs, num_experts):
+    main = getattr(param, "main_grad", None)
+    if main is not None:
+        native.gemm_tn(dy, x, out=main, accumulate=True, expert_offsets=offs, num_experts=num_experts)
+        return None
+    return native.gemm_tn(dy, x, out_dtype=param.dtype, expert_offsets=offs, num_experts=num_experts)
+
+
+class _MoEFused(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weights, idx, w1, w2, w3, recompute, ep_ctx):
+        tokens, dim = x.shape
+        experts = w1.shape[0]
+        x = x.contiguous()
+        weights = weights.float().contiguous()
+        if ep_ctx is None:
+            cap = capacity_rows(tokens * 2, experts)
+            slot_row, row_slot, offs, tile_expert, meta, _ = native.moe_plan(idx, experts, cap)
+            x_perm = native.moe_gather(x, row_slot, meta, cap)
+            route = None
+        else:
+            route = ep_ctx.dispatch(x, idx)
+            cap, offs, tile_expert, meta, x_perm = route.cap, route.offs, route.tile_expert, route.meta, route.x_perm
+            slot_row = row_slot = None
+        tiles = meta[0:1]
+        h, gate, up = native.gemm_swiglu(x_perm, w1, w3, tile_expert, tiles, save_gate_up=not recompute)
+        y_perm = native.gemm_nt(h, w2, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=experts)
+        if ep_ctx is None:
+            out = native.moe_combine(y_perm, slot_row, weights, tokens)
+        else:
+            out = ep_ctx.combine(route, y_perm, weights, tokens)
+        ctx.params = (w1, w2, w3)
+        ctx.meta_py = (tokens, dim, experts, cap, recompute, ep_ctx, route)
+        saved = [x_perm, y_perm, weights, offs, tile_expert, meta]
+        if ep_ctx is None:
+            saved += [slot_row, row_slot]
+        if not recompute:
+            saved += [gate, up]
+        ctx.save_for_backward(*saved)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        w1, w2, w3 = ctx.params
+        tokens, dim, experts, cap, recompute, ep_ctx, route = ctx.meta_py
+        saved = list(ctx.saved_tensors)
+        x_perm, y_perm, weights, offs, tile_expert, meta = saved[:6]
+        rest = saved[6:]
+        if ep_ctx is None:
+            slot_row, row_slot = rest[:2]
+            rest = rest[2:]
+        tiles, live_rows = meta[0:1], meta[1:2]
+        dout = dout.contiguous()
+        ffn = w1.shape[1]
+        if recompute:
+            _, gate, up = native.gemm_swiglu(x_perm, w1, w3, tile_expert, tiles, save_gate_up=True)
+        else:
+            gate, up = rest
+        dweights = torch.zeros(tokens, 2, dtype=torch.float32, device=dout.device)
+        if ep_ctx is None:
+            dy_perm = native.moe_gather(dout, row_slot, meta, cap, scale=weights.view(-1), y_perm=y_perm,
+                                        dweights=dweights.view(-1))
+        else:
+            dy_perm = ep_ctx.combine_backward(route, dout, y_perm, weights, dweights)
+        dh = native.gemm_nn(dy_perm, w2, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=experts)
+        dgu, h = native.swiglu_bwd(dh, gate, up, live_rows=live_rows)
+        del dh, gate, up
+        dx_perm = native.gemm_nn(dgu, w1, w2=w3, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=experts)
+        dw2 = _wgrad(dy_perm, h, w2, offs, experts)
+        dw1 = _wgrad(dgu[:, :ffn], x_perm, w1, offs, experts)
+        dw3 = _wgrad(dgu[:, ffn:], x_perm, w3, offs, experts)
+        if ep_ctx is None:
+            dx = native.moe_combine(dx_perm, slot_row, None, tokens)
+        else:
+            dx = ep_ctx.dispatch_backward(route, dx_perm, tokens)
+        return dx, dweights, None, dw1, dw2, dw3, None, None
+
+
+def moe_ffn_fused(x, weights, idx, w1, w2, w3, ep_ctx=None, recompute: bool = False):
+    return _MoEFused.apply(x, weights, idx, w1, w2, w3, recompute, ep_ctx)

@@ -1,6 +1,327 @@
-"""Loader and Python bindings of the in-tree sm_100a extension (placeholder
-until the first kernels land: reports that nothing is available)."""
+"""ctypes bindings of the in-tree sm_100a library ``b200moe/_C/libb200moe.so``.
+
+Every function takes torch tensors, launches on the current CUDA stream and
+returns torch tensors.  ``has(op)`` tells the op layer whether the kernel family
+``op`` is loaded; ``require()`` raises if the library is missing, so a GPU run
+can never fall back silently.  ``launch_count()`` counts launches of this
+library's kernels (the benchmark reports it).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_LIB_PATH = os.path.join(_HERE, "_C", "libb200moe.so")
+_lib = None
+_load_error = None
+_launches = 0
+_status = {}
+
+_FAMILIES = {
+    "gemm": "b2_gemm_nt", "rmsnorm": "b2_rmsnorm_fwd", "router": "b2_router_top2_fwd",
+    "lmhead_ce": "b2_cross_entropy", "adamw": "b2_adamw", "embedding": "b2_embedding_fwd",
+    "rope": "b2_rope", "moe": "b2_moe_plan", "attention": "b2_attention_fwd", "comm": "b2_comm_allreduce",
+    "swiglu": "b2_swiglu_bwd",
+}
+
+
+def _load():
+    global _lib, _load_error
+    if _lib is not None or _load_error is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        _load_error = f"{_LIB_PATH} not found; run `python -m b200moe.build`"
+        return None
+    try:
+        _lib = ctypes.CDLL(_LIB_PATH)
+    except OSError as error:
+        _load_error = str(error)
+        _lib = None
+    return _lib
+
+
+def require():
+    if _load() is None:
+        raise RuntimeError(f"b200moe native library unavailable: {_load_error}")
+    return _lib
 
 
 def has(op: str) -> bool:
-    return False
+    lib = _load()
+    if lib is None:
+        return False
+    symbol = _FAMILIES.get(op)
+    return symbol is not None and hasattr(lib, symbol)
+
+
+def available_ops() -> list:
+    return sorted(op for op in _FAMILIES if has(op))
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def _p(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Device int32 word that kernels set non-zero when a bounded wait ran out."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _status.get(device)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[device] = word
+    return word
+
+
+def check_status() -> int:
+    """Synchronising read of the status word; raises if a kernel gave up."""
+    value = int(status_word().item())
+    if value:
+        raise RuntimeError(f"b200moe kernel reported wait timeout code {value}")
+    return value
+
+
+def _call(name, *args, n: int = 1):
+    global _launches
+    rc = getattr(require(), name)(*args)
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with code {rc}")
+    _launches += n
+
+
+_I, _L, _F = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+def _bf16(t):
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"expected bfloat16, got {t.dtype}")
+    return t
+
+
+# ------------------------------------------------------------------------------ GEMM
+def gemm_nt(x, w, out_dtype=None, tile_expert=None, num_m_tiles=None, num_experts: int = 1):
+    """``x [M,K] @ w[e] [N,K]ᵀ``.  Rows of ``w`` below 17: skinny path, fp32 result."""
+    M, K = x.shape
+    N = w.shape[-2]
+    if N <= 16 and num_experts == 1:
+        out = torch.empty(M, N, dtype=torch.float32, device=x.device)
+        _call("b2_skinny_nt", _p(_bf16(x)), _p(_bf16(w)), _p(out), _I(M), _I(N), _I(K), _stream())
+        return out
+    out_dtype = out_dtype or torch.bfloat16
+    out = torch.empty(M, N, dtype=out_dtype, device=x.device)
+    assert x.stride(-1) == 1 and w.is_contiguous()
+    _call("b2_gemm_nt", _p(_bf16(x)), _p(_bf16(w)), _p(out), _I(M), _I(N), _I(K), _L(x.stride(0)), _L(K), _L(N),
+          _I(num_experts), _p(tile_expert), _p(num_m_tiles), _I(0 if out_dtype == torch.bfloat16 else 4),
+          _p(status_word(x.device)), _stream())
+    return out
+
+
+def gemm_nn(dy, w, w2=None, tile_expert=None, num_m_tiles=None, num_experts: int = 1):
+    """``dy [M,K] @ w[e] [K,N]`` (``w`` rows are the reduction index).  With ``w2``
+    the reduction continues over ``w2``'s rows: ``dy = [a | b]``, result ``a w + b w2``."""
+    M, K = dy.shape
+    N = w.shape[-1]
+    if K <= 16 and num_experts == 1 and w2 is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dy.device)
+        _call("b2_skinny_nn", _p(dy.float().contiguous()), _p(_bf16(w)), _p(out), _I(M), _I(K), _I(N), _stream())
+        return out
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=dy.device)
+    k_split = w.shape[-2] if w2 is not None else 0
+    assert dy.stride(-1) == 1 and w.is_contiguous()
+    _call("b2_gemm_nn", _p(_bf16(dy)), _p(_bf16(w)), _p(w2), _p(out), _I(M), _I(N), _I(K), _I(k_split),
+          _L(dy.stride(0)), _L(N), _L(N), _I(num_experts), _p(tile_expert), _p(num_m_tiles),
+          _p(status_word(dy.device)), _stream())
+    return out
+
+
+def gemm_tn(dy, x, out=None, accumulate: bool = False, out_dtype=None, expert_offsets=None, num_experts: int = 1):
+    """``out[e] (+)= dy[rows_e]ᵀ @ x[rows_e]`` -> ``[E?, N_out, K_in]``; fp32 or bf16 output."""
+    R, M = dy.shape
+    N = x.shape[1]
+    if M <= 16 and expert_offsets is None:
+        if out is None:
+            out = torch.zeros(M, N, dtype=torch.float32, device=dy.device)
+            accumulate = True
+        if out.dtype != torch.float32:
+            raise TypeError("skinny weight gradients accumulate in fp32")
+        if not accumulate:
+            out.zero_()
+        _call("b2_skinny_tn", _p(dy.float().contiguous()), _p(_bf16(x)), _p(out), _I(R), _I(M), _I(N), _stream())
+        return out if out_dtype is None else out.to(out_dtype)
+    want = None
+    if out is None:
+        want = out_dtype or torch.float32
+        store = torch.float32 if want not in (torch.float32, torch.bfloat16) else want
+        shape = (num_experts, M, N) if expert_offsets is not None else (M, N)
+        out = torch.empty(shape, dtype=store, device=dy.device)
+        accumulate = False
+    kind = 1 if out.dtype == torch.float32 else 2
+    assert dy.stride(-1) == 1 and x.stride(-1) == 1 and out.is_contiguous()
+    _call("b2_gemm_tn", _p(_bf16(dy)), _p(_bf16(x)), _p(out), _I(M), _I(N), _I(R), _L(dy.stride(0)), _L(x.stride(0)),
+          _L(N), _I(num_experts), _p(expert_offsets), _I(kind), _F(1.0 if accumulate else 0.0),
+          _p(status_word(dy.device)), _stream())
+    return out if want is None or want == out.dtype else out.to(want)
+
+
+def gemm_swiglu(x, w1, w3, tile_expert=None, num_m_tiles=None, save_gate_up: bool = True):
+    """``h = silu(x w1ᵀ) · (x w3ᵀ)`` per expert tile; optionally also the two pre-activations."""
+    M, K = x.shape
+    E, F = w1.shape[0], w1.shape[1]
+    h = torch.empty(M, F, dtype=torch.bfloat16, device=x.device)
+    gate = torch.empty_like(h) if save_gate_up else None
+    up = torch.empty_like(h) if save_gate_up else None
+    _call("b2_gemm_swiglu", _p(_bf16(x)), _p(_bf16(w1)), _p(_bf16(w3)), _p(h), _p(gate), _p(up), _I(M), _I(F), _I(K),
+          _L(x.stride(0)), _I(E), _p(tile_expert), _p(num_m_tiles), _p(status_word(x.device)), _stream())
+    return h, gate, up
+
+
+# ------------------------------------------------------------------------------ norms
+def rmsnorm_fwd(x, weight, eps):
+    x2 = _bf16(x).reshape(-1, x.shape[-1])
+    y = torch.empty_like(x2)
+    rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+    _call("b2_rmsnorm_fwd", _p(x2), _p(None), _p(weight), _p(None), _p(y), _p(rstd), _I(x2.shape[0]), _I(x2.shape[1]),
+          _F(eps), _stream())
+    return y.view(x.shape), rstd
+
+
+def add_rmsnorm_fwd(x, delta, weight, eps):
+    x2, d2 = _bf16(x).reshape(-1, x.shape[-1]), _bf16(delta).reshape(-1, x.shape[-1])
+    summed, y = torch.empty_like(x2), torch.empty_like(x2)
+    rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+    _call("b2_rmsnorm_fwd", _p(x2), _p(d2), _p(weight), _p(summed), _p(y), _p(rstd), _I(x2.shape[0]), _I(x2.shape[1]),
+          _F(eps), _stream())
+    return summed.view(x.shape), y.view(x.shape), rstd
+
+
+def rmsnorm_bwd(dy, x, weight, rstd, residual_grad=None):
+    x2 = x.reshape(-1, x.shape[-1])
+    dy2 = _bf16(dy).reshape(-1, x.shape[-1])
+    rows, D = x2.shape
+    parts = require().b2_rmsnorm_bwd_parts(_I(rows))
+    partial = torch.empty(parts, D, dtype=torch.float32, device=x.device)
+    dx = torch.empty_like(x2)
+    dw = torch.empty(D, dtype=torch.float32, device=x.device)
+    res = None if residual_grad is None else _bf16(residual_grad).reshape(-1, D).contiguous()
+    _call("b2_rmsnorm_bwd", _p(dy2), _p(x2), _p(weight), _p(rstd), _p(res), _p(dx), _p(partial), _p(dw), _I(rows), _I(D),
+          _stream(), n=2)
+    return dx.view(x.shape), dw
+
+
+# ------------------------------------------------------------------------------ router
+def router_top2_fwd(logits):
+    logits = logits.float().contiguous()
+    T, E = logits.shape
+    weights = torch.empty(T, 2, dtype=torch.float32, device=logits.device)
+    idx = torch.empty(T, 2, dtype=torch.int64, device=logits.device)
+    probs = torch.empty(T, E, dtype=torch.float32, device=logits.device)
+    _call("b2_router_top2_fwd", _p(logits), _p(weights), _p(idx), _p(probs), _I(T), _I(E), _stream())
+    return weights, idx, probs
+
+
+def router_top2_bwd(dweights, probs, idx, weights):
+    T, E = probs.shape
+    dlogits = torch.empty(T, E, dtype=torch.float32, device=probs.device)
+    _call("b2_router_top2_bwd", _p(dweights.float().contiguous()), _p(probs), _p(idx), _p(weights), _p(dlogits), _I(T),
+          _I(E), _stream())
+    return dlogits
+
+
+# ------------------------------------------------------------------------------ loss
+def cross_entropy_fwd_bwd_(logits, targets):
+    """Mean loss; ``logits`` (bf16 [T,V]) is overwritten with d(mean loss)/dlogits."""
+    T, V = logits.shape
+    loss = torch.zeros((), dtype=torch.float32, device=logits.device)
+    _call("b2_cross_entropy", _p(_bf16(logits)), _p(targets.contiguous()), _p(loss), _I(T), _I(V), _F(1.0 / T), _stream())
+    return loss
+
+
+def scale_(x, factor):
+    factor = factor.to(device=x.device, dtype=torch.float32).reshape(1)
+    _call("b2_scale_bf16", _p(_bf16(x)), _p(factor), _L(x.numel()), _stream())
+    return x
+
+
+# ------------------------------------------------------------------------------ optimizer
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def adamw_(p, g, m, v, lr, beta1, beta2, eps, weight_decay, a_t, grad_scale=1.0, p_bf16=None):
+    for t in (p, g, m, v):
+        if not t.is_contiguous():
+            raise ValueError("adamw_ needs contiguous tensors")
+    _call("b2_adamw", _p(p), _p(g), _p(m), _p(v), _p(p_bf16), _L(p.numel()), _I(_DT[p.dtype]), _I(_DT[g.dtype]),
+          _I(_DT[m.dtype]), _F(lr), _F(beta1), _F(beta2), _F(eps), _F(weight_decay), _F(a_t), _F(grad_scale), _stream())
+
+
+def cast_f32_bf16(src, dst):
+    _call("b2_cast_f32_bf16", _p(src), _p(dst), _L(src.numel()), _stream())
+
+
+# ------------------------------------------------------------------------------ embedding / rope
+def embedding_fwd(ids, table):
+    flat = ids.reshape(-1).contiguous()
+    out = torch.empty(flat.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    _call("b2_embedding_fwd", _p(flat), _p(_bf16(table)), _p(out), _I(flat.numel()), _I(table.shape[1]), _stream())
+    return out.view(*ids.shape, table.shape[1])
+
+
+def embedding_bwd(flat_ids, dy2d, main_grad):
+    _call("b2_embedding_bwd", _p(flat_ids.contiguous()), _p(_bf16(dy2d.contiguous())), _p(main_grad),
+          _I(flat_ids.numel()), _I(dy2d.shape[1]), _stream())
+
+
+def rope_inplace(buf, first_elem_offset, tokens, seq, heads, head_dim, pitch, cos, sin, sign):
+    ptr = ctypes.c_void_p(buf.data_ptr() + first_elem_offset * buf.element_size())
+    _call("b2_rope", ptr, _p(cos), _p(sin), _I(tokens), _I(seq), _I(heads), _I(head_dim), _L(pitch), _F(sign), _stream())
+
+
+# ------------------------------------------------------------------------------ MoE routing
+def moe_plan(idx, num_experts, capacity_rows):
+    slots = idx.numel()
+    dev = idx.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    slot_row = torch.empty(slots, **i32)
+    row_slot = torch.empty(capacity_rows, **i32)
+    offs = torch.empty(num_experts, **i32)
+    tile_expert = torch.empty(capacity_rows // 128, **i32)
+    meta = torch.zeros(4, **i32)
+    counts = torch.empty(num_experts, **i32)
+    _call("b2_moe_plan", _p(idx.contiguous()), _I(slots), _I(num_experts), _p(slot_row), _p(row_slot), _p(offs),
+          _p(tile_expert), _p(meta), _p(counts), _I(capacity_rows), _stream())
+    return slot_row, row_slot, offs, tile_expert, meta, counts
+
+
+def moe_gather(x, row_slot, meta, capacity_rows, scale=None, y_perm=None, dweights=None, out=None):
+    D = x.shape[1]
+    if out is None:
+        out = torch.empty(capacity_rows, D, dtype=torch.bfloat16, device=x.device)
+    _call("b2_moe_gather", _p(_bf16(x)), _p(row_slot), _p(meta), _p(scale), _p(y_perm), _p(dweights), _p(out), _I(D),
+          _I(capacity_rows), _stream())
+    return out
+
+
+def moe_combine(y_perm, slot_row, weights, tokens, residual=None):
+    D = y_perm.shape[1]
+    out = torch.empty(tokens, D, dtype=torch.bfloat16, device=y_perm.device)
+    _call("b2_moe_combine", _p(_bf16(y_perm)), _p(slot_row), _p(weights), _p(residual), _p(out), _I(tokens), _I(D),
+          _stream())
+    return out
+
+
+def swiglu_bwd(dh, gate, up, live_rows=None, want_h: bool = True):
+    rows, F = dh.shape
+    dgu = torch.empty(rows, 2 * F, dtype=torch.bfloat16, device=dh.device)
+    h = torch.empty(rows, F, dtype=torch.bfloat16, device=dh.device) if want_h else None
+    _call("b2_swiglu_bwd", _p(_bf16(dh)), _p(gate), _p(up), _p(dgu), _p(h), _p(live_rows), _I(rows), _I(F), _stream())
+    return dgu, h

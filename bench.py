@@ -1,0 +1,372 @@
+"""Headline benchmark: training throughput of the Mixtral-8x7B-like MoE decoder.
+
+``python bench.py --gpus N --steps K --warmup W`` (under ``torch.distributed.run``
+for N > 1) runs full training steps (forward, backward, gradient reduction,
+AdamW) on synthetic tokens with random-init weights and prints one JSON line.
+
+Model per GPU count (layer count scaled so per-GPU work is constant; d_model
+4096, d_ff 14336, 32/8 heads, 8 experts top-2, vocab 32000, sequence 8192,
+32 microbatches of 2 sequences per data rank):
+
+  N=1  8 blocks,  PP1 × FSDP1 × EP1, global batch 64
+  N=2  8 blocks,  PP1 × FSDP2 × EP2, global batch 128
+  N=4  16 blocks, PP2 × FSDP2 × EP2, global batch 128
+  N=8  32 blocks, PP4 × FSDP2 × EP2, global batch 128   (the named configuration)
+
+``value`` is tokens/s normalised to the 32-block model: raw tokens/s times
+``flops_per_token(blocks) / flops_per_token(32)``; at N=8 it is the raw number.
+``tokens_per_s_raw`` and ``mfu`` (of 2.25 PFLOP/s dense bf16 per GPU) are also
+reported.  ``--impl reference`` times the unmodified reference package from
+``baseline/_ref`` through its own public API on the same configuration.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+BASELINE_TOKENS_PER_S = 75076.0
+MODEL = {"d_model": 4096, "d_ff": 14336, "num_head": 32, "experts": 8, "vocab": 32000, "seq": 8192}
+LAYOUT = {1: (1, 1, 8, 64), 2: (1, 2, 8, 128), 4: (2, 2, 8, 128), 8: (4, 2, 8, 128)}  # pp, fsdp, blocks/stage, batch
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=2)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="b200moe", choices=["b200moe", "reference"])
+    # development overrides (change the workload; the JSON line records them)
+    p.add_argument("--layers", type=int, default=None, help="blocks per stage")
+    p.add_argument("--microbatches", type=int, default=32)
+    p.add_argument("--batch", type=int, default=None, help="global batch in sequences")
+    p.add_argument("--seq", type=int, default=MODEL["seq"])
+    p.add_argument("--recompute", default=None, choices=["none", "swiglu", "block"])
+    p.add_argument("--backend", default=None, choices=["fused", "nccl"])
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi every 200 ms."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int = 0):
+        self.gpu, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, peak, power, reasons = [], None, [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            if len(row) < 9:
+                continue
+            try:
+                clocks.append(float(row[1]))
+                peak = float(row[2])
+                power.append(float(row[3]))
+            except ValueError:
+                continue
+            for name, cell in zip(names, row[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": peak,
+                "power_w_max": max(power) if power else None, "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def run_config(args):
+    if args.gpus not in LAYOUT:
+        raise SystemExit(f"--gpus must be one of {sorted(LAYOUT)}")
+    pp, fsdp, blocks, batch = LAYOUT[args.gpus]
+    blocks = args.layers or blocks
+    batch = args.batch or batch
+    return {"pp": pp, "fsdp": fsdp, "ddp": 1, "blocks_per_stage": blocks, "batch": batch,
+            "microbatches": args.microbatches, "seq": args.seq, "experts_per_rank": MODEL["experts"] // fsdp}
+
+
+def init_dist(args):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"WORLD_SIZE={world} does not match --gpus {args.gpus}")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    return rank, world, local, device
+
+
+def measure(step_device, step_e2e, args, device, rank, launches_fn):
+    """Warm up, then time K device-only steps and K end-to-end steps."""
+    import torch
+    import torch.distributed as dist
+
+    def fence():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step_device()
+    fence()
+    sampler = ClockSampler(device.index) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    launches_before = launches_fn()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    last = None
+    for _ in range(args.steps):
+        last = step_device()
+    end.record()
+    fence()
+    launches = launches_fn() - launches_before
+    clocks = sampler.stop() if sampler else None
+    ms = torch.tensor([begin.elapsed_time(end)], dtype=torch.float64, device=device)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    device_ms = float(ms.item()) / args.steps
+    e2e_ms = None
+    if step_e2e is not None:
+        step_e2e()
+        fence()
+        begin.record()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            last = step_e2e()
+        end.record()
+        fence()
+        wall = (time.perf_counter() - t0) * 1e3
+        ms = torch.tensor([max(begin.elapsed_time(end), wall)], dtype=torch.float64, device=device)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        e2e_ms = float(ms.item()) / args.steps
+    return device_ms, e2e_ms, clocks, launches, last
+
+
+def report(args, cfg, device_ms, e2e_ms, clocks, launches, loss, h2d, d2h, impl, extra=None):
+    sys.path.insert(0, ROOT) if ROOT not in sys.path else None
+    from b200moe.utils.metrics import PEAK_BF16_DENSE, flops_per_token
+    blocks_total = cfg["blocks_per_stage"] * cfg["pp"]
+    fpt = flops_per_token(MODEL["d_model"], MODEL["d_ff"], MODEL["num_head"], MODEL["experts"], MODEL["vocab"],
+                          blocks_total, cfg["seq"])
+    fpt32 = flops_per_token(MODEL["d_model"], MODEL["d_ff"], MODEL["num_head"], MODEL["experts"], MODEL["vocab"],
+                            32, cfg["seq"])
+    tokens = cfg["batch"] * cfg["seq"]
+
+    def rate(ms):
+        raw = tokens / (ms / 1e3)
+        return raw, raw * fpt / fpt32
+    raw, value = rate(device_ms)
+    line = {
+        "metric": "total tokens/s (32-block-equivalent), Mixtral-8x7B-like MoE, seq 8192, PP/FSDP/EP training step",
+        "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": device_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": value / BASELINE_TOKENS_PER_S, "dtype": "bf16" if impl == "b200moe" else "fp16+bf16 (stock)",
+        "data": "synthetic uniform token ids, random-init weights", "impl": impl,
+        "tokens_per_s_raw": raw, "mfu": raw * fpt / (args.gpus * PEAK_BF16_DENSE),
+        "gflops_per_token": fpt / 1e9, "loss": loss,
+        "config": {"model": f"{blocks_total}-block 8x7B-like MoE (d_model 4096, d_ff 14336, 32/8 GQA heads, "
+                            f"8 experts top-2, vocab 32000)",
+                   "global_batch": cfg["batch"], "seq_len": cfg["seq"], "microbatches": cfg["microbatches"],
+                   "parallelism": f"pp{cfg['pp']}·fsdp{cfg['fsdp']}·ep{cfg['fsdp']}·ddp{cfg['ddp']}",
+                   "blocks_total": blocks_total,
+                   "l2": "no flush: every step streams >20 GB of weights and activations (inputs larger than L2)"},
+        "clocks": clocks, "gpu_launches": launches,
+    }
+    if e2e_ms is not None:
+        line["e2e"] = {"value": rate(e2e_ms)[1], "unit": "tokens/s", "ms_per_step": e2e_ms,
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    if extra:
+        line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------ this framework
+def bench_b200moe(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    rank, world, local, device = init_dist(args)
+    from b200moe.ops import native
+    from b200moe.ops.functional import cross_entropy
+    from b200moe.parallel import pipelined_train_overlap
+    from b200moe.topology import build_groups
+    from b200moe.trainer import build_model
+    from b200moe.utils.data import BatchStager
+    cfg = run_config(args)
+    recompute = args.recompute or ("none" if cfg["pp"] <= 2 else "swiglu")
+    single = args.gpus == 1
+    config = {
+        "general": {"device": "gpu", "n_workers": world, "gpu_per_node": world, "info_src": 0},
+        "data": {"vocab_size": MODEL["vocab"], "mock_data": True, "seed": 42},
+        "model": {"num_head": MODEL["num_head"], "d_model": MODEL["d_model"], "d_ff": MODEL["d_ff"],
+                  "context_len": cfg["seq"], "num_layers": cfg["blocks_per_stage"],
+                  "num_expert_per_node": cfg["experts_per_rank"], "rope_theta": 10000},
+        "comm": {"backend": args.backend or "fused"},
+        "train": {"fsdp_parallel_num": cfg["fsdp"], "data_parallel_num": 1, "pipeline_parallel_stages": cfg["pp"],
+                  "microbatch_num": cfg["microbatches"], "batch_size": cfg["batch"], "learning_rate": 1e-4,
+                  "optimizer": {"beta1": 0.9, "beta2": 0.999, "lambda": 0.01},
+                  "activation_recompute": recompute,
+                  # one GPU holds all 8 experts of 8 blocks (11.3 G parameters): moments and gradient
+                  # accumulators use the reference's bf16 there; fp32 everywhere else
+                  "expert_state_dtype": "bfloat16" if single else "float32",
+                  "expert_grad_dtype": "bfloat16" if single else "float32"},
+    }
+    mesh = build_groups(config["train"], rank, world, world)
+    comm = None
+    if config["comm"]["backend"] == "fused" and native.has("comm"):
+        from b200moe.comm import make_comm
+        comm = make_comm(mesh, device)
+    torch.manual_seed(1234 + mesh.stage)
+    model, optimizer = build_model(config, mesh, device, mesh.group("fsdp"), mesh.group("ddp"), torch.bfloat16, comm)
+    local_batch = cfg["batch"] // (cfg["fsdp"] * cfg["ddp"])
+    stager = BatchStager(local_batch, cfg["seq"], device)
+    rng = np.random.default_rng(42 + mesh.dp_idx)
+    edge = mesh.stage in (0, mesh.pp - 1)
+    fixed = stager.next(None, rng, MODEL["vocab"], mock_data=True) if edge else (None, None)
+    fixed = tuple(t.clone() if t is not None else None for t in fixed)
+    spec = [local_batch, cfg["seq"], MODEL["d_model"]]
+
+    def run(x, y):
+        return pipelined_train_overlap(model, optimizer, x, y, spec, cfg["microbatches"], mesh.stage, cross_entropy,
+                                       dtype=torch.bfloat16, device=device, pp_group=mesh.group("pp"),
+                                       dp_group=mesh.group("data"))
+
+    def step_device():
+        return run(*fixed)
+
+    def step_e2e():
+        x, y = stager.next(None, rng, MODEL["vocab"], mock_data=True) if edge else (None, None)
+        loss = run(x, y)
+        return float(loss) if torch.is_tensor(loss) else loss      # device -> host read of the step's loss
+
+    device_ms, e2e_ms, clocks, launches, last = measure(
+        step_device, None if args.no_e2e else step_e2e, args, device, rank, native.launch_count)
+    loss = torch.tensor([float(last) if last is not None else 0.0], device=device)
+    dist.all_reduce(loss, op=dist.ReduceOp.MAX)
+    peak = torch.tensor([torch.cuda.max_memory_allocated() / 2 ** 30], device=device)
+    dist.all_reduce(peak, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        report(args, cfg, device_ms, e2e_ms, clocks, launches, float(loss), stager.h2d_bytes if edge else 0, 4,
+               "b200moe", {"peak_mem_gib": float(peak), "activation_recompute": recompute,
+                           "comm_backend": "fused" if comm is not None else "nccl",
+                           "native_ops": native.available_ops()})
+    dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------ reference arm
+def bench_reference(args):
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "implementation")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed"}))
+        return
+    sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != ROOT]
+    sys.path.insert(0, ref_root)
+    try:
+        import numpy as np
+        import torch
+        import torch.distributed as dist
+        rank, world, local, device = init_dist(args)
+        from implementation.distributed.ddp_modules import FSDPWrapperPipelined
+        from implementation.layers import TransformerLMPipelined
+        from implementation.nnfunctions import cross_entropy
+        from implementation.optimizer import AdamW
+        from implementation.startup import parallel_rank_groups
+        from implementation.train_utils import compile_model, get_batch
+        from pipeline import pipelined_train_overlap
+        cfg = run_config(args)
+        train = {"fsdp_parallel_num": cfg["fsdp"], "data_parallel_num": 1, "pipeline_parallel_stages": cfg["pp"]}
+        groups = {}
+        for name, lists in parallel_rank_groups(train, world, world).items():
+            for ranks in lists:
+                g = dist.new_group(ranks=ranks)
+                if rank in ranks:
+                    groups[name] = g
+        width = cfg["fsdp"]
+        stage, dp_idx = rank // width, rank % width
+        torch.backends.cuda.matmul.allow_tf32 = True
+        torch.backends.cudnn.allow_tf32 = True
+        torch.manual_seed(1234 + stage)
+        model = TransformerLMPipelined(MODEL["vocab"], cfg["seq"], MODEL["d_model"], cfg["blocks_per_stage"],
+                                       MODEL["num_head"], stage, cfg["pp"],
+                                       num_expert_per_node=cfg["experts_per_rank"], d_ff=MODEL["d_ff"],
+                                       dp_group=groups["fsdp"], moe_compute_dtype=torch.bfloat16)
+        model.to(device)
+        model = FSDPWrapperPipelined(model, FSDP_communication_group=groups["fsdp"], DDP_communication_group=None,
+                                     compute_dtype=torch.float16, moe_compute_dtype=torch.bfloat16)
+        optimizer = AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01)
+        model = compile_model(model)
+        local_batch = cfg["batch"] // width
+        rng = np.random.default_rng(42 + dp_idx)
+        edge = stage in (0, cfg["pp"] - 1)
+        fixed = get_batch(None, local_batch, cfg["seq"], device, rng=rng, vocab_size=MODEL["vocab"],
+                          mock_data=True) if edge else (None, None)
+        spec = [local_batch, cfg["seq"], MODEL["d_model"]]
+
+        def run(x, y):
+            return pipelined_train_overlap(model, optimizer, x, y, spec, cfg["microbatches"], stage, cross_entropy,
+                                           dtype=torch.float16, device=device, pp_group=groups["pp"],
+                                           dp_group=groups["data"])
+
+        def step_device():
+            return run(*fixed)
+
+        def step_e2e():
+            x, y = get_batch(None, local_batch, cfg["seq"], device, rng=rng, vocab_size=MODEL["vocab"],
+                             mock_data=True) if edge else (None, None)
+            loss = run(x, y)
+            return float(loss) if torch.is_tensor(loss) else loss
+
+        device_ms, e2e_ms, clocks, _, last = measure(step_device, None if args.no_e2e else step_e2e, args, device,
+                                                     rank, lambda: 0)
+        loss = torch.tensor([float(last) if last is not None else 0.0], device=device)
+        dist.all_reduce(loss, op=dist.ReduceOp.MAX)
+        peak = torch.tensor([torch.cuda.max_memory_allocated() / 2 ** 30], device=device)
+        dist.all_reduce(peak, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            report(args, cfg, device_ms, e2e_ms, clocks, 0, float(loss), 2 * local_batch * cfg["seq"] * 8 if edge else 0,
+                   4, "reference", {"peak_mem_gib": float(peak)})
+        dist.destroy_process_group()
+    except Exception as error:  # report instead of failing the driver's run
+        reason = f"{type(error).__name__}: {str(error).splitlines()[0][:300] if str(error) else ''}"
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
+
+
+if __name__ == "__main__":
+    arguments = parse_args()
+    if arguments.impl == "reference":
+        bench_reference(arguments)
+    else:
+        bench_b200moe(arguments)

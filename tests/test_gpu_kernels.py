@@ -1,0 +1,305 @@
+"""sm_100a kernels against plain PyTorch fp32 statements of the same ops."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def native():
+    from b200moe.ops import native as n
+    n.require()
+    return n
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).bfloat16()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 1024, 4096), (1024, 6144, 1024),
+                                   (200, 384, 192), (128, 32000, 512)])
+def test_gemm_nt(native, M, N, K):
+    x, w = _rand(M, K), _rand(N, K, scale=0.05)
+    got = native.gemm_nt(x, w)
+    want = x.float() @ w.float().t()
+    assert _rel(got, want) < 6e-3
+    native.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 1024, 512), (384, 4096, 2048), (256, 320, 128)])
+def test_gemm_nn(native, M, N, K):
+    dy, w = _rand(M, K), _rand(K, N, scale=0.05)
+    got = native.gemm_nn(dy, w)
+    assert _rel(got, dy.float() @ w.float()) < 6e-3
+    native.check_status()
+
+
+@pytest.mark.parametrize("R,M,N", [(128, 128, 256), (512, 256, 512), (4096, 1024, 384), (1024, 6144, 1024)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tn_accumulates(native, R, M, N, dtype):
+    dy, x = _rand(R, M, scale=0.1), _rand(R, N, scale=0.1)
+    base = torch.randn(M, N, device="cuda").to(dtype)
+    out = base.clone()
+    native.gemm_tn(dy, x, out=out, accumulate=True)
+    want = base.float() + dy.float().t() @ x.float()
+    assert _rel(out, want) < (2e-3 if dtype == torch.float32 else 8e-3)
+    fresh = native.gemm_tn(dy, x, out_dtype=torch.float32)
+    assert _rel(fresh, dy.float().t() @ x.float()) < 2e-3
+    native.check_status()
+
+
+def _segments(counts):
+    padded = [(c + 127) // 128 * 128 for c in counts]
+    offs, tiles, row = [], [], 0
+    for e, p in enumerate(padded):
+        tiles += [e] * (p // 128)
+        row += p
+        offs.append(row)
+    dev = dict(device="cuda", dtype=torch.int32)
+    return (torch.tensor(offs, **dev), torch.tensor(tiles, **dev), torch.tensor([len(tiles), row, 0, 0], **dev), row)
+
+
+@pytest.mark.parametrize("counts", [[128, 256], [100, 0, 300, 17], [0, 0, 640, 0], [384] * 4])
+def test_grouped_expert_gemms(native, counts):
+    torch.manual_seed(0)
+    E, D, Fd = len(counts), 256, 512
+    offs, tile_expert, meta, rows = _segments(counts)
+    cap = rows + 256                                  # rows past the live count must be ignored
+    x = torch.zeros(cap, D, device="cuda", dtype=torch.bfloat16)
+    start = 0
+    for e, c in enumerate(counts):
+        x[start:start + c] = _rand(c, D)
+        start = int(offs[e])
+    x[rows:] = float("nan")
+    w1, w3, w2 = _rand(E, Fd, D, scale=0.05), _rand(E, Fd, D, scale=0.05), _rand(E, D, Fd, scale=0.05)
+    h, gate, up = native.gemm_swiglu(x, w1, w3, tile_expert, meta[0:1])
+    y = native.gemm_nt(h, w2, tile_expert=tile_expert, num_m_tiles=meta[0:1], num_experts=E)
+    start = 0
+    for e in range(E):
+        end = int(offs[e])
+        if end > start:
+            xe = x[start:end].float()
+            g, u = xe @ w1[e].float().t(), xe @ w3[e].float().t()
+            he = torch.nn.functional.silu(g) * u
+            assert _rel(gate[start:end], g) < 6e-3 and _rel(up[start:end], u) < 6e-3
+            assert _rel(h[start:end], he) < 8e-3
+            assert _rel(y[start:end], h[start:end].float() @ w2[e].float().t()) < 6e-3
+        start = end
+    # data gradients: dh = dy W2 ; dx = dg W1 + du W3 in one pass
+    dy = torch.zeros(cap, D, device="cuda", dtype=torch.bfloat16)
+    dy[:rows] = _rand(rows, D)
+    dh = native.gemm_nn(dy, w2, tile_expert=tile_expert, num_m_tiles=meta[0:1], num_experts=E)
+    dgu = torch.zeros(cap, 2 * Fd, device="cuda", dtype=torch.bfloat16)
+    dgu[:rows] = _rand(rows, 2 * Fd, scale=0.1)
+    dx = native.gemm_nn(dgu, w1, w2=w3, tile_expert=tile_expert, num_m_tiles=meta[0:1], num_experts=E)
+    acc = torch.randn(E, Fd, D, device="cuda")
+    dw1 = acc.clone()
+    native.gemm_tn(dgu[:, :Fd], x, out=dw1, accumulate=True, expert_offsets=offs, num_experts=E)
+    dw_new = native.gemm_tn(dy, h, out_dtype=torch.float32, expert_offsets=offs, num_experts=E)
+    start = 0
+    for e in range(E):
+        end = int(offs[e])
+        if end > start:
+            assert _rel(dh[start:end], dy[start:end].float() @ w2[e].float()) < 6e-3
+            want = dgu[start:end, :Fd].float() @ w1[e].float() + dgu[start:end, Fd:].float() @ w3[e].float()
+            assert _rel(dx[start:end], want) < 6e-3
+            assert _rel(dw1[e], acc[e] + dgu[start:end, :Fd].float().t() @ x[start:end].float()) < 3e-3
+            assert _rel(dw_new[e], dy[start:end].float().t() @ h[start:end].float()) < 3e-3
+        else:
+            assert torch.equal(dw1[e], acc[e]) and float(dw_new[e].abs().max()) == 0.0
+        start = end
+    native.check_status()
+
+
+def test_rmsnorm_forward_backward(native):
+    from b200moe import ops
+    from b200moe.ops import functional as Fn
+    for D in (128, 4096):
+        x = _rand(300, D).requires_grad_(True)
+        d = _rand(300, D).requires_grad_(True)
+        w = (torch.rand(D, device="cuda") + 0.5).requires_grad_(True)
+        y = ops.rmsnorm(x, w)
+        xr, wr = x.detach().float().requires_grad_(True), w.detach().clone().requires_grad_(True)
+        yr = Fn.rmsnorm_ref(xr, wr)
+        assert _rel(y, yr) < 5e-3
+        dy = _rand(300, D)
+        y.backward(dy)
+        yr.backward(dy.float())
+        assert _rel(x.grad, xr.grad) < 8e-3 and _rel(w.grad, wr.grad) < 8e-3
+        x.grad = w.grad = None
+        s, y2 = ops.add_rmsnorm(x, d, w)
+        (s.float().sum() * 0.5 + (y2.float() * dy.float()).sum()).backward()
+        xs = (x.detach().float() + d.detach().float()).bfloat16().float().requires_grad_(True)
+        wr2 = w.detach().clone().requires_grad_(True)
+        (xs.sum() * 0.5 + (Fn.rmsnorm_ref(xs, wr2) * dy.float()).sum()).backward()
+        assert _rel(s, xs) < 1e-6 and _rel(x.grad, xs.grad) < 8e-3 and _rel(d.grad, xs.grad) < 8e-3
+        assert _rel(w.grad, wr2.grad) < 8e-3
+
+
+def test_router_linear_and_top2(native):
+    from b200moe import ops
+    from b200moe.ops import functional as Fn
+    T, D, E = 1000, 512, 8
+    x = _rand(T, D).requires_grad_(True)
+    w = _rand(E, D, scale=0.05).requires_grad_(True)
+    logits = ops.linear(x, w)
+    assert logits.dtype == torch.float32
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    lr = xr @ wr.t()
+    assert _rel(logits, lr) < 1e-3
+    weights, idx = ops.router_top2(logits)
+    wref, iref = Fn.router_top2_ref(lr, 2)
+    assert torch.equal(idx, iref) and _rel(weights, wref) < 1e-4
+    dw = torch.randn(T, 2, device="cuda")
+    weights.backward(dw)
+    wref.backward(dw)
+    assert _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
+
+
+def test_cross_entropy_and_lm_head(native):
+    from b200moe import ops
+    T, D, V = 512, 256, 32000
+    h = _rand(2, T // 2, D).requires_grad_(True)
+    w = _rand(V, D, scale=0.05).requires_grad_(True)
+    t = torch.randint(0, V, (2, T // 2), device="cuda")
+    loss = ops.lm_head_cross_entropy(h, w, t)
+    hr, wr = h.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy((hr @ wr.t()).reshape(-1, V), t.reshape(-1))
+    assert abs(float(loss) - float(ref)) < 2e-2
+    (loss * 0.5).backward()
+    (ref * 0.5).backward()
+    assert _rel(h.grad, hr.grad) < 3e-2 and _rel(w.grad, wr.grad) < 3e-2
+
+
+def test_embedding_rope_adamw(native):
+    from b200moe import ops
+    from b200moe.ops import functional as Fn
+    from b200moe.ops.attention import rope_qk_
+    from b200moe.optim import AdamW
+    table = _rand(1000, 128)
+    table.main_grad = torch.zeros(1000, 128, device="cuda")
+    table.requires_grad_(True)
+    ids = torch.randint(0, 1000, (4, 33), device="cuda")
+    out = ops.embedding(ids, table)
+    assert torch.equal(out, table.detach()[ids])
+    dy = _rand(4, 33, 128)
+    out.backward(dy)
+    want = torch.zeros(1000, 128, device="cuda").index_add_(0, ids.reshape(-1), dy.reshape(-1, 128).float())
+    assert _rel(table.main_grad, want) < 1e-5
+    # rope
+    B, S, H, hd = 2, 64, 6, 128
+    cos, sin = Fn.rope_tables(10000.0, hd, 128, device="cuda")
+    qkv = _rand(B, S, H, hd).requires_grad_(True)
+    rotated = rope_qk_((qkv * 1.0).view(B * S, H * hd), S, H, 4, hd, cos, sin).view(B, S, H, hd)
+    ref_in = qkv.detach().float().requires_grad_(True)
+    ref = torch.cat((Fn.apply_rope_ref(ref_in[:, :, :4].transpose(1, 2), cos[:S], sin[:S]).transpose(1, 2),
+                     ref_in[:, :, 4:]), dim=2)
+    assert _rel(rotated, ref) < 5e-3
+    g = _rand(B, S, H, hd)
+    rotated.backward(g)
+    ref.backward(g.float())
+    assert _rel(qkv.grad, ref_in.grad) < 5e-3
+    # adamw: bf16 parameter with fp32 gradient accumulator and bf16 moments, and plain fp32
+    for p_dt, g_dt, s_dt in [(torch.bfloat16, torch.float32, torch.bfloat16), (torch.float32, torch.float32, torch.float32),
+                             (torch.bfloat16, torch.bfloat16, torch.float32)]:
+        p = torch.nn.Parameter(torch.randn(4097, device="cuda").to(p_dt))
+        cpu = torch.nn.Parameter(p.detach().cpu().clone())
+        p.main_grad = torch.randn(4097, device="cuda").to(g_dt)
+        cpu.main_grad = p.main_grad.cpu().clone()
+        o1, o2 = AdamW([p], lr=1e-2, state_dtype=s_dt), AdamW([cpu], lr=1e-2, state_dtype=s_dt)
+        for _ in range(3):
+            o1.step()
+            o2.step()
+        assert _rel(p.detach().cpu(), cpu.detach()) < (1e-6 if p_dt == torch.float32 else 4e-3)
+
+
+@pytest.mark.parametrize("T,E", [(257, 4), (1024, 8), (64, 8)])
+def test_moe_plan_gather_combine(native, T, E):
+    idx = torch.stack([torch.randperm(E, device="cuda")[:2] for _ in range(T)])
+    if T == 64:
+        idx[:] = torch.tensor([5, 2], device="cuda")          # everything on two experts
+    from b200moe.ops.moe_fused import capacity_rows
+    cap = capacity_rows(T * 2, E)
+    slot_row, row_slot, offs, tile_expert, meta, counts = native.moe_plan(idx, E, cap)
+    flat = idx.reshape(-1)
+    assert torch.equal(counts.long(), torch.bincount(flat, minlength=E))
+    ends = offs.tolist()
+    assert int(meta[1]) == ends[-1] and int(meta[0]) == ends[-1] // 128 and int(meta[2]) == 0
+    start = 0
+    for e, end in enumerate(ends):
+        slots_e = torch.nonzero(flat == e).flatten()
+        assert torch.equal(slot_row[slots_e].long(), torch.arange(start, start + slots_e.numel(), device="cuda"))
+        assert torch.equal(row_slot[start:start + slots_e.numel()].long(), slots_e)
+        assert bool((row_slot[start + slots_e.numel():end] == -1).all())
+        assert bool((tile_expert[start // 128:end // 128] == e).all())
+        start = end
+    x = _rand(T, 256)
+    xp = native.moe_gather(x, row_slot, meta, cap)
+    live = int(meta[1])
+    want = torch.where(row_slot[:live, None] >= 0, x[(row_slot[:live].clamp_min(0) // 2).long()], torch.zeros_like(x[:1]))
+    assert torch.equal(xp[:live], want)
+    w = torch.rand(T, 2, device="cuda")
+    out = native.moe_combine(xp, slot_row, w, T)
+    assert _rel(out, x.float() * w.sum(1, keepdim=True)) < 5e-3
+
+
+@pytest.mark.parametrize("recompute", [False, True])
+def test_moe_block_matches_torch_path(native, recompute):
+    from b200moe import ops
+    from b200moe.ops.moe import moe_ffn
+    torch.manual_seed(1)
+    T, D, Fd, E = 640, 256, 512, 4
+    x = _rand(T, D)
+    logits = torch.randn(T, E, device="cuda")
+    w1, w3, w2 = _rand(E, Fd, D, scale=0.06), _rand(E, Fd, D, scale=0.06), _rand(E, D, Fd, scale=0.06)
+    dout = _rand(T, D)
+    results = []
+    for use_native in (True, False):
+        ops.set_native(use_native)
+        try:
+            xs = x.clone().requires_grad_(True)
+            lg = logits.clone().requires_grad_(True)
+            params = [p.clone().requires_grad_(True) for p in (w1, w2, w3)]
+            weights, idx = ops.router_top2(lg)
+            out = moe_ffn(xs, weights, idx, *params, recompute=recompute)
+            out.backward(dout)
+            results.append([out.detach(), xs.grad, lg.grad] + [p.grad for p in params])
+        finally:
+            ops.set_native(True)
+    for got, want in zip(*results):
+        assert _rel(got, want) < 2e-2
+    native.check_status()
+
+
+def test_tiny_model_native_vs_torch_path(native):
+    from b200moe import ops
+    from b200moe.models import TransformerLMPipelined
+    from b200moe.ops.functional import cross_entropy
+    from b200moe.optim import AdamW
+    from b200moe.parallel import FSDPWrapperPipelined, pipelined_train_overlap
+    losses = []
+    for use_native in (True, False):
+        ops.set_native(use_native)
+        try:
+            torch.manual_seed(3)
+            model = TransformerLMPipelined(2048, 256, 512, 2, 4, 0, 1, num_expert_per_node=4, d_ff=1024).cuda()
+            wrapped = FSDPWrapperPipelined(model, None, None, compute_dtype=torch.bfloat16)
+            opt = AdamW(wrapped.parameters(), lr=1e-3, weight_decay=0.01)
+            ids = torch.randint(0, 2048, (4, 257), device="cuda")
+            run = []
+            for _ in range(4):
+                run.append(float(pipelined_train_overlap(wrapped, opt, ids[:, :-1], ids[:, 1:], [4, 256, 512], 2, 0,
+                                                         cross_entropy, dtype=torch.bfloat16, device=ids.device)))
+            losses.append(run)
+        finally:
+            ops.set_native(True)
+    assert losses[0][-1] < losses[0][0]
+    assert losses[0] == pytest.approx(losses[1], abs=5e-2)
+    native.check_status()
+    assert native.launch_count() > 0
