@@ -1,0 +1,347 @@
+"""Peer-memory communication layer (NVLink 5 / NVSwitch).
+
+``torch.distributed`` (NCCL) stays the plumbing: bootstrap, object broadcast,
+barriers, pipeline send/recv and the symmetric-memory rendezvous.  On top of it
+this module allocates symmetric buffers (``torch.distributed._symmetric_memory``:
+the same allocation mapped into every rank of a group, optionally bound to an
+NVSwitch multicast address) and drives the kernels of ``csrc/comm.cu`` that read
+and write those buffers through peer pointers:
+
+* ``EPContext``: expert-parallel dispatch / return of token rows, forward and
+  backward, with a device-side count exchange (replaces the reference's
+  ``TensorExchange`` all-to-alls and their ``.cpu()`` split sync,
+  implementation/layers.py:14-52,139-213);
+* ``Comm.fused_update``: FSDP reduce-scatter + AdamW + weight all-gather in one
+  kernel (replaces per-parameter ``reduce_scatter_tensor`` + eager AdamW + the
+  per-microbatch all-gathers, implementation/distributed/ddp_modules.py:24-100,
+  219-292);
+* ``Comm.allreduce_avg``: replica all-reduce, one-shot / two-shot / NVLS chosen
+  by message size (replaces ddp_modules.py:274-287).
+
+Sequence numbers: every synchronising phase owns a signal slot and a counter
+that all ranks of the group advance in the same order.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+
+MAX_RANKS = 8
+_U64x8 = ctypes.c_ulonglong * MAX_RANKS
+
+# signal slots
+SIG_EP_COUNTS, SIG_EP_FWD_DATA, SIG_EP_FWD_RET, SIG_EP_BWD_DATA, SIG_EP_BWD_RET = 0, 1, 2, 3, 4
+SIG_FSDP = 8      # +1
+SIG_AR = 12       # +1
+NUM_SLOTS = 32
+
+
+class SymmBuffer:
+    """One symmetric allocation: the local tensor plus every rank's address."""
+
+    def __init__(self, numel: int, dtype, device, group, zero: bool = True):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
+        if zero:
+            self.tensor.zero_()
+        self.handle = symm_mem.rendezvous(self.tensor, group)
+        ptrs = list(self.handle.buffer_ptrs)
+        self.world = len(ptrs)
+        self.rank = self.handle.rank
+        self.ptrs = _U64x8(*(ptrs + [0] * (MAX_RANKS - len(ptrs))))
+        mc = 0
+        try:
+            if self.handle.has_multicast_support:
+                mc = int(self.handle.multicast_ptr)
+        except Exception:
+            mc = 0
+        self.mc_ptr = mc
+
+    def table(self):
+        return self.ptrs
+
+
+def _null_table():
+    return _U64x8(*([0] * MAX_RANKS))
+
+
+def _i(v):
+    return ctypes.c_int(int(v))
+
+
+def _ptr(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class GroupComm:
+    """Signal pad, block counter and sequence numbers of one process group."""
+
+    def __init__(self, group, device):
+        self.group = group
+        self.device = device
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.sig = SymmBuffer(NUM_SLOTS * MAX_RANKS, torch.int32, device, group)
+        self.counter = torch.zeros(8, dtype=torch.int32, device=device)
+        self.seq = [0] * NUM_SLOTS
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def next_seq(self, slot: int) -> int:
+        self.seq[slot] += 1
+        return self.seq[slot]
+
+    def my_sig(self):
+        return ctypes.c_void_p(self.sig.tensor.data_ptr())
+
+
+class Comm:
+    def __init__(self, mesh, device):
+        native.require()
+        self.mesh = mesh
+        self.device = device
+        self.status = native.status_word(device)
+        self.fsdp = GroupComm(mesh.group("fsdp"), device) if mesh.fsdp > 1 else None
+        self.ddp = GroupComm(mesh.group("ddp"), device) if mesh.ddp > 1 else None
+        self._symm = {}
+        self._ep = {}
+        self._ar_stage = {}
+        self._entries = {}
+
+    # -- allocation ----------------------------------------------------------------------
+    def alloc_flat(self, numel: int, dtype):
+        """Symmetric, zero-filled flat buffer over the FSDP group (plain memory
+        when the group has one rank)."""
+        if self.fsdp is None:
+            return torch.zeros(numel, dtype=dtype, device=self.device)
+        padded = (numel + 255) // 256 * 256
+        buf = SymmBuffer(padded, dtype, self.device, self.fsdp.group)
+        view = buf.tensor[:numel]
+        self._symm[view.data_ptr()] = buf
+        return view
+
+    def _buffer_of(self, tensor) -> SymmBuffer:
+        return self._symm[tensor.data_ptr()]
+
+    # -- FSDP ----------------------------------------------------------------------------
+    def _entry_table(self, flat):
+        key = id(flat)
+        if key not in self._entries:
+            rows = [[e["full_off"], e["shard_off"], e["shard_numel"]] for e in flat.entries]
+            self._entries[key] = torch.tensor(rows, dtype=torch.int64, device=self.device)
+        return self._entries[key]
+
+    def _fsdp_launch(self, flat, mode, lr=0.0, beta1=0.0, beta2=0.0, eps=0.0, wd=0.0, a_t=0.0):
+        g = self.fsdp
+        entries = self._entry_table(flat)
+        if flat.m is None:
+            flat.m = torch.zeros_like(flat.master)
+            flat.v = torch.zeros_like(flat.master)
+        seq = g.next_seq(SIG_FSDP)
+        native._call("b2_fsdp_step", self._buffer_of(flat.full_g).table(), self._buffer_of(flat.full_w).table(),
+                     g.sig.table(), _ptr(entries), _i(len(flat.entries)), _i(g.rank), _i(g.world), _i(seq),
+                     _i(SIG_FSDP), _ptr(flat.master), _ptr(flat.m), _ptr(flat.v), _ptr(flat.shard_grad),
+                     ctypes.c_float(lr), ctypes.c_float(beta1), ctypes.c_float(beta2), ctypes.c_float(eps),
+                     ctypes.c_float(wd), ctypes.c_float(a_t), _i(mode), _ptr(g.counter), _ptr(self.status), _stream())
+
+    def allgather_cast(self, flat):
+        self._fsdp_launch(flat, 3)
+
+    def reduce_scatter_avg(self, flat):
+        self._fsdp_launch(flat, 0)
+
+    def fused_update(self, flat, reduce: bool, lr, beta1, beta2, eps, wd, a_t):
+        """AdamW on the owned shards and push of the new bf16 weights to every rank;
+        with ``reduce`` the gradient reduce-scatter happens in the same kernel."""
+        self._fsdp_launch(flat, 1 if reduce else 2, lr, beta1, beta2, eps, wd, a_t)
+
+    # -- replica all-reduce -----------------------------------------------------------------
+    ONE_SHOT_MAX = 1 << 18      # floats: below 1 MiB latency dominates, every rank reads everything
+    NVLS_MIN = 1 << 22          # floats: from 16 MiB the in-switch reduction wins
+
+    def allreduce_avg(self, tensor, group=None, kind: str | None = None):
+        """In-place average of an fp32 tensor over the replica group, staged through a
+        symmetric buffer in chunks."""
+        g = self.ddp if group is None or group is self.mesh.group("ddp") else None
+        if g is None:
+            dist.all_reduce(tensor, op=dist.ReduceOp.AVG, group=group)
+            return tensor
+        if tensor.dtype != torch.float32:
+            work = tensor.float()
+            self.allreduce_avg(work, group, kind)
+            tensor.copy_(work)
+            return tensor
+        flat = tensor.reshape(-1)
+        stage = self._ar_stage.get("f32")
+        if stage is None:
+            stage = SymmBuffer(1 << 26, torch.float32, self.device, g.group)     # 256 MiB
+            self._ar_stage["f32"] = stage
+        cap = stage.tensor.numel()
+        for lo in range(0, flat.numel(), cap):
+            n = min(cap, flat.numel() - lo)
+            padded = (n + 3) // 4 * 4
+            stage.tensor[:n].copy_(flat[lo:lo + n])
+            if padded != n:
+                stage.tensor[n:padded].zero_()
+            chosen = kind or ("oneshot" if padded <= self.ONE_SHOT_MAX else
+                              ("nvls" if stage.mc_ptr and padded >= self.NVLS_MIN else "twoshot"))
+            seq = g.next_seq(SIG_AR)
+            out = flat[lo:lo + n] if (chosen == "oneshot" and padded == n) else None
+            scratch = out if out is not None else (torch.empty(padded, dtype=torch.float32, device=self.device)
+                                                   if chosen == "oneshot" else None)
+            native._call("b2_comm_allreduce", stage.table(), g.sig.table(), ctypes.c_void_p(stage.mc_ptr),
+                         _ptr(scratch), _i({"oneshot": 0, "twoshot": 1, "nvls": 2}[chosen]), _i(g.rank), _i(g.world),
+                         _i(seq), _i(SIG_AR), ctypes.c_longlong(padded), ctypes.c_float(1.0 / g.world),
+                         _ptr(g.counter[1:]), _ptr(self.status), _stream())
+            if chosen == "oneshot":
+                if out is None:
+                    flat[lo:lo + n].copy_(scratch[:n])
+            else:
+                flat[lo:lo + n].copy_(stage.tensor[:n])
+        return tensor
+
+    # -- expert parallel --------------------------------------------------------------------
+    def ep_context(self, tokens: int, dim: int, experts_total: int, capacity_factor: float = 1.5):
+        key = (tokens, dim, experts_total)
+        ctx = self._ep.get(key)
+        if ctx is None:
+            ctx = EPContext(self, tokens, dim, experts_total, capacity_factor)
+            self._ep[key] = ctx
+        return ctx
+
+
+@dataclass
+class Route:
+    cap: int
+    offs: torch.Tensor
+    tile_expert: torch.Tensor
+    meta: torch.Tensor
+    x_perm: torch.Tensor
+    slot_row: torch.Tensor
+    slot_dest: torch.Tensor
+    row_tag: torch.Tensor
+    row_src: torch.Tensor
+    seg_live_end: torch.Tensor
+
+
+class _Landing:
+    """Symmetric landing area for pushed rows plus their per-row tags."""
+
+    def __init__(self, rows, dim, device, group, with_scalar):
+        self.rows = SymmBuffer(rows * dim, torch.bfloat16, device, group, zero=False)
+        self.tag = SymmBuffer(rows, torch.int32, device, group)
+        self.src = SymmBuffer(rows, torch.int32, device, group)
+        self.scalar = SymmBuffer(rows, torch.float32, device, group) if with_scalar else None
+
+
+class EPContext:
+    """Dispatch and return of token rows between the ranks of the expert group."""
+
+    def __init__(self, comm: Comm, tokens: int, dim: int, experts_total: int, capacity_factor: float):
+        g = comm.fsdp
+        self.comm, self.g = comm, g
+        self.tokens, self.dim, self.experts_total = tokens, dim, experts_total
+        self.ep = g.world
+        self.e_local = experts_total // self.ep
+        self.slots = tokens * 2
+        worst = self.slots * self.ep
+        want = min(worst, int(self.slots * capacity_factor))
+        self.cap = (want + self.e_local * 127 + 127) // 128 * 128
+        dev = comm.device
+        self.counts_all = SymmBuffer(MAX_RANKS * 32, torch.int32, dev, g.group)
+        self.fwd_land = _Landing(self.cap, dim, dev, g.group, with_scalar=False)
+        self.bwd_land = _Landing(self.cap, dim, dev, g.group, with_scalar=True)
+        self.fwd_ret = SymmBuffer(self.slots * dim, torch.bfloat16, dev, g.group, zero=False)
+        self.bwd_ret = SymmBuffer(self.slots * dim, torch.bfloat16, dev, g.group, zero=False)
+        self.ret_scalar = SymmBuffer(self.slots, torch.float32, dev, g.group)
+        self.slot_ids = torch.arange(self.slots, dtype=torch.int32, device=dev)
+        self.null = _null_table()
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=g.group)
+
+    # forward: tokens -> expert owners
+    def dispatch(self, x, idx) -> Route:
+        g, dev = self.g, x.device
+        i32 = dict(dtype=torch.int32, device=dev)
+        slot_row, slot_dest = torch.empty(self.slots, **i32), torch.empty(self.slots, **i32)
+        offs, seg_live_end = torch.empty(self.e_local, **i32), torch.empty(self.e_local, **i32)
+        tile_expert = torch.empty(self.cap // 128, **i32)
+        meta = torch.zeros(4, **i32)
+        seq = g.next_seq(SIG_EP_COUNTS)
+        native._call("b2_ep_plan", _ptr(idx.contiguous()), _i(self.slots), _i(self.experts_total), _i(self.ep),
+                     _i(g.rank), _i(seq), _i(self.cap), self.counts_all.table(), g.sig.table(), _i(SIG_EP_COUNTS),
+                     _ptr(slot_row), _ptr(slot_dest), _ptr(offs), _ptr(seg_live_end), _ptr(tile_expert), _ptr(meta),
+                     _ptr(self.comm.status), _stream())
+        seq = g.next_seq(SIG_EP_FWD_DATA)
+        self._push(x, slot_row, slot_dest, self.slot_ids, None, None, self.slots, 1, self.cap, seq, SIG_EP_FWD_DATA,
+                   self.fwd_land)
+        x_perm = torch.empty(self.cap, self.dim, dtype=torch.bfloat16, device=dev)
+        row_tag, row_src = torch.empty(self.cap, **i32), torch.empty(self.cap, **i32)
+        land = self.fwd_land
+        native._call("b2_ep_consume", _ptr(land.rows.tensor), _ptr(land.tag.tensor), _ptr(land.src.tensor), _ptr(None),
+                     _ptr(tile_expert), _ptr(seg_live_end), _ptr(meta), _ptr(None), self.null, _ptr(x_perm),
+                     _ptr(row_tag), _ptr(row_src), g.my_sig(), _i(self.dim), _i(self.cap), _i(self.ep), _i(seq),
+                     _i(SIG_EP_FWD_DATA), _ptr(self.comm.status), _stream())
+        return Route(self.cap, offs, tile_expert, meta, x_perm, slot_row, slot_dest, row_tag, row_src, seg_live_end)
+
+    def _push(self, src, row_of, dest_of, tag_of, scalar_of, live_items, items, shift, dest_cap, seq, slot, land):
+        g = self.g
+        if isinstance(land, _Landing):
+            rows, tag, source = land.rows.table(), land.tag.table(), land.src.table()
+            scalar = land.scalar.table() if land.scalar is not None else self.null
+        else:
+            rows, tag, source, scalar = land.table(), self.null, self.null, self.null
+        native._call("b2_ep_push", _ptr(src), _ptr(row_of), _ptr(dest_of), _ptr(tag_of), _ptr(scalar_of),
+                     _ptr(live_items), _i(items), _i(self.dim), _i(shift), _i(dest_cap), _i(g.rank), _i(self.ep),
+                     _i(seq), _i(slot), rows, tag, source, scalar, g.sig.table(), _ptr(g.counter[2:]), _stream())
+
+    def _wait(self, slot, seq):
+        native._call("b2_ep_wait", self.g.my_sig(), _i(slot), _i(self.ep), _i(seq), _ptr(self.comm.status), _stream())
+
+    # forward: expert outputs -> token owners, weighted sum
+    def combine(self, route: Route, y_perm, weights, tokens):
+        seq = self.g.next_seq(SIG_EP_FWD_RET)
+        self._push(y_perm, route.row_tag, route.row_src, None, None, route.meta[1:2], route.cap, 0, self.slots, seq,
+                   SIG_EP_FWD_RET, self.fwd_ret)
+        self._wait(SIG_EP_FWD_RET, seq)
+        ret = self.fwd_ret.tensor.view(self.slots, self.dim)
+        return native.moe_combine(ret, self.slot_ids, weights, tokens)
+
+    # backward of combine: d(out) rows -> expert owners, scaled by the routing weight there
+    def combine_backward(self, route: Route, dout, y_perm, weights):
+        g = self.g
+        seq = g.next_seq(SIG_EP_BWD_DATA)
+        self._push(dout, route.slot_row, route.slot_dest, self.slot_ids, weights.reshape(-1), None, self.slots, 1,
+                   self.cap, seq, SIG_EP_BWD_DATA, self.bwd_land)
+        dy_perm = torch.empty(self.cap, self.dim, dtype=torch.bfloat16, device=dout.device)
+        land = self.bwd_land
+        native._call("b2_ep_consume", _ptr(land.rows.tensor), _ptr(land.tag.tensor), _ptr(land.src.tensor),
+                     _ptr(land.scalar.tensor), _ptr(route.tile_expert), _ptr(route.seg_live_end), _ptr(route.meta),
+                     _ptr(y_perm), self.ret_scalar.table(), _ptr(dy_perm), _ptr(None), _ptr(None), g.my_sig(),
+                     _i(self.dim), _i(self.cap), _i(self.ep), _i(seq), _i(SIG_EP_BWD_DATA), _ptr(self.comm.status),
+                     _stream())
+        return dy_perm
+
+    # backward of dispatch: d(x_perm) rows -> token owners, summed over the two slots
+    def dispatch_backward(self, route: Route, dx_perm, tokens):
+        seq = self.g.next_seq(SIG_EP_BWD_RET)
+        self._push(dx_perm, route.row_tag, route.row_src, None, None, route.meta[1:2], route.cap, 0, self.slots, seq,
+                   SIG_EP_BWD_RET, self.bwd_ret)
+        self._wait(SIG_EP_BWD_RET, seq)
+        ret = self.bwd_ret.tensor.view(self.slots, self.dim)
+        dx = native.moe_combine(ret, self.slot_ids, None, tokens)
+        dweights = self.ret_scalar.tensor.view(tokens, 2).clone()
+        return dx, dweights
+
+
+def make_comm(mesh, device) -> Comm:
+    return Comm(mesh, device)

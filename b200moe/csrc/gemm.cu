@@ -1,5 +1,5 @@
 // bf16 GEMM family on 5th-generation tensor cores (tcgen05), fp32 accumulation in
-// tensor memory, operands staged by TMA (plain tile loads, no cluster multicast).
+// tensor memory, operands staged by TMA (one plain tile load per CTA and tile).
 //
 // One persistent kernel template covers every contraction of the training step:
 //   NT  y = x W^T            (forward linears, grouped expert forward)

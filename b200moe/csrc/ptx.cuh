@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the kernels use: mbarrier,
-// TMA tile loads (never with cluster multicast), tcgen05 (TMEM allocation, MMA,
+// plain per-CTA TMA tile loads, tcgen05 (TMEM allocation, MMA,
 // commit, load) and the fences that order them.  Every wait is bounded: it gives
 // up after a cycle budget and reports through its return value.
 #pragma once
@@ -59,7 +59,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return true;
 }
 
-// ---------------------------------------------------------------- TMA (2-D tiles, no multicast)
+// ---------------------------------------------------------------- TMA (2-D tiles, one CTA per load)
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

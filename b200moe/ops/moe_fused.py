@@ -85,12 +85,12 @@ class _MoEFused(torch.autograd.Function):
             _, gate, up = native.gemm_swiglu(x_perm, w1, w3, tile_expert, tiles, save_gate_up=True)
         else:
             gate, up = rest
-        dweights = torch.zeros(tokens, 2, dtype=torch.float32, device=dout.device)
         if ep_ctx is None:
+            dweights = torch.zeros(tokens, 2, dtype=torch.float32, device=dout.device)
             dy_perm = native.moe_gather(dout, row_slot, meta, cap, scale=weights.view(-1), y_perm=y_perm,
                                         dweights=dweights.view(-1))
         else:
-            dy_perm = ep_ctx.combine_backward(route, dout, y_perm, weights, dweights)
+            dy_perm = ep_ctx.combine_backward(route, dout, y_perm, weights)
         dh = native.gemm_nn(dy_perm, w2, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=experts)
         dgu, h = native.swiglu_bwd(dh, gate, up, live_rows=live_rows)
         del dh, gate, up
@@ -101,7 +101,7 @@ class _MoEFused(torch.autograd.Function):
         if ep_ctx is None:
             dx = native.moe_combine(dx_perm, slot_row, None, tokens)
         else:
-            dx = ep_ctx.dispatch_backward(route, dx_perm, tokens)
+            dx, dweights = ep_ctx.dispatch_backward(route, dx_perm, tokens)
         return dx, dweights, None, dw1, dw2, dw3, None, None
 
 

@@ -94,8 +94,10 @@ class AdamW(torch.optim.Optimizer):
                 if flat is not None:
                     if id(flat) not in done_flats:
                         done_flats.add(id(flat))
-                        adamw_update_(flat.master, flat.shard_grad, flat.m, flat.v,
-                                      lr, beta1, beta2, eps, decay, a_t)
+                        fused = getattr(flat, "fused_update", None)
+                        if fused is None or not fused(lr, beta1, beta2, eps, decay, a_t):
+                            adamw_update_(flat.master, flat.shard_grad, flat.m, flat.v,
+                                          lr, beta1, beta2, eps, decay, a_t)
                     continue
                 adamw_update_(p.data, grad, m, v, lr, beta1, beta2, eps, decay, a_t,
                               grad_scale=getattr(p, "_grad_scale", 1.0))

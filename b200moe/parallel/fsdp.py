@@ -160,6 +160,16 @@ class FSDPWrapperPipelined(nn.Module):
 
         if hasattr(module, "activation_dtype"):
             module.activation_dtype = compute_dtype
+        self.fused = backend == "fused" and comm is not None and device.type == "cuda"
+        self._pending_reduce = False
+        self._weights_fresh = False
+        if self.fused:
+            from ..models.layers import MoELayerMulti
+            for sub in module.modules():
+                if isinstance(sub, MoELayerMulti):
+                    sub.comm = comm
+        if device.type == "cuda":
+            self.flat.fused_update = self._fused_update
         self._gain_flat = None
         self._seen_versions = None
         self.materialize()
@@ -207,7 +217,7 @@ class FSDPWrapperPipelined(nn.Module):
     def materialize(self):
         """Refresh the gathered compute weights from the fp32 master shards."""
         flat = self.flat
-        if self.backend == "fused" and self.comm is not None and self.group_size > 1:
+        if getattr(self, "fused", False) and self.group_size > 1:
             self.comm.allgather_cast(flat)
         else:
             for e in flat.entries:
@@ -222,7 +232,33 @@ class FSDPWrapperPipelined(nn.Module):
     def _versions(self):
         return self.flat.master._version
 
+    def _fused_update(self, lr, beta1, beta2, eps, decay, a_t) -> bool:
+        """Optimizer hook for the flat shards.  One rank: AdamW and the bf16 cast of
+        the new weights in one kernel.  Several ranks, fused backend: reduce-scatter,
+        AdamW and the weight all-gather in one peer-memory kernel."""
+        from ..ops import native, use_native
+        flat = self.flat
+        if not use_native(flat.master, "adamw"):
+            return False
+        if flat.m is None:
+            flat.m, flat.v = torch.zeros_like(flat.master), torch.zeros_like(flat.master)
+        if self.group_size == 1:
+            native.adamw_(flat.master, flat.shard_grad, flat.m, flat.v, lr, beta1, beta2, eps, decay, a_t,
+                          p_bf16=flat.full_w if flat.full_w.dtype == torch.bfloat16 else None)
+            self._weights_fresh = flat.full_w.dtype == torch.bfloat16
+            return True
+        if not self.fused:
+            return False
+        self.comm.fused_update(flat, self._pending_reduce, lr, beta1, beta2, eps, decay, a_t)
+        self._pending_reduce = False
+        self._weights_fresh = True
+        return True
+
     def after_optimizer_step(self):
+        if self._weights_fresh:
+            self._weights_fresh = False
+            self._seen_versions = self._versions()
+            return
         self.materialize()
 
     def forward(self, x, **kwargs):
@@ -258,7 +294,9 @@ class FSDPWrapperPipelined(nn.Module):
         flat = self.flat
         fsdp_group, ddp_group = self.FSDP_communication_group, self.DDP_communication_group
         if self.group_size > 1:
-            if self.backend == "fused" and self.comm is not None:
+            if self.fused and self.ddp_size == 1:
+                self._pending_reduce = True          # folded into the optimizer kernel
+            elif self.fused:
                 self.comm.reduce_scatter_avg(flat)
             else:
                 works = []
@@ -280,7 +318,7 @@ class FSDPWrapperPipelined(nn.Module):
                 p.grad.copy_(packed[offset:offset + p.numel()].view_as(p.grad))
                 offset += p.numel()
         if self.ddp_size > 1:
-            if self.backend == "fused" and self.comm is not None:
+            if self.fused:
                 self.comm.allreduce_avg(flat.shard_grad, ddp_group)
                 for p in self.expert_params:
                     self.comm.allreduce_avg(p.main_grad, ddp_group)

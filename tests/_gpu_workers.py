@@ -1,0 +1,172 @@
+"""Worker bodies for multi-GPU tests (one process per GPU, NCCL); not collected."""
+import os
+import sys
+import traceback
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def _setup(rank, world, port):
+    import torch
+    import torch.distributed as dist
+    os.environ.update({"RANK": str(rank), "LOCAL_RANK": str(rank), "WORLD_SIZE": str(world),
+                       "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    return torch.device("cuda", rank)
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+def _guarded(fn, rank, world, port, out_dir, *args):
+    import torch.distributed as dist
+    try:
+        fn(rank, world, port, out_dir, *args)
+        with open(os.path.join(out_dir, f"ok_{rank}"), "w") as f:
+            f.write("ok")
+    except Exception:
+        with open(os.path.join(out_dir, f"err_{rank}.txt"), "w") as f:
+            f.write(traceback.format_exc())
+        raise
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def _allreduce(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+    from b200moe.comm import make_comm
+    from b200moe.ops import native
+    from b200moe.topology import build_groups
+    device = _setup(rank, world, port)
+    mesh = build_groups({"fsdp_parallel_num": 1, "data_parallel_num": world, "pipeline_parallel_stages": 1},
+                        rank, world, world)
+    comm = make_comm(mesh, device)
+    kinds = ["oneshot", "twoshot"] + (["nvls"] if comm.ddp is not None else [])
+    for n in (1000, 262144, 5_000_000):
+        for kind in kinds:
+            torch.manual_seed(100 + rank)
+            x = torch.randn(n, device=device)
+            want = x.clone()
+            dist.all_reduce(want, op=dist.ReduceOp.AVG)
+            got = x.clone()
+            try:
+                comm.allreduce_avg(got, mesh.group("ddp"), kind=kind)
+            except RuntimeError as error:
+                if kind == "nvls" and "-11" in str(error):
+                    continue          # no multicast address on this system
+                raise
+            assert _rel(got, want) < 1e-6, (n, kind, _rel(got, want))
+    auto = torch.randn(3_000_001, device=device)
+    want = auto.clone()
+    dist.all_reduce(want, op=dist.ReduceOp.AVG)
+    comm.allreduce_avg(auto, mesh.group("ddp"))
+    assert _rel(auto, want) < 1e-6
+    native.check_status()
+
+
+def _moe_ep(rank, world, port, out_dir):
+    """Peer-memory dispatch/return against the NCCL all-to-all path, forward and backward."""
+    import torch
+    from b200moe import ops
+    from b200moe.comm import make_comm
+    from b200moe.ops import native
+    from b200moe.ops.moe import moe_ffn
+    from b200moe.topology import build_groups
+    device = _setup(rank, world, port)
+    mesh = build_groups({"fsdp_parallel_num": world, "data_parallel_num": 1, "pipeline_parallel_stages": 1},
+                        rank, world, world)
+    comm = make_comm(mesh, device)
+    group = mesh.group("fsdp")
+    T, D, Fd, E_total = 1024, 256, 512, 8
+    e_local = E_total // world
+    torch.manual_seed(5 + rank)
+    x = (torch.randn(T, D, device=device)).bfloat16()
+    logits = torch.randn(T, E_total, device=device)
+    if rank == 0:
+        logits[:, 0] += 2.0                      # unbalanced routing
+    w1, w3, w2 = ((torch.randn(e_local, Fd, D, device=device) * 0.06).bfloat16(),
+                  (torch.randn(e_local, Fd, D, device=device) * 0.06).bfloat16(),
+                  (torch.randn(e_local, D, Fd, device=device) * 0.06).bfloat16())
+    dout = torch.randn(T, D, device=device).bfloat16()
+    results = []
+    for fused in (True, False, True):
+        xs, lg = x.clone().requires_grad_(True), logits.clone().requires_grad_(True)
+        params = [p.clone().requires_grad_(True) for p in (w1, w2, w3)]
+        weights, idx = ops.router_top2(lg)
+        ctx = comm.ep_context(T, D, E_total, capacity_factor=2.0) if fused else None
+        ops.set_native(fused)
+        try:
+            out = moe_ffn(xs, weights, idx, *params, group=group, ep_ctx=ctx)
+            out.backward(dout)
+        finally:
+            ops.set_native(True)
+        results.append([out.detach(), xs.grad, lg.grad] + [p.grad for p in params])
+    for got, want, again in zip(*results):
+        assert _rel(got, want) < 2e-2, _rel(got, want)
+        assert _rel(again, want) < 2e-2
+    native.check_status()
+
+
+def _train_parity(rank, world, port, out_dir, pp):
+    """A few training steps: fused peer-memory backend against the NCCL backend."""
+    import torch
+    from b200moe.comm import make_comm
+    from b200moe.ops import native
+    from b200moe.ops.functional import cross_entropy
+    from b200moe.parallel import pipelined_train_overlap
+    from b200moe.topology import build_groups
+    from b200moe.trainer import build_model
+    device = _setup(rank, world, port)
+    fsdp = world // pp
+    config = {
+        "general": {"device": "gpu"}, "data": {"vocab_size": 2048},
+        "model": {"num_head": 4, "d_model": 512, "d_ff": 1024, "context_len": 256, "num_layers": 2,
+                  "num_expert_per_node": 8 // fsdp},
+        "train": {"fsdp_parallel_num": fsdp, "data_parallel_num": 1, "pipeline_parallel_stages": pp,
+                  "learning_rate": 1e-3, "optimizer": {"beta1": 0.9, "beta2": 0.999, "lambda": 0.01}},
+    }
+    mesh = build_groups(config["train"], rank, world, world)
+    comm = make_comm(mesh, device)
+    losses = {}
+    weights = {}
+    for backend in ("fused", "nccl"):
+        config["comm"] = {"backend": backend}
+        torch.manual_seed(77 + mesh.stage)
+        model, opt = build_model(config, mesh, device, mesh.group("fsdp"), mesh.group("ddp"), torch.bfloat16,
+                                 comm if backend == "fused" else None)
+        assert model.fused == (backend == "fused")
+        torch.manual_seed(1000 + mesh.dp_idx)
+        ids = torch.randint(0, 2048, (4, 257), device=device)
+        run = []
+        for _ in range(3):
+            x = ids[:, :-1] if mesh.stage == 0 else None
+            y = ids[:, 1:] if mesh.stage == pp - 1 else None
+            loss = pipelined_train_overlap(model, opt, x, y, [4, 256, 512], 2, mesh.stage, cross_entropy,
+                                           dtype=torch.bfloat16, device=device, pp_group=mesh.group("pp"),
+                                           dp_group=mesh.group("data"))
+            run.append(float(loss))
+        losses[backend] = run
+        weights[backend] = model.flat.full_w.clone()
+    if mesh.stage == pp - 1:
+        for a, b in zip(losses["fused"], losses["nccl"]):
+            assert abs(a - b) < 5e-2, losses
+    assert _rel(weights["fused"], weights["nccl"]) < 2e-2
+    native.check_status()
+
+
+def run_allreduce(rank, world, port, out_dir):
+    _guarded(_allreduce, rank, world, port, out_dir)
+
+
+def run_moe_ep(rank, world, port, out_dir):
+    _guarded(_moe_ep, rank, world, port, out_dir)
+
+
+def run_train_parity(rank, world, port, out_dir, pp):
+    _guarded(_train_parity, rank, world, port, out_dir, pp)
