@@ -112,6 +112,7 @@ class Comm:
         self.status = native.status_word(device)
         self.fsdp = GroupComm(mesh.group("fsdp"), device) if mesh.fsdp > 1 else None
         self.ddp = GroupComm(mesh.group("ddp"), device) if mesh.ddp > 1 else None
+        self.capacity_mode = "exact"
         self._symm = {}
         self._ep = {}
         self._ar_stage = {}
@@ -210,11 +211,12 @@ class Comm:
         return tensor
 
     # -- expert parallel --------------------------------------------------------------------
-    def ep_context(self, tokens: int, dim: int, experts_total: int, capacity_factor: float = 1.5):
+    def ep_context(self, tokens: int, dim: int, experts_total: int, capacity_factor: float = 1.25,
+                   capacity_mode: str | None = None):
         key = (tokens, dim, experts_total)
         ctx = self._ep.get(key)
         if ctx is None:
-            ctx = EPContext(self, tokens, dim, experts_total, capacity_factor)
+            ctx = EPContext(self, tokens, dim, experts_total, capacity_factor, capacity_mode or self.capacity_mode)
             self._ep[key] = ctx
         return ctx
 
@@ -246,16 +248,30 @@ class _Landing:
 class EPContext:
     """Dispatch and return of token rows between the ranks of the expert group."""
 
-    def __init__(self, comm: Comm, tokens: int, dim: int, experts_total: int, capacity_factor: float):
+    def __init__(self, comm: Comm, tokens: int, dim: int, experts_total: int, capacity_factor: float,
+                 capacity_mode: str = "exact"):
         g = comm.fsdp
         self.comm, self.g = comm, g
         self.tokens, self.dim, self.experts_total = tokens, dim, experts_total
         self.ep = g.world
         self.e_local = experts_total // self.ep
         self.slots = tokens * 2
-        worst = self.slots * self.ep
-        want = min(worst, int(self.slots * capacity_factor))
-        self.cap = (want + self.e_local * 127 + 127) // 128 * 128
+        # Landing buffers hold the worst case (every slot of every rank routed here), so a push can
+        # never overflow.  The owned per-call buffers (saved for the backward pass) are sized by
+        # ``capacity_mode``:
+        #   exact  one 16-byte read of the row count per dispatch (the host waits for the plan kernel;
+        #          with millisecond-scale expert GEMMs behind it the queue refills at once); never
+        #          drops, never overflows, least memory.  Default.
+        #   hint   no host wait: rows the same layer needed on its previous call (read back
+        #          asynchronously) times ``capacity_factor``; an abrupt routing change overflows and
+        #          is reported through the status word.
+        #   worst  no host wait, worst-case buffers (``ep`` times the average).
+        if capacity_mode not in ("exact", "hint", "worst"):
+            raise ValueError("capacity_mode must be exact, hint or worst")
+        self.capacity_mode = capacity_mode
+        self.capacity_factor = capacity_factor
+        self.cap = (self.slots * self.ep + self.e_local * 127 + 127) // 128 * 128
+        self._hints = {}
         dev = comm.device
         self.counts_all = SymmBuffer(MAX_RANKS * 32, torch.int32, dev, g.group)
         self.fwd_land = _Landing(self.cap, dim, dev, g.group, with_scalar=False)
@@ -269,29 +285,60 @@ class EPContext:
         dist.barrier(group=g.group)
 
     # forward: tokens -> expert owners
-    def dispatch(self, x, idx) -> Route:
+    def _sized(self, needed: int, factor: float | None = None) -> int:
+        factor = self.capacity_factor if factor is None else factor
+        want = int(needed * factor) + (self.e_local * 128 if factor > 1.0 else 0)
+        return min(self.cap, (want + 1023) // 1024 * 1024)
+
+    def _capacity_for(self, key):
+        """Capacity from the layer's previous call, or ``None`` when no readback has
+        arrived yet (the caller then reads the count once, synchronously)."""
+        if self.capacity_mode == "worst":
+            return self.cap
+        hint = self._hints.get(key)
+        if self.capacity_mode == "exact" or hint is None or not hint[1].query():
+            return None
+        return self._sized(int(hint[0][3]))
+
+    def _record_hint(self, key, meta):
+        hint = self._hints.get(key)
+        if hint is None:
+            hint = (torch.zeros(4, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+            self._hints[key] = hint
+        hint[0].copy_(meta, non_blocking=True)
+        hint[1].record()
+
+    def dispatch(self, x, idx, key=None) -> Route:
         g, dev = self.g, x.device
         i32 = dict(dtype=torch.int32, device=dev)
+        cap = self._capacity_for(key)
+        cold = cap is None
+        if cold:
+            cap = self.cap
         slot_row, slot_dest = torch.empty(self.slots, **i32), torch.empty(self.slots, **i32)
         offs, seg_live_end = torch.empty(self.e_local, **i32), torch.empty(self.e_local, **i32)
-        tile_expert = torch.empty(self.cap // 128, **i32)
+        tile_expert = torch.empty(cap // 128, **i32)
         meta = torch.zeros(4, **i32)
         seq = g.next_seq(SIG_EP_COUNTS)
         native._call("b2_ep_plan", _ptr(idx.contiguous()), _i(self.slots), _i(self.experts_total), _i(self.ep),
-                     _i(g.rank), _i(seq), _i(self.cap), self.counts_all.table(), g.sig.table(), _i(SIG_EP_COUNTS),
+                     _i(g.rank), _i(seq), _i(cap), self.counts_all.table(), g.sig.table(), _i(SIG_EP_COUNTS),
                      _ptr(slot_row), _ptr(slot_dest), _ptr(offs), _ptr(seg_live_end), _ptr(tile_expert), _ptr(meta),
                      _ptr(self.comm.status), _stream())
+        self._record_hint(key, meta)
+        if cold:
+            # first call of this layer: one blocking read of the row count sizes the owned buffers
+            cap = self._sized(int(meta.cpu()[3]), 1.0 if self.capacity_mode == "exact" else None)
         seq = g.next_seq(SIG_EP_FWD_DATA)
         self._push(x, slot_row, slot_dest, self.slot_ids, None, None, self.slots, 1, self.cap, seq, SIG_EP_FWD_DATA,
                    self.fwd_land)
-        x_perm = torch.empty(self.cap, self.dim, dtype=torch.bfloat16, device=dev)
-        row_tag, row_src = torch.empty(self.cap, **i32), torch.empty(self.cap, **i32)
+        x_perm = torch.empty(cap, self.dim, dtype=torch.bfloat16, device=dev)
+        row_tag, row_src = torch.empty(cap, **i32), torch.empty(cap, **i32)
         land = self.fwd_land
         native._call("b2_ep_consume", _ptr(land.rows.tensor), _ptr(land.tag.tensor), _ptr(land.src.tensor), _ptr(None),
                      _ptr(tile_expert), _ptr(seg_live_end), _ptr(meta), _ptr(None), self.null, _ptr(x_perm),
-                     _ptr(row_tag), _ptr(row_src), g.my_sig(), _i(self.dim), _i(self.cap), _i(self.ep), _i(seq),
+                     _ptr(row_tag), _ptr(row_src), g.my_sig(), _i(self.dim), _i(cap), _i(self.ep), _i(seq),
                      _i(SIG_EP_FWD_DATA), _ptr(self.comm.status), _stream())
-        return Route(self.cap, offs, tile_expert, meta, x_perm, slot_row, slot_dest, row_tag, row_src, seg_live_end)
+        return Route(cap, offs, tile_expert, meta, x_perm, slot_row, slot_dest, row_tag, row_src, seg_live_end)
 
     def _push(self, src, row_of, dest_of, tag_of, scalar_of, live_items, items, shift, dest_cap, seq, slot, land):
         g = self.g
@@ -322,12 +369,12 @@ class EPContext:
         seq = g.next_seq(SIG_EP_BWD_DATA)
         self._push(dout, route.slot_row, route.slot_dest, self.slot_ids, weights.reshape(-1), None, self.slots, 1,
                    self.cap, seq, SIG_EP_BWD_DATA, self.bwd_land)
-        dy_perm = torch.empty(self.cap, self.dim, dtype=torch.bfloat16, device=dout.device)
+        dy_perm = torch.empty(route.cap, self.dim, dtype=torch.bfloat16, device=dout.device)
         land = self.bwd_land
         native._call("b2_ep_consume", _ptr(land.rows.tensor), _ptr(land.tag.tensor), _ptr(land.src.tensor),
                      _ptr(land.scalar.tensor), _ptr(route.tile_expert), _ptr(route.seg_live_end), _ptr(route.meta),
                      _ptr(y_perm), self.ret_scalar.table(), _ptr(dy_perm), _ptr(None), _ptr(None), g.my_sig(),
-                     _i(self.dim), _i(self.cap), _i(self.ep), _i(seq), _i(SIG_EP_BWD_DATA), _ptr(self.comm.status),
+                     _i(self.dim), _i(route.cap), _i(self.ep), _i(seq), _i(SIG_EP_BWD_DATA), _ptr(self.comm.status),
                      _stream())
         return dy_perm
 

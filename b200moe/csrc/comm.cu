@@ -79,7 +79,7 @@ struct EpPlanArgs {
   int* offs;              // [E_local] padded cumulative segment ends (this rank as expert owner)
   int* seg_live_end;      // [E_local] first padding row of each segment
   int* tile_expert;       // [capacity_rows / 128]
-  int* meta;              // {live tiles, live rows, overflow, 0}
+  int* meta;              // {live tiles, live rows, overflow, rows needed}
   int* status;
 };
 
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) ep_plan_kernel(const EpPlanArgs 
   const int per = (a.slots + PLAN_THREADS - 1) / PLAN_THREADS;
   const int s0 = min(a.slots, tid * per), s1 = min(a.slots, s0 + per);
   for (int e = 0; e < E; ++e) local[e * PLAN_THREADS + tid] = 0;
-  for (int s = s0; s < s1; ++s) local[static_cast<int>(a.idx[s]) * PLAN_THREADS + tid] += 1;
+  for (int s = s0; s < s1; ++s) local[min(max(static_cast<int>(a.idx[s]), 0), E - 1) * PLAN_THREADS + tid] += 1;
   __syncthreads();
   for (int e = 0; e < E; ++e) {
     const int mine = local[e * PLAN_THREADS + tid];
@@ -162,13 +162,14 @@ __global__ void __launch_bounds__(PLAN_THREADS) ep_plan_kernel(const EpPlanArgs 
         a.meta[0] = overflow ? 0 : tile;
         a.meta[1] = overflow ? 0 : row;
         a.meta[2] = overflow ? 1 : 0;
+        a.meta[3] = row;                       // rows this call needed (capacity hint for the host)
         if (overflow) atomicExch(a.status, 102);
       }
     }
   }
   __syncthreads();
   for (int s = s0; s < s1; ++s) {
-    const int e = static_cast<int>(a.idx[s]);
+    const int e = min(max(static_cast<int>(a.idx[s]), 0), E - 1);
     const int pos = local[e * PLAN_THREADS + tid];
     local[e * PLAN_THREADS + tid] = static_cast<uint32_t>(pos + 1);
     a.slot_row[s] = base_row[e] + pos;

@@ -325,6 +325,10 @@ __global__ void router_top2_fwd_kernel(const float* __restrict__ logits, float* 
       pb = p[e]; b = e;
     }
   }
+  if (b < 0) {                 // only reachable with non-finite logits: keep the indices valid
+    b = a == 0 ? 1 : 0;
+    pb = p[b];
+  }
   const float s = pa + pb;
   weights[2 * t] = pa / s;
   weights[2 * t + 1] = pb / s;

@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long*
   const int s0 = min(slots, tid * per), s1 = min(slots, s0 + per);
 
   for (int e = 0; e < E; ++e) local[e * PLAN_THREADS + tid] = 0;
-  for (int s = s0; s < s1; ++s) local[static_cast<int>(idx[s]) * PLAN_THREADS + tid] += 1;
+  for (int s = s0; s < s1; ++s) local[min(max(static_cast<int>(idx[s]), 0), E - 1) * PLAN_THREADS + tid] += 1;
   __syncthreads();
   // exclusive scan over threads for each expert
   for (int e = 0; e < E; ++e) {
@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long*
   for (int r = tid; r < min(live_rows, capacity_rows); r += PLAN_THREADS) row_slot[r] = -1;
   __syncthreads();
   for (int s = s0; s < s1; ++s) {
-    const int e = static_cast<int>(idx[s]);
+    const int e = min(max(static_cast<int>(idx[s]), 0), E - 1);
     const int pos = local[e * PLAN_THREADS + tid];
     local[e * PLAN_THREADS + tid] = static_cast<uint32_t>(pos + 1);
     const int row = seg_start[e] + pos;

@@ -257,7 +257,7 @@ class MoELayerMulti(nn.Module):
             ep_ctx = self.comm.ep_context(flat.shape[0], flat.shape[1], self.world_size * self.num_expert_per_node)
         out = ops.moe_ffn(flat, weights, idx, self.experts.w1, self.experts.w2, self.experts.w3,
                           group=self.dp_group if self.world_size > 1 else None,
-                          recompute=self.recompute, ep_ctx=ep_ctx)
+                          recompute=self.recompute, ep_ctx=ep_ctx, key=id(self))
         out = out.view(shape).to(in_dtype)
         if return_aux_loss:
             from ..ops.moe import aux_loss_from

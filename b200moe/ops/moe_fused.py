@@ -37,7 +37,7 @@ def _wgrad(dy, x, param, offs, num_experts):
 
 class _MoEFused(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weights, idx, w1, w2, w3, recompute, ep_ctx):
+    def forward(ctx, x, weights, idx, w1, w2, w3, recompute, ep_ctx, key):
         tokens, dim = x.shape
         experts = w1.shape[0]
         x = x.contiguous()
@@ -48,7 +48,7 @@ class _MoEFused(torch.autograd.Function):
             x_perm = native.moe_gather(x, row_slot, meta, cap)
             route = None
         else:
-            route = ep_ctx.dispatch(x, idx)
+            route = ep_ctx.dispatch(x, idx, key)
             cap, offs, tile_expert, meta, x_perm = route.cap, route.offs, route.tile_expert, route.meta, route.x_perm
             slot_row = row_slot = None
         tiles = meta[0:1]
@@ -102,8 +102,10 @@ class _MoEFused(torch.autograd.Function):
             dx = native.moe_combine(dx_perm, slot_row, None, tokens)
         else:
             dx, dweights = ep_ctx.dispatch_backward(route, dx_perm, tokens)
-        return dx, dweights, None, dw1, dw2, dw3, None, None
+        return dx, dweights, None, dw1, dw2, dw3, None, None, None
 
 
-def moe_ffn_fused(x, weights, idx, w1, w2, w3, ep_ctx=None, recompute: bool = False):
-    return _MoEFused.apply(x, weights, idx, w1, w2, w3, recompute, ep_ctx)
+def moe_ffn_fused(x, weights, idx, w1, w2, w3, ep_ctx=None, recompute: bool = False, key=None):
+    """``key`` names the calling layer; the expert-parallel context keeps one
+    capacity hint per key."""
+    return _MoEFused.apply(x, weights, idx, w1, w2, w3, recompute, ep_ctx, key if key is not None else id(w1))

@@ -185,6 +185,10 @@ def train(local_rank: int, cluster_rank: int, world_size: int, config: dict):
             if profiling or reporting:
                 with nvtx_range("post_step_synchronization"):
                     span_dev_ms += timer.stop_ms()
+                if device.type == "cuda":
+                    from .ops import native
+                    if native.has("gemm"):
+                        native.check_status()
             span_s += time.perf_counter() - t0
             loss_acc = loss_acc + loss
             span_tokens += batch_size * ctx_len

@@ -225,7 +225,7 @@ def bench_b200moe(args):
     from b200moe.trainer import build_model
     from b200moe.utils.data import BatchStager
     cfg = run_config(args)
-    recompute = args.recompute or ("none" if cfg["pp"] <= 2 else "swiglu")
+    recompute = args.recompute or ("none" if cfg["pp"] <= 2 else "swiglu")   # 4 microbatches in flight on stage 0
     single = args.gpus == 1
     config = {
         "general": {"device": "gpu", "n_workers": world, "gpu_per_node": world, "info_src": 0},
@@ -273,6 +273,7 @@ def bench_b200moe(args):
 
     device_ms, e2e_ms, clocks, launches, last = measure(
         step_device, None if args.no_e2e else step_e2e, args, device, rank, native.launch_count)
+    native.check_status()      # a device-side wait that ran out or an expert-capacity overflow is an error
     loss = torch.tensor([float(last) if last is not None else 0.0], device=device)
     dist.all_reduce(loss, op=dist.ReduceOp.MAX)
     peak = torch.tensor([torch.cuda.max_memory_allocated() / 2 ** 30], device=device)

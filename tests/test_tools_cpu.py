@@ -1,0 +1,150 @@
+"""Launchers, tools, chaos hooks and the side car, all on CPU with fakes."""
+import random
+
+import pytest
+import yaml
+
+import modal_wrapper
+import run_experiment
+from b200moe.utils import chaos
+from b200moe.utils.metrics import MetricsSink, flops_per_token, mfu
+from rl.worker_node.prompt_loader import DatabasePromptLoader
+from rl.worker_node.start_vllm import build_command, start_server
+
+
+def test_flops_per_token_matches_published_figure():
+    fpt = flops_per_token(4096, 14336, 32, 8, 32000, 32, 8192)
+    assert abs(fpt / 1e9 - 84.01) < 0.01
+    assert abs(mfu(75076, fpt, 8) - 0.350) < 0.001
+
+
+def test_metrics_sink(tmp_path):
+    sink = MetricsSink(tmp_path / "m.jsonl")
+    sink.write(iteration=1, tokens_per_s=10.0)
+    assert (tmp_path / "m.jsonl").read_text().count("\n") == 1 and sink.records[0]["iteration"] == 1
+
+
+def test_torchrun_and_nsys_commands():
+    config = {"general": {"n_workers": 8, "gpu_per_node": 8}, "recovery": {"max_restarts": 2},
+              "profile": {"enabled": True, "output_dir": "/p", "nsight_trace": "cuda-sw,nvtx"}}
+    cmd = modal_wrapper.torchrun_command(config, "c.yaml")
+    assert "--nproc-per-node=8" in cmd and "--max-restarts=2" in cmd and "--monitor-interval=1" in cmd
+    assert cmd[-4:] == ["--module", "distributed_parallel_training_pipelined", "--config-path", "c.yaml"]
+    prefix = modal_wrapper.nsys_prefix(config, "run")
+    assert prefix[:2] == ["nsys", "profile"] and "--trace=cuda-sw,nvtx" in prefix
+    assert modal_wrapper.nsys_prefix({"profile": {"enabled": False}}, "run") == []
+    assert modal_wrapper.nccl_environment()["NCCL_IB_DISABLE"] == "1"
+
+
+def test_experiment_config_validation(tmp_path):
+    good = {"experiment": {"device": "cuda:0", "dtype": "bfloat16", "input_shapes": [[2, 8, 16]], "warmup": 0,
+                           "iterations": 1, "mode": "training"}}
+    path = tmp_path / "e.yaml"
+    path.write_text(yaml.safe_dump(good))
+    assert run_experiment.load_experiment_config(path)["experiment"]["mode"] == "training"
+    for key, value in [("dtype", "int8"), ("mode", "x"), ("iterations", 0), ("input_shapes", [[0]]), ("warmup", -1)]:
+        bad = {"experiment": {**good["experiment"], key: value}}
+        path.write_text(yaml.safe_dump(bad))
+        with pytest.raises(ValueError):
+            run_experiment.load_experiment_config(path)
+    with pytest.raises(ValueError, match="CUDA"):
+        run_experiment.cuda_device("cpu")
+
+
+def test_make_module_step_runs_on_cpu():
+    import torch
+    from b200moe.models import ModuleStack
+    from b200moe.utils.profiling import make_module_step
+    module = ModuleStack(16, 16, d_ff=32)
+    x = torch.randn(2, 3, 16)
+    step = make_module_step(module, [x], "training")
+    assert step().dim() == 0 and x.grad is None and all(p.grad is None for p in module.parameters())
+    assert make_module_step(module, [x], "evaluation")().shape == (2, 3, 16)
+
+
+def test_chaos_triggers_and_leak_cap(monkeypatch):
+    slept = []
+    monkeypatch.setattr(chaos.time, "sleep", slept.append)
+    trig = chaos.ChaosEnginnerTrigger({"random_delay": {"enabled": True, "delay_time": 3, "chance": 1.0},
+                                       "random_kill": {"enabled": False, "chance": 1.0},
+                                       "random_gpu_memory_leak": {"enabled": True, "size_mb": 1, "chance": 1.0,
+                                                                  "max_total_mb": 2}})
+    assert len(trig) == 2
+    assert trig.trigger() == 2 and slept == [3]
+    trig.trigger()
+    assert trig.trigger() == 1          # the leak stopped at its cap
+    assert chaos.release_leaks() == 2 and chaos.release_leaks() == 0
+    with pytest.raises(ValueError, match="Unknown chaos"):
+        chaos.ChaosEnginnerTrigger({"nope": {"enabled": True}})
+    random.seed(0)
+    assert chaos.random_delay(1, chance=0.0) is False
+
+
+def test_chaos_kill_sends_sigkill_to_self(monkeypatch):
+    sent = []
+    monkeypatch.setattr(chaos.os, "kill", lambda pid, sig: sent.append((pid, sig)))
+    assert chaos.random_kill(chance=1.0) is True
+    assert sent == [(chaos.os.getpid(), chaos.signal.SIGKILL)]
+
+
+def test_prompt_loader_with_fake_connection(tmp_path):
+    class Cursor:
+        def __init__(self, rows):
+            self.rows, self.seen = rows, []
+
+        def __enter__(self):
+            return self
+
+        def __exit__(self, *a):
+            return False
+
+        def execute(self, query, params):
+            self.seen.append((query, params))
+
+        def fetchone(self):
+            return self.rows.pop(0) if self.rows else None
+
+    class Conn:
+        def __init__(self, **kw):
+            self.kw, self.cur = kw, Cursor([(7, "hello", {"a": 1})])
+
+        def cursor(self):
+            return self.cur
+
+        def close(self):
+            self.closed = True
+
+    path = tmp_path / "ds.yaml"
+    path.write_text(yaml.safe_dump({"data_source": {"host": "h", "port": 1, "dbname": "d", "user": "u",
+                                                    "dataset": "gsm"}}))
+    made = []
+    loader = DatabasePromptLoader(path, connect=lambda **kw: made.append(Conn(**kw)) or made[-1])
+    assert loader.samplePrompt() == {"id": 7, "prompt": "hello", "metadata": {"a": 1}}
+    assert "WHERE dataset = %s" in made[0].cur.seen[0][0] and made[0].cur.seen[0][1] == ("gsm",)
+    assert loader.samplePrompt() is None
+    loader.close()
+    path.write_text(yaml.safe_dump({"data_source": {"host": "h"}}))
+    with pytest.raises(ValueError, match="missing"):
+        DatabasePromptLoader(path)
+
+
+def test_vllm_launcher_pins_gpu():
+    calls = []
+    start_server("m", gpu=3, port=9000, popen=lambda cmd, env: calls.append((cmd, env)) or "proc")
+    cmd, env = calls[0]
+    assert cmd[:3] == ["vllm", "serve", "m"] and "--weight-transfer-config" in cmd
+    assert env["CUDA_VISIBLE_DEVICES"] == "3"
+    assert "--max-model-len" in build_command("m", max_model_len=128)
+
+
+def test_helm_values_hold_a_valid_run_config():
+    import os
+    from b200moe import config as cfg
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with open(os.path.join(root, "kubernetes", "chart", "values.yaml")) as f:
+        values = yaml.safe_load(f)
+    run = values["config"]
+    run["general"]["n_workers"] = values["nodes"] * values["gpusPerNode"]
+    run["general"]["gpu_per_node"] = values["gpusPerNode"]
+    run["train"].setdefault("validation_interval", 1)
+    cfg.validate_config(run)
