@@ -61,8 +61,16 @@ def build_model(config: dict, mesh, device, fsdp_group, ddp_group, compute_dtype
     model.to(device)
     recompute = train_cfg.get("activation_recompute", "none")
     model.block_recompute = recompute == "block"
-    for layer in model.layers:
-        layer.ffn.recompute = recompute == "swiglu"
+    # ``train.recompute_layers``: how many blocks (from the front of the stage) rebuild their gate/up
+    # activations in the backward pass; an int, or one int per pipeline stage (earlier stages keep more
+    # microbatches in flight under 1F1B and need it more).  Default: all blocks when ``swiglu``.
+    count = train_cfg.get("recompute_layers")
+    if isinstance(count, (list, tuple)):
+        count = count[mesh.stage]
+    if count is None:
+        count = len(model.layers)
+    for index, layer in enumerate(model.layers):
+        layer.ffn.recompute = recompute == "swiglu" and index < count
     backend = (config.get("comm") or {}).get("backend", "fused" if device.type == "cuda" else "nccl")
     wrapped = FSDPWrapperPipelined(
         model, FSDP_communication_group=fsdp_group,

@@ -238,6 +238,8 @@ def bench_b200moe(args):
                   "microbatch_num": cfg["microbatches"], "batch_size": cfg["batch"], "learning_rate": 1e-4,
                   "optimizer": {"beta1": 0.9, "beta2": 0.999, "lambda": 0.01},
                   "activation_recompute": recompute,
+                  # 1F1B keeps pp - stage microbatches alive: only the early stages have to drop activations
+                  "recompute_layers": [4, 2, 0, 0] if cfg["pp"] == 4 and args.recompute is None else None,
                   # one GPU holds all 8 experts of 8 blocks (11.3 G parameters): moments and gradient
                   # accumulators use the reference's bf16 there; fp32 everywhere else
                   "expert_state_dtype": "bfloat16" if single else "float32",
