@@ -270,7 +270,7 @@ class EPContext:
             raise ValueError("capacity_mode must be exact, hint or worst")
         self.capacity_mode = capacity_mode
         self.capacity_factor = capacity_factor
-        self.cap = (self.slots * self.ep + self.e_local * 127 + 127) // 128 * 128
+        self.cap = (self.slots * self.ep + self.e_local * 255 + 255) // 256 * 256
         self._hints = {}
         dev = comm.device
         self.counts_all = SymmBuffer(MAX_RANKS * 32, torch.int32, dev, g.group)
@@ -287,7 +287,7 @@ class EPContext:
     # forward: tokens -> expert owners
     def _sized(self, needed: int, factor: float | None = None) -> int:
         factor = self.capacity_factor if factor is None else factor
-        want = int(needed * factor) + (self.e_local * 128 if factor > 1.0 else 0)
+        want = int(needed * factor) + (self.e_local * 256 if factor > 1.0 else 0)
         return min(self.cap, (want + 1023) // 1024 * 1024)
 
     def _capacity_for(self, key):

@@ -65,7 +65,8 @@ struct alignas(16) vec16 {
 
 // ------------------------------------------------------------------ EP plan with count exchange
 constexpr int PLAN_THREADS = 1024;
-constexpr int ALIGN_ROWS = 128;
+constexpr int ALIGN_ROWS = 256;   // segment padding; tile tables are per 128-row unit
+constexpr int TILE_ROWS = 128;
 constexpr int MAX_EXPERTS = 32;
 
 struct EpPlanArgs {
@@ -152,7 +153,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) ep_plan_kernel(const EpPlanArgs 
         if (d == a.rank) {
           a.seg_live_end[j] = row + total;
           if (row + padded <= a.capacity_rows)
-            for (int t = 0; t < padded / ALIGN_ROWS; ++t) a.tile_expert[tile++] = j;
+            for (int t = 0; t < padded / TILE_ROWS; ++t) a.tile_expert[tile++] = j;
           a.offs[j] = row + padded;
         }
         row += padded;
@@ -242,7 +243,7 @@ __global__ void __launch_bounds__(256) ep_consume_kernel(const EpConsumeArgs a) 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int live_rows = min(a.meta[1], a.capacity);
   for (int r = blockIdx.x * 8 + warp; r < live_rows; r += gridDim.x * 8) {
-    const int expert = a.tile_expert[r / ALIGN_ROWS];
+    const int expert = a.tile_expert[r / TILE_ROWS];
     const bool live = r < a.seg_live_end[expert];
     __nv_bfloat16* dst = a.out + static_cast<size_t>(r) * a.D;
     if (!live) {

@@ -65,7 +65,9 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_MAX_CHUNKS = 4;  // D <= 256 * 8 * 4 = 8192
 
-// y = (x [+ delta]) * rstd * w ; optionally writes the sum.  One CTA per row (grid-stride).
+// y = (x [+ delta]) * rstd * w ; optionally writes the sum.  One CTA per row (grid-stride); CH = 8-element
+// vectors per thread (compile time, so the row stays in registers as packed bf16).
+template <int CH>
 __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
                                                                   const __nv_bfloat16* __restrict__ delta,
                                                                   const float* __restrict__ w,
@@ -73,42 +75,49 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_fwd_kernel(const __nv_bf
                                                                   __nv_bfloat16* __restrict__ y,
                                                                   float* __restrict__ rstd, int rows, int D, float eps) {
   __shared__ float scratch[NORM_THREADS / 32];
+  float wv[CH][8];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int col = (c * NORM_THREADS + threadIdx.x) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) wv[c][i] = col < D ? w[col + i] : 0.f;
+  }
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const size_t base = static_cast<size_t>(row) * D;
-    float vals[NORM_MAX_CHUNKS][8];
+    bf16x8 raw[CH];
     float ss = 0.f;
 #pragma unroll
-    for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    for (int c = 0; c < CH; ++c) {
       const int col = (c * NORM_THREADS + threadIdx.x) * 8;
       if (col < D) {
-        unpack8(*reinterpret_cast<const bf16x8*>(x + base + col), vals[c]);
+        raw[c] = *reinterpret_cast<const bf16x8*>(x + base + col);
+        float v[8];
+        unpack8(raw[c], v);
         if (delta) {
           float d[8];
           unpack8(*reinterpret_cast<const bf16x8*>(delta + base + col), d);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) vals[c][i] += d[i];
+          for (int i = 0; i < 8; ++i) v[i] += d[i];
           // the sum is rounded to bf16 once; the norm sees the rounded value, like the unfused path
-          bf16x8 rounded = pack8(vals[c]);
-          *reinterpret_cast<bf16x8*>(sum_out + base + col) = rounded;
-          unpack8(rounded, vals[c]);
+          raw[c] = pack8(v);
+          *reinterpret_cast<bf16x8*>(sum_out + base + col) = raw[c];
+          unpack8(raw[c], v);
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ss += vals[c][i] * vals[c][i];
+        for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
       }
     }
     const float total = block_sum<NORM_THREADS>(ss, scratch);
     const float r = rsqrtf(total / D + eps);
     if (threadIdx.x == 0) rstd[row] = r;
 #pragma unroll
-    for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    for (int c = 0; c < CH; ++c) {
       const int col = (c * NORM_THREADS + threadIdx.x) * 8;
       if (col < D) {
-        float o[8];
-        const float4 w0 = *reinterpret_cast<const float4*>(w + col);
-        const float4 w1 = *reinterpret_cast<const float4*>(w + col + 4);
-        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        float v[8], o[8];
+        unpack8(raw[c], v);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = vals[c][i] * r * ww[i];
+        for (int i = 0; i < 8; ++i) o[i] = v[i] * r * wv[c][i];
         *reinterpret_cast<bf16x8*>(y + base + col) = pack8(o);
       }
     }
@@ -116,6 +125,7 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_fwd_kernel(const __nv_bf
 }
 
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) [+ residual]; dw partial per CTA.
+template <int CH>
 __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                                                   const __nv_bfloat16* __restrict__ x,
                                                                   const float* __restrict__ w,
@@ -124,10 +134,10 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_bwd_kernel(const __nv_bf
                                                                   __nv_bfloat16* __restrict__ dx,
                                                                   float* __restrict__ dw_partial, int rows, int D) {
   __shared__ float scratch[NORM_THREADS / 32];
-  float dw_acc[NORM_MAX_CHUNKS][8];
-  float wv[NORM_MAX_CHUNKS][8];
+  float dw_acc[CH][8];
+  float wv[CH][8];
 #pragma unroll
-  for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+  for (int c = 0; c < CH; ++c) {
     const int col = (c * NORM_THREADS + threadIdx.x) * 8;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -138,32 +148,35 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_bwd_kernel(const __nv_bf
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const size_t base = static_cast<size_t>(row) * D;
     const float r = rstd[row];
-    float g[NORM_MAX_CHUNKS][8], xh[NORM_MAX_CHUNKS][8];
+    bf16x8 rdy[CH], rx[CH];
     float dot = 0.f;
 #pragma unroll
-    for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    for (int c = 0; c < CH; ++c) {
       const int col = (c * NORM_THREADS + threadIdx.x) * 8;
       if (col < D) {
+        rdy[c] = *reinterpret_cast<const bf16x8*>(dy + base + col);
+        rx[c] = *reinterpret_cast<const bf16x8*>(x + base + col);
         float dyv[8], xv[8];
-        unpack8(*reinterpret_cast<const bf16x8*>(dy + base + col), dyv);
-        unpack8(*reinterpret_cast<const bf16x8*>(x + base + col), xv);
+        unpack8(rdy[c], dyv);
+        unpack8(rx[c], xv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          xh[c][i] = xv[i] * r;
-          dw_acc[c][i] += dyv[i] * xh[c][i];
-          g[c][i] = dyv[i] * wv[c][i];
-          dot += g[c][i] * xh[c][i];
+          const float xh = xv[i] * r;
+          dw_acc[c][i] += dyv[i] * xh;
+          dot += dyv[i] * wv[c][i] * xh;
         }
       }
     }
     const float mean = block_sum<NORM_THREADS>(dot, scratch) / D;
 #pragma unroll
-    for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    for (int c = 0; c < CH; ++c) {
       const int col = (c * NORM_THREADS + threadIdx.x) * 8;
       if (col < D) {
-        float o[8];
+        float dyv[8], xv[8], o[8];
+        unpack8(rdy[c], dyv);
+        unpack8(rx[c], xv);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = r * (g[c][i] - xh[c][i] * mean);
+        for (int i = 0; i < 8; ++i) o[i] = r * (dyv[i] * wv[c][i] - xv[i] * r * mean);
         if (residual) {
           float res[8];
           unpack8(*reinterpret_cast<const bf16x8*>(residual + base + col), res);
@@ -175,7 +188,7 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_bwd_kernel(const __nv_bf
     }
   }
 #pragma unroll
-  for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+  for (int c = 0; c < CH; ++c) {
     const int col = (c * NORM_THREADS + threadIdx.x) * 8;
     if (col < D) {
 #pragma unroll
@@ -458,22 +471,68 @@ __device__ __forceinline__ void stf<float>(float* p, size_t i, float v) { p[i] =
 template <>
 __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 
+template <typename T>
+__device__ __forceinline__ void ld8(const T* p, float (&f)[8]);
+template <>
+__device__ __forceinline__ void ld8<float>(const float* p, float (&f)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void ld8<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) {
+  unpack8(*reinterpret_cast<const bf16x8*>(p), f);
+}
+template <typename T>
+__device__ __forceinline__ void st8(T* p, const float (&f)[8]);
+template <>
+__device__ __forceinline__ void st8<float>(float* p, const float (&f)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+}
+template <>
+__device__ __forceinline__ void st8<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[8]) {
+  *reinterpret_cast<bf16x8*>(p) = pack8(f);
+}
+
 // p <- p(1 - lr*wd); m, v moments; p <- p - a_t m/(sqrt(v)+eps).  Optional bf16 copy of the new p.
+// Eight elements per thread as 16/32-byte vectors; the last n % 8 elements go one by one.
 template <typename P, typename G, typename S>
 __global__ void adamw_kernel(P* __restrict__ p, const G* __restrict__ g, S* __restrict__ m, S* __restrict__ v,
                              __nv_bfloat16* __restrict__ p_bf16, size_t n, float lr, float beta1, float beta2,
                              float eps, float wd, float a_t, float grad_scale) {
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+  const size_t vecs = n / 8;
+  const float decay = 1.f - lr * wd;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < vecs;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const float gv = ldf(g, i) * grad_scale;
-    float pv = ldf(p, i) * (1.f - lr * wd);
-    const float mv = beta1 * ldf(m, i) + (1.f - beta1) * gv;
-    const float vv = beta2 * ldf(v, i) + (1.f - beta2) * gv * gv;
-    pv -= a_t * mv / (sqrtf(vv) + eps);
-    stf(p, i, pv);
-    stf(m, i, mv);
-    stf(v, i, vv);
-    if (p_bf16) p_bf16[i] = __float2bfloat16_rn(pv);
+    const size_t o = i * 8;
+    float pv[8], gv[8], mv[8], vv[8];
+    ld8(p + o, pv);
+    ld8(g + o, gv);
+    ld8(m + o, mv);
+    ld8(v + o, vv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gj = gv[j] * grad_scale;
+      mv[j] = beta1 * mv[j] + (1.f - beta1) * gj;
+      vv[j] = beta2 * vv[j] + (1.f - beta2) * gj * gj;
+      pv[j] = pv[j] * decay - a_t * mv[j] / (sqrtf(vv[j]) + eps);
+    }
+    st8(p + o, pv);
+    st8(m + o, mv);
+    st8(v + o, vv);
+    if (p_bf16) st8(p_bf16 + o, pv);
+  }
+  if (blockIdx.x == 0) {
+    for (size_t i = vecs * 8 + threadIdx.x; i < n; i += blockDim.x) {
+      const float gj = ldf(g, i) * grad_scale;
+      const float mj = beta1 * ldf(m, i) + (1.f - beta1) * gj;
+      const float vj = beta2 * ldf(v, i) + (1.f - beta2) * gj * gj;
+      const float pj = ldf(p, i) * decay - a_t * mj / (sqrtf(vj) + eps);
+      stf(p, i, pj);
+      stf(m, i, mj);
+      stf(v, i, vj);
+      if (p_bf16) p_bf16[i] = __float2bfloat16_rn(pj);
+    }
   }
 }
 
@@ -556,19 +615,30 @@ extern "C" {
 int b2_rmsnorm_fwd(const void* x, const void* delta, const float* w, void* sum_out, void* y, float* rstd, int rows,
                    int D, float eps, cudaStream_t s) {
   if (D % 8 || D > NORM_THREADS * 8 * NORM_MAX_CHUNKS) return -10;
-  rmsnorm_fwd_kernel<<<min(rows, 148 * 8), NORM_THREADS, 0, s>>>((const bf16*)x, (const bf16*)delta, w, (bf16*)sum_out,
-                                                                 (bf16*)y, rstd, rows, D, eps);
+  const int grid = min(rows, 148 * 8);
+#define B2_NORM_FWD(CH)                                                                                         \
+  rmsnorm_fwd_kernel<CH><<<grid, NORM_THREADS, 0, s>>>((const bf16*)x, (const bf16*)delta, w, (bf16*)sum_out, \
+                                                       (bf16*)y, rstd, rows, D, eps)
+  if (D <= 2048) B2_NORM_FWD(1);
+  else if (D <= 4096) B2_NORM_FWD(2);
+  else B2_NORM_FWD(4);
+#undef B2_NORM_FWD
   return ok();
 }
 
 // dw_partial: fp32 [parts, D] scratch with parts = b2_rmsnorm_bwd_parts(rows); dw: fp32 [D] (overwritten).
-int b2_rmsnorm_bwd_parts(int rows) { return min(rows, 148 * 4); }
+int b2_rmsnorm_bwd_parts(int rows) { return min(rows, 148 * 6); }
 int b2_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* residual, void* dx,
                    float* dw_partial, float* dw, int rows, int D, cudaStream_t s) {
   if (D % 8 || D > NORM_THREADS * 8 * NORM_MAX_CHUNKS) return -10;
   const int parts = b2_rmsnorm_bwd_parts(rows);
-  rmsnorm_bwd_kernel<<<parts, NORM_THREADS, 0, s>>>((const bf16*)dy, (const bf16*)x, w, rstd, (const bf16*)residual,
-                                                    (bf16*)dx, dw_partial, rows, D);
+#define B2_NORM_BWD(CH)                                                                                       \
+  rmsnorm_bwd_kernel<CH><<<parts, NORM_THREADS, 0, s>>>((const bf16*)dy, (const bf16*)x, w, rstd,             \
+                                                        (const bf16*)residual, (bf16*)dx, dw_partial, rows, D)
+  if (D <= 2048) B2_NORM_BWD(1);
+  else if (D <= 4096) B2_NORM_BWD(2);
+  else B2_NORM_BWD(4);
+#undef B2_NORM_BWD
   column_sum_kernel<<<(D + 255) / 256, 256, 0, s>>>(dw_partial, dw, parts, D);
   return ok();
 }
@@ -641,7 +711,7 @@ int b2_scale_bf16(void* x, const float* factor, long long n, cudaStream_t s) {
 // dtype codes: 0 fp32, 1 bf16.  p_bf16 may be null.
 int b2_adamw(void* p, const void* g, void* m, void* v, void* p_bf16, long long n, int p_dt, int g_dt, int s_dt,
              float lr, float beta1, float beta2, float eps, float wd, float a_t, float grad_scale, cudaStream_t s) {
-  const int grid = grid_for(n, 256, 148 * 32);
+  const int grid = grid_for((n + 7) / 8, 256, 148 * 16);
 #define B2_ADAMW(P, G, S)                                                                                      \
   adamw_kernel<P, G, S><<<grid, 256, 0, s>>>((P*)p, (const G*)g, (S*)m, (S*)v, (bf16*)p_bf16, n, lr, beta1, beta2, \
                                              eps, wd, a_t, grad_scale)

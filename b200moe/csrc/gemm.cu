@@ -24,12 +24,19 @@ namespace b2 {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2;   // 16 KiB
-constexpr int B_BYTES = BN * BK * 2;   // 32 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int A_SUB_BYTES = BM * BK * 2;   // 16 KiB per 128-row sub-tile of A
+constexpr int B_BYTES = BN * BK * 2;       // 32 KiB
 constexpr int GEMM_THREADS = 192;
-constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+// MT = 128-row sub-tiles of A per CTA tile.  MT=1: 128x256 tile, 4 stages, accumulator double-buffered in
+// TMEM (epilogue overlaps the next main loop).  MT=2: 256x256 tile (two MMAs per k-step share the B tile in
+// shared memory, a third fewer operand bytes per FLOP), 3 stages, both accumulators fill TMEM.
+template <int MT> struct Cfg {
+  static constexpr int STAGES = MT == 2 ? 3 : 4;
+  static constexpr int A_BYTES = MT * A_SUB_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int NACC = MT == 2 ? 1 : 2;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
 constexpr int GROUP_M = 8;
 
 enum Epilogue : int {
@@ -54,7 +61,8 @@ struct GemmParams {
   int b_expert_rows;           // rows of one expert in the B map (outer TMA coordinate pitch)
   int k_split;                 // K index where map_b2 takes over (0 = unused)
   const int* tile_expert;      // [m_tiles] expert of each m-tile, or null
-  const int* num_m_tiles;      // device scalar: live m-tiles, or null (= ceil(M/128))
+  const int* num_m_tiles;      // device scalar: live 128-row tiles, or null (= ceil(M/128))
+  int group_align256;          // grouped problems: every expert segment is a multiple of 256 rows
   const int* expert_offsets;   // [E] cumulative row ends (SCHED_WGRAD)
   void* d;                     // output
   void* d_gate;                // optional gate pre-activation (SwiGLU)
@@ -70,7 +78,7 @@ struct TileCoord {
   bool valid;
 };
 
-template <int SCHED>
+template <int SCHED, int MT>
 __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, long long tile, int m_tiles, int n_tiles) {
   TileCoord t;
   t.valid = true;
@@ -95,15 +103,20 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, long long 
     const int in_group = static_cast<int>(tile - static_cast<long long>(group) * GROUP_M * n_tiles);
     t.m_tile = first_m + in_group % rows_in_group;
     t.n_tile = in_group / rows_in_group;
-    t.expert = p.tile_expert ? p.tile_expert[t.m_tile] : 0;
+    t.expert = p.tile_expert ? p.tile_expert[t.m_tile * MT] : 0;
     t.k_begin = 0;
     t.k_blocks = (p.K + BK - 1) / BK;
   }
   return t;
 }
 
-template <int A_MN, int B_MN, int EPI, int SCHED>
+template <int A_MN, int B_MN, int EPI, int SCHED, int MT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+  constexpr int STAGES = Cfg<MT>::STAGES;
+  constexpr int A_BYTES = Cfg<MT>::A_BYTES;
+  constexpr int STAGE_BYTES = Cfg<MT>::STAGE_BYTES;
+  constexpr int NACC = Cfg<MT>::NACC;
+  constexpr int TILE_M = BM * MT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -116,7 +129,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int m_tiles = p.num_m_tiles ? *p.num_m_tiles : (p.M + BM - 1) / BM;
+  const int m_tiles = p.num_m_tiles ? (*p.num_m_tiles + MT - 1) / MT : (p.M + TILE_M - 1) / TILE_M;
   const int n_tiles = (p.N + BN - 1) / BN;
   const long long total_tiles = static_cast<long long>(m_tiles) * n_tiles * (SCHED == SCHED_WGRAD ? p.num_experts : 1);
 
@@ -150,8 +163,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       int stage = 0;
       uint32_t phase = 0;
       for (long long tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-        const TileCoord t = decode_tile<SCHED>(p, tile, m_tiles, n_tiles);
-        const int m0 = t.m_tile * BM;
+        const TileCoord t = decode_tile<SCHED, MT>(p, tile, m_tiles, n_tiles);
+        const int m0 = t.m_tile * TILE_M;
         const int n0 = t.n_tile * BN;
         for (int kb = 0; kb < t.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
@@ -164,12 +177,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
           const int k0 = t.k_begin + kb * BK;
           // ---- A
-          if (A_MN) {
-            // MN-major: two boxes of [64 (m) x 64 (k)]; inner coordinate = m, outer = k row
-            tma_load_2d(sa, &p.map_a, &full_bar[stage], m0, k0);
-            tma_load_2d(sa + 8192, &p.map_a, &full_bar[stage], m0 + 64, k0);
-          } else {
-            tma_load_2d(sa, &p.map_a, &full_bar[stage], k0, m0);
+#pragma unroll
+          for (int i = 0; i < MT; ++i) {
+            if (A_MN) {
+              // MN-major: two boxes of [64 (m) x 64 (k)]; inner coordinate = m, outer = k row
+              tma_load_2d(sa + i * A_SUB_BYTES, &p.map_a, &full_bar[stage], m0 + i * BM, k0);
+              tma_load_2d(sa + i * A_SUB_BYTES + 8192, &p.map_a, &full_bar[stage], m0 + i * BM + 64, k0);
+            } else {
+              tma_load_2d(sa + i * A_SUB_BYTES, &p.map_a, &full_bar[stage], k0, m0 + i * BM);
+            }
           }
           // ---- B
           if (EPI == EPI_SWIGLU) {
@@ -202,14 +218,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       int acc = 0;
       uint32_t acc_phase = 0;
       for (long long tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-        const TileCoord t = decode_tile<SCHED>(p, tile, m_tiles, n_tiles);
+        const TileCoord t = decode_tile<SCHED, MT>(p, tile, m_tiles, n_tiles);
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
           *abort_flag = 1;
           atomicExch(p.status, 2);
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + (MT == 2 ? 0 : acc * BN);
         bool failed = false;
         for (int kb = 0; kb < t.k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) {
@@ -221,9 +237,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const uint32_t sb = sa + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t da = A_MN ? umma_smem_desc(sa + k * 2048, 8192, 1024) : umma_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc(sb + k * 2048, 8192, 1024) : umma_smem_desc(sb + k * 32, 16, 1024);
-            umma_bf16_ss(d_tmem, da, db, idesc, (kb | k) != 0);
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+              const uint32_t sai = sa + i * A_SUB_BYTES;
+              const uint64_t da = A_MN ? umma_smem_desc(sai + k * 2048, 8192, 1024) : umma_smem_desc(sai + k * 32, 16, 1024);
+              umma_bf16_ss(d_tmem + i * BN, da, db, idesc, (kb | k) != 0);
+            }
           }
           umma_commit(&empty_bar[stage]);   // frees the stage once these MMAs have read it
           if (++stage == STAGES) {
@@ -237,8 +257,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           break;
         }
         umma_commit(&tmem_full[acc]);
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1;
+        if (++acc == NACC) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
       }
     }
   } else {
@@ -248,17 +270,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     int acc = 0;
     uint32_t acc_phase = 0;
     for (long long tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-      const TileCoord t = decode_tile<SCHED>(p, tile, m_tiles, n_tiles);
+      const TileCoord t = decode_tile<SCHED, MT>(p, tile, m_tiles, n_tiles);
       if (!mbar_wait(&tmem_full[acc], acc_phase)) {
         *abort_flag = 1;
         atomicExch(p.status, 4);
         break;
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
-      const long long row = static_cast<long long>(t.m_tile) * BM + row_in_tile;
-      const bool row_ok = row < p.M;
       const bool empty_k = t.k_blocks == 0;   // an expert without rows contributes nothing
+#pragma unroll 1
+      for (int sub = 0; sub < MT; ++sub) {
+      const uint32_t taddr = tmem_base + (MT == 2 ? sub * BN : acc * BN) + (static_cast<uint32_t>(quad * 32) << 16);
+      const long long row = static_cast<long long>(t.m_tile) * TILE_M + sub * BM + row_in_tile;
+      const bool row_ok = row < p.M;
       if (EPI == EPI_SWIGLU) {
         __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(p.d);
         const long long half_n = p.N / 2;
@@ -364,11 +388,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           }
         }
       }
+      }  // sub
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1;
+      if (++acc == NACC) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
     }
   }
 
@@ -412,16 +439,35 @@ static int make_map(CUtensorMap* map, const void* base, long long inner, long lo
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-template <int A_MN, int B_MN, int EPI, int SCHED>
-static int launch(const GemmParams& p, int sms, cudaStream_t stream) {
-  auto kernel = gemm_tcgen05_kernel<A_MN, B_MN, EPI, SCHED>;
+template <int A_MN, int B_MN, int EPI, int SCHED, int MT>
+static int launch_mt(const GemmParams& p, int sms, cudaStream_t stream) {
+  auto kernel = gemm_tcgen05_kernel<A_MN, B_MN, EPI, SCHED, MT>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess) return -3;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MT>::SMEM) != cudaSuccess)
+      return -3;
     configured = true;
   }
-  kernel<<<sms, GEMM_THREADS, GEMM_SMEM, stream>>>(p);
+  kernel<<<sms, GEMM_THREADS, Cfg<MT>::SMEM, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+static int g_tile_mode = 0;   // 0 auto, 1 force 128x256, 2 force 256x256 where legal
+
+// 256x256 tiles need whole 256-row tiles of one expert (the caller says whether its segments are padded to
+// 256 rows) and enough tiles to fill the machine.  Grouped weight gradients stay on 128x256: their K extent per
+// expert is short, so losing the epilogue/main-loop overlap costs more than the operand traffic saves.
+template <int A_MN, int B_MN, int EPI, int SCHED>
+static int launch(const GemmParams& p, int sms, cudaStream_t stream) {
+  const bool legal = SCHED == SCHED_FLAT &&
+                     (p.tile_expert == nullptr ? p.num_m_tiles == nullptr : p.group_align256 != 0);
+  const long long tiles256 = static_cast<long long>((p.M + 255) / 256) * ((p.N + BN - 1) / BN) *
+                             (SCHED == SCHED_WGRAD ? p.num_experts : 1);
+  // measured: 256x256 wins from K ~ 6144 up (+14 % at K = 14336 and 28672); at K = 4096 the exposed epilogue
+  // costs more than the operand traffic saves
+  const bool big = g_tile_mode == 2 || (g_tile_mode == 0 && tiles256 >= 2LL * sms && p.K >= 6144);
+  if (legal && big) return launch_mt<A_MN, B_MN, EPI, SCHED, 2>(p, sms, stream);
+  return launch_mt<A_MN, B_MN, EPI, SCHED, 1>(p, sms, stream);
 }
 
 static int sm_count() {
@@ -446,17 +492,21 @@ using namespace b2;
 //   status         device int32 word, set non-zero if an in-kernel wait ran out
 extern "C" {
 
+// 0 automatic, 1 always 128x256 tiles, 2 256x256 tiles wherever they are legal.
+void b2_gemm_set_tile_mode(int mode) { g_tile_mode = mode; }
+
 // y[M,N] = a[M,K] * w[e][N,K]^T      (a K-major, w K-major)
 // epi: 0 bf16 store, 4 fp32 store.
 int b2_gemm_nt(const void* a, const void* w, void* d, int M, int N, int K, long long lda, long long ldw,
-               long long ldd, int num_experts, const int* tile_expert, const int* num_m_tiles, int epi, int* status,
-               cudaStream_t stream) {
+               long long ldd, int num_experts, const int* tile_expert, const int* num_m_tiles, int group_align256,
+               int epi, int* status, cudaStream_t stream) {
   if (N % 32 || K % 8) return -10;
   GemmParams p{};
   if (make_map(&p.map_a, a, K, M, lda, BM)) return -11;
   if (make_map(&p.map_b, w, K, static_cast<long long>(num_experts) * N, ldw, BN)) return -12;
   p.M = M; p.N = N; p.K = K; p.num_experts = num_experts; p.b_expert_rows = N; p.k_split = 0;
   p.tile_expert = tile_expert; p.num_m_tiles = num_m_tiles; p.d = d; p.ldd = ldd; p.status = status; p.beta = 0.f;
+  p.group_align256 = group_align256;
   if (epi == EPI_STORE_BF16) return launch<0, 0, EPI_STORE_BF16, SCHED_FLAT>(p, sm_count(), stream);
   if (epi == EPI_STORE_F32) return launch<0, 0, EPI_STORE_F32, SCHED_FLAT>(p, sm_count(), stream);
   return -13;
@@ -464,8 +514,8 @@ int b2_gemm_nt(const void* a, const void* w, void* d, int M, int N, int K, long 
 
 // h[M,F] = silu(a w1[e]^T) * (a w3[e]^T); optional gate/up pre-activations [M,F].
 int b2_gemm_swiglu(const void* a, const void* w1, const void* w3, void* h, void* gate, void* up, int M, int F, int K,
-                   long long lda, int num_experts, const int* tile_expert, const int* num_m_tiles, int* status,
-                   cudaStream_t stream) {
+                   long long lda, int num_experts, const int* tile_expert, const int* num_m_tiles, int group_align256,
+                   int* status, cudaStream_t stream) {
   if (F % 128 || K % 8) return -10;
   GemmParams p{};
   if (make_map(&p.map_a, a, K, M, lda, BM)) return -11;
@@ -473,7 +523,7 @@ int b2_gemm_swiglu(const void* a, const void* w1, const void* w3, void* h, void*
   if (make_map(&p.map_b2, w3, K, static_cast<long long>(num_experts) * F, K, 128)) return -12;
   p.M = M; p.N = 2 * F; p.K = K; p.num_experts = num_experts; p.b_expert_rows = F; p.k_split = 0;
   p.tile_expert = tile_expert; p.num_m_tiles = num_m_tiles; p.d = h; p.d_gate = gate; p.d_up = up; p.ldd = F;
-  p.status = status;
+  p.status = status; p.group_align256 = group_align256;
   return launch<0, 0, EPI_SWIGLU, SCHED_FLAT>(p, sm_count(), stream);
 }
 
@@ -481,7 +531,7 @@ int b2_gemm_swiglu(const void* a, const void* w1, const void* w3, void* h, void*
 // If w2 is given, K = k_split + K2 and rows k >= k_split come from w2 (dx = dg W1 + du W3 in one pass).
 int b2_gemm_nn(const void* a, const void* w, const void* w2, void* d, int M, int N, int K, int k_split, long long lda,
                long long ldw, long long ldd, int num_experts, const int* tile_expert, const int* num_m_tiles,
-               int* status, cudaStream_t stream) {
+               int group_align256, int* status, cudaStream_t stream) {
   if (N % 32 || K % 64 || (w2 && k_split % 64)) return -10;
   GemmParams p{};
   const int rows = w2 ? k_split : K;
@@ -490,6 +540,7 @@ int b2_gemm_nn(const void* a, const void* w, const void* w2, void* d, int M, int
   if (w2 && make_map(&p.map_b2, w2, N, static_cast<long long>(num_experts) * (K - k_split), ldw, 64)) return -12;
   p.M = M; p.N = N; p.K = K; p.num_experts = num_experts; p.b_expert_rows = rows; p.k_split = w2 ? k_split : 0;
   p.tile_expert = tile_expert; p.num_m_tiles = num_m_tiles; p.d = d; p.ldd = ldd; p.status = status;
+  p.group_align256 = group_align256;
   return launch<0, 1, EPI_STORE_BF16, SCHED_FLAT>(p, sm_count(), stream);
 }
 

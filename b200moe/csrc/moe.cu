@@ -5,7 +5,7 @@
 //
 // Layout contract.  Slots are numbered s = 2*token + j.  Expert e owns rows
 // [seg_start[e], seg_start[e] + count[e]) of the permuted buffer, in slot order;
-// every segment is padded with zero rows to a multiple of 128 so a GEMM tile
+// every segment is padded with zero rows to a multiple of 256 so a GEMM tile
 // never straddles two experts.  ``slot_row[s]`` is the row of slot s,
 // ``row_slot[r]`` the slot of row r (-1 for padding), ``offs[e]`` the padded
 // cumulative segment ends, ``tile_expert[i]`` the expert of 128-row tile i and
@@ -17,7 +17,8 @@
 namespace b2 {
 
 constexpr int PLAN_THREADS = 1024;
-constexpr int ALIGN_ROWS = 128;
+constexpr int ALIGN_ROWS = 256;   // segment padding; tile tables are per 128-row unit
+constexpr int TILE_ROWS = 128;
 
 __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long* __restrict__ idx, int slots, int E,
                                                                 int* __restrict__ slot_row, int* __restrict__ row_slot,
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long*
     for (int e = 0; e < E; ++e) {
       seg_start[e] = row;
       const int padded = (seg_count[e] + ALIGN_ROWS - 1) / ALIGN_ROWS * ALIGN_ROWS;
-      for (int t = 0; t < padded / ALIGN_ROWS; ++t) tile_expert[tile++] = e;
+      for (int t = 0; t < padded / TILE_ROWS; ++t) tile_expert[tile++] = e;
       row += padded;
       offs[e] = row;
       if (counts_out) counts_out[e] = seg_count[e];

@@ -19,7 +19,7 @@ import torch
 
 from . import native
 
-ALIGN = 128
+ALIGN = 256       # expert segments are padded to 256 rows (whole 256x256 GEMM tiles)
 
 
 def capacity_rows(slots: int, num_experts: int) -> int:
@@ -52,8 +52,8 @@ class _MoEFused(torch.autograd.Function):
             cap, offs, tile_expert, meta, x_perm = route.cap, route.offs, route.tile_expert, route.meta, route.x_perm
             slot_row = row_slot = None
         tiles = meta[0:1]
-        h, gate, up = native.gemm_swiglu(x_perm, w1, w3, tile_expert, tiles, save_gate_up=not recompute)
-        y_perm = native.gemm_nt(h, w2, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=experts)
+        h, gate, up = native.gemm_swiglu(x_perm, w1, w3, tile_expert, tiles, save_gate_up=not recompute, align256=True)
+        y_perm = native.gemm_nt(h, w2, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=experts, align256=True)
         if ep_ctx is None:
             out = native.moe_combine(y_perm, slot_row, weights, tokens)
         else:
@@ -82,7 +82,7 @@ class _MoEFused(torch.autograd.Function):
         dout = dout.contiguous()
         ffn = w1.shape[1]
         if recompute:
-            _, gate, up = native.gemm_swiglu(x_perm, w1, w3, tile_expert, tiles, save_gate_up=True)
+            _, gate, up = native.gemm_swiglu(x_perm, w1, w3, tile_expert, tiles, save_gate_up=True, align256=True)
         else:
             gate, up = rest
         if ep_ctx is None:
@@ -91,10 +91,11 @@ class _MoEFused(torch.autograd.Function):
                                         dweights=dweights.view(-1))
         else:
             dy_perm = ep_ctx.combine_backward(route, dout, y_perm, weights)
-        dh = native.gemm_nn(dy_perm, w2, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=experts)
+        dh = native.gemm_nn(dy_perm, w2, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=experts, align256=True)
         dgu, h = native.swiglu_bwd(dh, gate, up, live_rows=live_rows)
         del dh, gate, up
-        dx_perm = native.gemm_nn(dgu, w1, w2=w3, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=experts)
+        dx_perm = native.gemm_nn(dgu, w1, w2=w3, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=experts,
+                                 align256=True)
         dw2 = _wgrad(dy_perm, h, w2, offs, experts)
         dw1 = _wgrad(dgu[:, :ffn], x_perm, w1, offs, experts)
         dw3 = _wgrad(dgu[:, ffn:], x_perm, w3, offs, experts)

@@ -109,7 +109,13 @@ def _bf16(t):
 
 
 # ------------------------------------------------------------------------------ GEMM
-def gemm_nt(x, w, out_dtype=None, tile_expert=None, num_m_tiles=None, num_experts: int = 1):
+def set_gemm_tile_mode(mode: int) -> None:
+    """0: automatic; 1: always 128x256 CTA tiles; 2: 256x256 tiles wherever legal
+    (dense and weight-gradient problems).  For A/B measurements."""
+    require().b2_gemm_set_tile_mode(_I(mode))
+
+
+def gemm_nt(x, w, out_dtype=None, tile_expert=None, num_m_tiles=None, num_experts: int = 1, align256: bool = False):
     """``x [M,K] @ w[e] [N,K]ᵀ``.  Rows of ``w`` below 17: skinny path, fp32 result."""
     M, K = x.shape
     N = w.shape[-2]
@@ -121,12 +127,13 @@ def gemm_nt(x, w, out_dtype=None, tile_expert=None, num_m_tiles=None, num_expert
     out = torch.empty(M, N, dtype=out_dtype, device=x.device)
     assert x.stride(-1) == 1 and w.is_contiguous()
     _call("b2_gemm_nt", _p(_bf16(x)), _p(_bf16(w)), _p(out), _I(M), _I(N), _I(K), _L(x.stride(0)), _L(K), _L(N),
-          _I(num_experts), _p(tile_expert), _p(num_m_tiles), _I(0 if out_dtype == torch.bfloat16 else 4),
+          _I(num_experts), _p(tile_expert), _p(num_m_tiles), _I(int(align256)),
+          _I(0 if out_dtype == torch.bfloat16 else 4),
           _p(status_word(x.device)), _stream())
     return out
 
 
-def gemm_nn(dy, w, w2=None, tile_expert=None, num_m_tiles=None, num_experts: int = 1):
+def gemm_nn(dy, w, w2=None, tile_expert=None, num_m_tiles=None, num_experts: int = 1, align256: bool = False):
     """``dy [M,K] @ w[e] [K,N]`` (``w`` rows are the reduction index).  With ``w2``
     the reduction continues over ``w2``'s rows: ``dy = [a | b]``, result ``a w + b w2``."""
     M, K = dy.shape
@@ -139,7 +146,7 @@ def gemm_nn(dy, w, w2=None, tile_expert=None, num_m_tiles=None, num_experts: int
     k_split = w.shape[-2] if w2 is not None else 0
     assert dy.stride(-1) == 1 and w.is_contiguous()
     _call("b2_gemm_nn", _p(_bf16(dy)), _p(_bf16(w)), _p(w2), _p(out), _I(M), _I(N), _I(K), _I(k_split),
-          _L(dy.stride(0)), _L(N), _L(N), _I(num_experts), _p(tile_expert), _p(num_m_tiles),
+          _L(dy.stride(0)), _L(N), _L(N), _I(num_experts), _p(tile_expert), _p(num_m_tiles), _I(int(align256)),
           _p(status_word(dy.device)), _stream())
     return out
 
@@ -173,7 +180,7 @@ def gemm_tn(dy, x, out=None, accumulate: bool = False, out_dtype=None, expert_of
     return out if want is None or want == out.dtype else out.to(want)
 
 
-def gemm_swiglu(x, w1, w3, tile_expert=None, num_m_tiles=None, save_gate_up: bool = True):
+def gemm_swiglu(x, w1, w3, tile_expert=None, num_m_tiles=None, save_gate_up: bool = True, align256: bool = False):
     """``h = silu(x w1ᵀ) · (x w3ᵀ)`` per expert tile; optionally also the two pre-activations."""
     M, K = x.shape
     E, F = w1.shape[0], w1.shape[1]
@@ -181,7 +188,8 @@ def gemm_swiglu(x, w1, w3, tile_expert=None, num_m_tiles=None, save_gate_up: boo
     gate = torch.empty_like(h) if save_gate_up else None
     up = torch.empty_like(h) if save_gate_up else None
     _call("b2_gemm_swiglu", _p(_bf16(x)), _p(_bf16(w1)), _p(_bf16(w3)), _p(h), _p(gate), _p(up), _I(M), _I(F), _I(K),
-          _L(x.stride(0)), _I(E), _p(tile_expert), _p(num_m_tiles), _p(status_word(x.device)), _stream())
+          _L(x.stride(0)), _I(E), _p(tile_expert), _p(num_m_tiles), _I(int(align256)), _p(status_word(x.device)),
+          _stream())
     return h, gate, up
 
 

@@ -50,8 +50,10 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--compare", action="store_true", help="also time the PyTorch library op")
+    ap.add_argument("--tile-mode", type=int, default=0, help="GEMM CTA tile: 0 auto, 1 128x256, 2 256x256")
     args = ap.parse_args()
     native.require()
+    native.set_gemm_tile_mode(args.tile_mode)
     tf_peak, bw_peak, tag = peaks()
     T, D, Fd, E = args.tokens, 4096, 14336, 8
     rows = []
@@ -86,18 +88,19 @@ def main():
     xp = rnd(R, D)
     w1, w3, w2 = rnd(E, Fd, D, scale=0.02), rnd(E, Fd, D, scale=0.02), rnd(E, D, Fd, scale=0.02)
     gemm_case("moe gate/up + swiglu 32768x(2x14336)x4096", 2 * R * 2 * Fd * D,
-              lambda: native.gemm_swiglu(xp, w1, w3, tile_expert, tiles, save_gate_up=True))
+              lambda: native.gemm_swiglu(xp, w1, w3, tile_expert, tiles, save_gate_up=True, align256=True))
     gemm_case("moe gate/up + swiglu (h only)", 2 * R * 2 * Fd * D,
-              lambda: native.gemm_swiglu(xp, w1, w3, tile_expert, tiles, save_gate_up=False))
+              lambda: native.gemm_swiglu(xp, w1, w3, tile_expert, tiles, save_gate_up=False, align256=True))
     h = rnd(R, Fd, scale=0.1)
     gemm_case("moe down 32768x4096x14336", 2 * R * D * Fd,
-              lambda: native.gemm_nt(h, w2, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=E))
+              lambda: native.gemm_nt(h, w2, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=E, align256=True))
     dyp = rnd(R, D)
     gemm_case("moe dh = dy W2 32768x14336x4096", 2 * R * D * Fd,
-              lambda: native.gemm_nn(dyp, w2, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=E))
+              lambda: native.gemm_nn(dyp, w2, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=E, align256=True))
     dgu = rnd(R, 2 * Fd, scale=0.1)
     gemm_case("moe dx = dg W1 + du W3 32768x4096x28672", 2 * R * D * 2 * Fd,
-              lambda: native.gemm_nn(dgu, w1, w2=w3, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=E))
+              lambda: native.gemm_nn(dgu, w1, w2=w3, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=E,
+                                     align256=True))
     g32 = torch.zeros(E, D, Fd, device="cuda", dtype=torch.bfloat16)
     gemm_case("moe dW2 += dy^T h (bf16 acc)", 2 * R * D * Fd,
               lambda: native.gemm_tn(dyp, h, out=g32, accumulate=True, expert_offsets=offs, num_experts=E))
@@ -137,7 +140,7 @@ def main():
     wts = torch.rand(T, 2, device="cuda")
     bw_case("moe_combine 16384x4096", 3 * T * D * 2, lambda: native.moe_combine(xp, slot_row, wts, T))
     os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    with open(os.path.join(ROOT, "gpurun_out", "kernels.json"), "w") as f:
+    with open(os.path.join(ROOT, "gpurun_out", f"kernels_mode{args.tile_mode}.json"), "w") as f:
         json.dump(rows, f, indent=1)
 
 
