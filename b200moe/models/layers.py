@@ -158,8 +158,13 @@ class MultiHeadLayerLL(nn.Module):
         fused_rope = False
         if self.qkv_weight is not None:
             qkv = ops.linear(x.reshape(batch * seq, -1), self.qkv_weight)
-            if (self.use_rope and token_positions is None and mask is None and ops.use_native(qkv, "rope")
-                    and not ops.use_native(qkv, "attention")):
+            from ..ops.attention import attention_backend, fused_qkv_attention
+            if (token_positions is None and mask is None and ops.use_native(qkv, "attention")
+                    and attention_backend() == "native" and hd == 128 and seq % 128 == 0):
+                cos, sin = (self.RoPE.cos, self.RoPE.sin) if self.use_rope else (None, None)
+                out = fused_qkv_attention(qkv, batch, seq, hq, hkv, hd, cos, sin)
+                return self.output_proj(out.reshape(batch, seq, hq * hd))
+            if self.use_rope and token_positions is None and mask is None and ops.use_native(qkv, "rope"):
                 from ..ops.attention import rope_qk_
                 qkv = rope_qk_(qkv, seq, hq + 2 * hkv, hq + hkv, hd, self.RoPE.cos, self.RoPE.sin)
                 fused_rope = True

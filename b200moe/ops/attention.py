@@ -58,11 +58,59 @@ def rope_qk_(qkv2d, seq, total_heads, heads, head_dim, cos, sin):
     return _RopeQK.apply(qkv2d, seq, total_heads, heads, head_dim, cos, sin)
 
 
+class _FusedQKVAttention(torch.autograd.Function):
+    """RoPE + causal GQA attention on the fused QKV projection ``[tokens, (Hq + 2 Hkv) * hd]``.
+    Forward rotates q and k in place inside the projection buffer and runs the tcgen05 attention kernel
+    on views of it; backward writes dq, dk, dv into one fused gradient buffer and un-rotates it in place,
+    so autograd sees a single gradient for the projection output."""
+
+    @staticmethod
+    def forward(ctx, qkv, batch, seq, hq, hkv, hd, cos, sin):
+        native = _native()
+        total = hq + 2 * hkv
+        if cos is not None:
+            native.rope_inplace(qkv, 0, qkv.shape[0], seq, hq + hkv, hd, total * hd, cos, sin, 1.0)
+        ctx.mark_dirty(qkv)
+        view = qkv.view(batch, seq, total, hd)
+        out, lse, _, _ = native.attention_fwd(view[:, :, :hq], view[:, :, hq:hq + hkv], view[:, :, hq + hkv:])
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.meta = (batch, seq, hq, hkv, hd, cos, sin)
+        return qkv, out
+
+    @staticmethod
+    def backward(ctx, _dqkv_unused, dout):
+        native = _native()
+        qkv, out, lse = ctx.saved_tensors
+        batch, seq, hq, hkv, hd, cos, sin = ctx.meta
+        total = hq + 2 * hkv
+        view = qkv.view(batch, seq, total, hd)
+        dqkv = torch.empty_like(qkv)
+        dview = dqkv.view(batch, seq, total, hd)
+        native.attention_bwd(dout, view[:, :, :hq], view[:, :, hq:hq + hkv], view[:, :, hq + hkv:], out, lse,
+                             grads=(dview[:, :, :hq], dview[:, :, hq:hq + hkv], dview[:, :, hq + hkv:]))
+        if cos is not None:
+            native.rope_inplace(dqkv, 0, dqkv.shape[0], seq, hq + hkv, hd, total * hd, cos, sin, -1.0)
+        return dqkv, None, None, None, None, None, None, None
+
+
+def fused_qkv_attention(qkv2d, batch, seq, hq, hkv, hd, cos, sin):
+    """Returns the attention output ``[B, S, Hq, hd]`` of a fused projection ``[B*S, (Hq+2Hkv)*hd]``."""
+    _, out = _FusedQKVAttention.apply(qkv2d, batch, seq, hq, hkv, hd, cos, sin)
+    return out
+
+
+def attention_backend() -> str:
+    """``native`` (this repository's tcgen05 kernels) or ``library`` (cuDNN through PyTorch); chosen by the
+    environment variable ``B200MOE_ATTENTION``."""
+    import os
+    return os.environ.get("B200MOE_ATTENTION", "library")
+
+
 def rope_attention(q, k, v, cos, sin):
     """Returns ``[B, S, Hq, head_dim]``.  ``cos``/``sin`` are ``[S_max, hd/2]``
     fp32 tables or ``None`` for no rotation."""
     from . import use_native
-    if use_native(q, "attention"):
+    if use_native(q, "attention") and attention_backend() == "native" and q.shape[-1] == 128 and q.shape[1] % 128 == 0:
         return _RopeAttention.apply(q, k, v, cos, sin)
     if q.is_cuda:
         # library attention on the GPU (A/B baseline only)

@@ -294,6 +294,54 @@ def rope_inplace(buf, first_elem_offset, tokens, seq, heads, head_dim, pitch, co
     _call("b2_rope", ptr, _p(cos), _p(sin), _I(tokens), _I(seq), _I(heads), _I(head_dim), _L(pitch), _F(sign), _stream())
 
 
+# ------------------------------------------------------------------------------ attention
+def _token_pitch(t):
+    B, S, H, hd = t.shape
+    if hd != 128 or t.stride(3) != 1 or t.stride(2) != hd or t.stride(0) != S * t.stride(1):
+        raise ValueError("attention tensors must be [B, S, H, 128] views with contiguous heads and uniform token pitch")
+    return t.stride(1)
+
+
+def attention_fwd(q, k, v, cos=None, sin=None):
+    """Causal GQA attention.  ``q [B,S,Hq,128]``, ``k, v [B,S,Hkv,128]`` bf16 (views of a fused projection are
+    fine).  With ``cos``/``sin`` the rotation is applied to copies of q and k first.  Returns
+    ``(out [B,S,Hq,128], lse fp32 [B,Hq,S], q_used, k_used)``."""
+    B, S, Hq, hd = q.shape
+    Hkv = k.shape[2]
+    if cos is not None:
+        q, k = q.contiguous().clone(), k.contiguous().clone()
+        rope_inplace(q, 0, B * S, S, Hq, hd, Hq * hd, cos, sin, 1.0)
+        rope_inplace(k, 0, B * S, S, Hkv, hd, Hkv * hd, cos, sin, 1.0)
+    out = torch.empty(B, S, Hq, hd, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
+    _call("b2_attention_fwd", _p(_bf16(q)), _p(_bf16(k)), _p(_bf16(v)), _L(_token_pitch(q)), _L(_token_pitch(k)),
+          _L(_token_pitch(v)), _p(out), _p(lse), _I(B), _I(S), _I(Hq), _I(Hkv), _F(hd ** -0.5),
+          _p(status_word(q.device)), _stream())
+    return out, lse, q, k
+
+
+def attention_bwd(dout, q, k, v, out, lse, cos=None, sin=None, grads=None):
+    """Gradients of ``attention_fwd`` w.r.t. the (rotated) q, k and v.  ``grads`` may give three preallocated
+    ``[B,S,H,128]`` views (for instance slices of one fused buffer) to write into."""
+    B, S, Hq, hd = q.shape
+    Hkv = k.shape[2]
+    if grads is None:
+        grads = (torch.empty(B, S, Hq, hd, dtype=torch.bfloat16, device=q.device),
+                 torch.empty(B, S, Hkv, hd, dtype=torch.bfloat16, device=q.device),
+                 torch.empty(B, S, Hkv, hd, dtype=torch.bfloat16, device=q.device))
+    dq, dk, dv = grads
+    delta = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
+    dout = _bf16(dout).contiguous()
+    _call("b2_attention_bwd", _p(dout), _p(q), _p(k), _p(v), _p(_bf16(out)), _p(lse), _L(_token_pitch(q)),
+          _L(_token_pitch(k)), _L(_token_pitch(v)), _p(delta), _p(dq), _p(dk), _p(dv), _L(_token_pitch(dq)),
+          _L(_token_pitch(dk)), _L(_token_pitch(dv)), _I(B), _I(S), _I(Hq), _I(Hkv), _F(hd ** -0.5),
+          _p(status_word(q.device)), _stream(), n=3)
+    if cos is not None:
+        rope_inplace(dq, 0, B * S, S, Hq, hd, _token_pitch(dq), cos, sin, -1.0)
+        rope_inplace(dk, 0, B * S, S, Hkv, hd, _token_pitch(dk), cos, sin, -1.0)
+    return dq, dk, dv
+
+
 # ------------------------------------------------------------------------------ MoE routing
 def moe_plan(idx, num_experts, capacity_rows):
     slots = idx.numel()

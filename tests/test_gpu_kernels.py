@@ -303,3 +303,43 @@ def test_tiny_model_native_vs_torch_path(native):
     assert losses[0] == pytest.approx(losses[1], abs=5e-2)
     native.check_status()
     assert native.launch_count() > 0
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 4, 1), (2, 512, 8, 2), (1, 1024, 4, 4)])
+def test_attention_forward_backward(native, B, S, Hq, Hkv):
+    from b200moe.ops import functional as Fn
+    torch.manual_seed(2)
+    hd, total = 128, Hq + 2 * Hkv
+    qkv = _rand(B, S, total, hd)
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    out, lse, _, _ = native.attention_fwd(q, k, v)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = Fn.attention_ref(qf, kf, vf, None, None, causal=True)
+    assert _rel(out, ref) < 1e-2
+    scores = torch.einsum("bshd,bthd->bhst", qf, kf.repeat_interleave(Hq // Hkv, 2)) / math.sqrt(hd)
+    scores = scores.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool, device="cuda"), 1), float("-inf"))
+    assert _rel(lse, torch.logsumexp(scores, -1)) < 1e-3
+    dout = _rand(B, S, Hq, hd)
+    dq, dk, dv = native.attention_bwd(dout, q, k, v, out, lse)
+    ref.backward(dout.float())
+    assert _rel(dq, qf.grad) < 2e-2 and _rel(dk, kf.grad) < 2e-2 and _rel(dv, vf.grad) < 2e-2
+    native.check_status()
+
+
+def test_fused_qkv_attention_with_rope(native):
+    from b200moe.ops import functional as Fn
+    from b200moe.ops.attention import fused_qkv_attention
+    B, S, Hq, Hkv, hd = 2, 256, 8, 2, 128
+    total = Hq + 2 * Hkv
+    cos, sin = Fn.rope_tables(10000.0, hd, S, device="cuda")
+    base = _rand(B * S, total * hd).requires_grad_(True)
+    out = fused_qkv_attention(base * 1.0, B, S, Hq, Hkv, hd, cos, sin)
+    ref_in = base.detach().float().requires_grad_(True)
+    view = ref_in.view(B, S, total, hd)
+    ref = Fn.attention_ref(view[:, :, :Hq], view[:, :, Hq:Hq + Hkv], view[:, :, Hq + Hkv:], cos, sin, causal=True)
+    assert _rel(out, ref) < 1e-2
+    g = _rand(B, S, Hq, hd)
+    out.backward(g)
+    ref.backward(g.float())
+    assert _rel(base.grad, ref_in.grad) < 2e-2
+    native.check_status()
