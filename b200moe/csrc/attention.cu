@@ -186,18 +186,23 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_fwd_kernel(const __grid_
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(ts + c * 32, raw[c]);
       tmem_ld_wait();
-      float mx = -INFINITY;
-      const bool diag = j == qt;
+      float mx = m_ref;
+      if (j == qt) {                       // diagonal tile: keys after the query are masked
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i > r) raw[c][i] = 0xff800000u;   // -inf
+      }
+      float mpart[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mpart[i] = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(raw[c][i]);
-          if (diag && c * 32 + i > r) v = -INFINITY;
-          raw[c][i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
-      mx = fmaxf(mx, m_ref);
+        for (int i = 0; i < 32; ++i) mpart[i & 7] = fmaxf(mpart[i & 7], __uint_as_float(raw[c][i]));
+      mx = fmaxf(mx, fmaxf(fmaxf(fmaxf(mpart[0], mpart[1]), fmaxf(mpart[2], mpart[3])),
+                           fmaxf(fmaxf(mpart[4], mpart[5]), fmaxf(mpart[6], mpart[7]))));
       const bool need = (mx - m_ref) * p.scale_log2 > 8.f;      // also true on the first tile (m_ref = -inf)
       const bool any = __any_sync(0xffffffffu, need);
       float alpha = 1.f;
@@ -206,17 +211,19 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_fwd_kernel(const __grid_
         m_ref = mx;
       }
       const float neg = -m_ref * p.scale_log2;
-      float sum = 0.f;
+      float part[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // independent partial sums: no 128-long add chain
       uint32_t packed[2][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(raw[c][i]), p.scale_log2, neg));
-          const float p1 = ex2(fmaf(__uint_as_float(raw[c][i + 1]), p.scale_log2, neg));
-          sum += p0 + p1;
+          const float x0 = fmaf(__uint_as_float(raw[c][i]), p.scale_log2, neg);
+          const float x1 = fmaf(__uint_as_float(raw[c][i + 1]), p.scale_log2, neg);
+          const float p0 = ex2(x0), p1 = ex2(x1);
+          part[(i >> 1) & 7] += p0 + p1;
           packed[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16(p0, p1);
         }
+      const float sum = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
       l = l * alpha + sum;
       // P (bf16 pairs) overwrites the first 64 columns of this S buffer
       tmem_st_32x32(ts, packed[0]);
@@ -430,13 +437,19 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_bwd_dkv_kernel(const __g
         for (int i = 0; i < 32; ++i) {
           const int q = c * 32 + i;
           const float lq = __shfl_sync(0xffffffffu, lse_reg[c], i);
-          float v = ex2(fmaf(__uint_as_float(raw[i]), p.scale_log2, -lq));
-          if (diag && r > q) v = 0.f;                       // key after query
-          pf[q] = v;
+          const float x = fmaf(__uint_as_float(raw[i]), p.scale_log2, -lq);
+          pf[q] = ex2(x);
         }
+      }
+      if (diag) {                                           // key after query
+#pragma unroll
+        for (int q = 0; q < 128; ++q)
+          if (r > q) pf[q] = 0.f;
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16(pf[c * 32 + i], pf[c * 32 + i + 1]);
-      }
       tmem_st_32x32(t_st + lane_base, pk[0]);
       tmem_st_32x32(t_st + lane_base + 32, pk[1]);
       tmem_st_wait();
@@ -615,10 +628,14 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_bwd_dq_kernel(const __gr
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float v = ex2(fmaf(__uint_as_float(raw[i]), p.scale_log2, -lse2));
-          if (diag && c * 32 + i > r) v = 0.f;
-          pf[c * 32 + i] = v;
+          const float x = fmaf(__uint_as_float(raw[i]), p.scale_log2, -lse2);
+          pf[c * 32 + i] = ex2(x);
         }
+      }
+      if (diag) {
+#pragma unroll
+        for (int k = 0; k < 128; ++k)
+          if (k > r) pf[k] = 0.f;
       }
       if (!mbar_wait(&bars->dp_full, ph)) { ATTN_FAIL(226); break; }
       tc_fence_after();

@@ -100,10 +100,10 @@ def fused_qkv_attention(qkv2d, batch, seq, hq, hkv, hd, cos, sin):
 
 
 def attention_backend() -> str:
-    """``native`` (this repository's tcgen05 kernels) or ``library`` (cuDNN through PyTorch); chosen by the
+    """``native`` (this repository's tcgen05 kernels, the default) or ``library`` (cuDNN through PyTorch, for A/B runs); chosen by the
     environment variable ``B200MOE_ATTENTION``."""
     import os
-    return os.environ.get("B200MOE_ATTENTION", "library")
+    return os.environ.get("B200MOE_ATTENTION", "native")
 
 
 def rope_attention(q, k, v, cos, sin):
