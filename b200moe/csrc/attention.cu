@@ -12,6 +12,7 @@
 //   warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax / correction / epilogue
 //   (one query row per thread).  Two S buffers let QK^T of tile j+1 run under the
 //   softmax of tile j; O is rescaled only when a row maximum grew by more than 2^8.
+// Backward kernels run 320 threads: two softmax groups split the 128 columns of a tile.
 // Backward dK/dV, one CTA per (128 keys, kv head, batch): loops over the 4 query heads
 //   of the group and their causal query tiles with S^T = K Q^T, dP^T = V dO^T, so P^T
 //   and dS^T are A operands in TMEM; dV and dK accumulate in TMEM over the whole loop
@@ -29,6 +30,7 @@ constexpr int TK = 128;
 constexpr int TILE_BYTES = 128 * HD * 2;      // 32 KiB: two swizzle atoms of [128 rows x 64 cols]
 constexpr int ATOM_BYTES = 16384;
 constexpr int ATTN_THREADS = 192;
+constexpr int ATTN_BWD_THREADS = 320;   // TMA warp, MMA warp, two softmax groups of four warps
 
 struct AttnParams {
   CUtensorMap map_q, map_k, map_v, map_do;
@@ -310,7 +312,11 @@ struct KvBars {
 };
 
 // TMEM: S^T / P^T [0,128), dP^T / dS^T [128,256), dV [256,384), dK [384,512).
-__global__ void __launch_bounds__(ATTN_THREADS, 1) attn_bwd_dkv_kernel(const __grid_constant__ AttnParams p) {
+// 320 threads: warp 0 TMA, warp 1 MMA, warps 2-9 two softmax groups; group g handles query columns
+// [64 g, 64 g + 64) of the 128 x 128 tile (two warps per scheduler hide each other's latency).
+// MMA order per query tile: dV(it), S^T(it+1), dK(it), dP^T(it+1) - S^T of the next tile runs on the
+// tensor core while the softmax warps turn dP^T into dS^T.
+__global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_bwd_dkv_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
@@ -337,8 +343,8 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_bwd_dkv_kernel(const __g
     }
     mbar_init(&bars->st_full, 1);
     mbar_init(&bars->dpt_full, 1);
-    mbar_init(&bars->p_ready, 4);
-    mbar_init(&bars->ds_ready, 4);
+    mbar_init(&bars->p_ready, 8);
+    mbar_init(&bars->ds_ready, 8);
     mbar_init(&bars->acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -374,84 +380,96 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_bwd_dkv_kernel(const __g
       constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 128, 0, 0);   // both operands K-major
       constexpr uint32_t idesc_tn = umma_idesc_bf16(128, 128, 0, 1);   // A from TMEM, B MN-major
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-      bool ok = mbar_wait(&bars->kv_full, 0);
+      auto issue_st = [&](int it) {          // S^T[key, q] = K Q^T
+        const uint32_t q_addr = smem_u32(sQ + (it & 1) * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16_ss(t_st, desc_kmajor(k_addr, ks), desc_kmajor(q_addr, ks), idesc_kk, ks != 0);
+        umma_commit(&bars->st_full);
+      };
+      auto issue_dpt = [&](int it) {         // dP^T[key, q] = V dO^T
+        const uint32_t do_addr = smem_u32(sDO + (it & 1) * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16_ss(t_dpt, desc_kmajor(v_addr, ks), desc_kmajor(do_addr, ks), idesc_kk, ks != 0);
+        umma_commit(&bars->dpt_full);
+      };
+      bool ok = mbar_wait(&bars->kv_full, 0) && mbar_wait(&bars->qd_full[0], 0);
       if (!ok) ATTN_FAIL(212);
+      if (ok) {
+        tc_fence_after();
+        issue_st(0);
+        issue_dpt(0);
+      }
       for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
         const int s = it & 1;
         const uint32_t ph = it & 1;
-        if (!mbar_wait(&bars->qd_full[s], (it >> 1) & 1)) { ATTN_FAIL(213); break; }
-        // the previous iteration's dV/dK MMAs read P^T/dS^T from the buffers S^T/dP^T overwrite:
-        // same-thread issue order keeps them ahead of these writes
-        tc_fence_after();
         const uint32_t q_addr = smem_u32(sQ + s * TILE_BYTES), do_addr = smem_u32(sDO + s * TILE_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)      // S^T[key, q] = K Q^T
-          umma_bf16_ss(t_st, desc_kmajor(k_addr, ks), desc_kmajor(q_addr, ks), idesc_kk, ks != 0);
-        umma_commit(&bars->st_full);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)      // dP^T[key, q] = V dO^T
-          umma_bf16_ss(t_dpt, desc_kmajor(v_addr, ks), desc_kmajor(do_addr, ks), idesc_kk, ks != 0);
-        umma_commit(&bars->dpt_full);
         if (!mbar_wait(&bars->p_ready, ph)) { ATTN_FAIL(214); break; }
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)      // dV[key, d] += P^T[key, q] dO[q, d]
-          umma_bf16_ts(t_dv, t_st + ks * 8, desc_mnmajor(do_addr, ks), idesc_tn, (it | ks) != 0);
+          umma_bf16_ts(t_dv, t_st + (ks >> 2) * 64 + (ks & 3) * 8, desc_mnmajor(do_addr, ks), idesc_tn, (it | ks) != 0);
+        const bool more = it + 1 < iters;
+        if (more) {
+          if (!mbar_wait(&bars->qd_full[(it + 1) & 1], ((it + 1) >> 1) & 1)) { ATTN_FAIL(213); break; }
+          tc_fence_after();
+          issue_st(it + 1);                 // overwrites P^T only after dV above (same-thread issue order)
+        }
         if (!mbar_wait(&bars->ds_ready, ph)) { ATTN_FAIL(215); break; }
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)      // dK[key, d] += dS^T[key, q] Q[q, d]
-          umma_bf16_ts(t_dk, t_dpt + ks * 8, desc_mnmajor(q_addr, ks), idesc_tn, (it | ks) != 0);
+          umma_bf16_ts(t_dk, t_dpt + (ks >> 2) * 64 + (ks & 3) * 8, desc_mnmajor(q_addr, ks), idesc_tn, (it | ks) != 0);
         umma_commit(&bars->qd_empty[s]);
         umma_commit(&bars->acc_done);
+        if (more) issue_dpt(it + 1);        // overwrites dS^T only after dK above
       }
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;                      // which 64 query columns this thread handles
     const int r = quad * 32 + lane;                        // key row inside the tile
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const int col0 = half * 64;
     for (int it = 0; it < iters && !*abort_flag; ++it) {
       const int hq = hk * group + it / per_head;
       const int qi = kt + it % per_head;
       const uint32_t ph = it & 1;
-      const size_t stat = (static_cast<size_t>(b) * p.Hq + hq) * p.S + qi * TQ;
-      // statistics of the 128 query columns: lane i keeps those of queries 32c + i and the warp shuffles them
-      float lse_reg[4], dl_reg[4];
+      const size_t stat = (static_cast<size_t>(b) * p.Hq + hq) * p.S + qi * TQ + col0;
+      // statistics of my 64 query columns: lane i keeps those of columns 32c + i and the warp shuffles them
+      float lse_reg[2], dl_reg[2];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         lse_reg[c] = p.lse[stat + c * 32 + lane] * 1.4426950408889634f;
         dl_reg[c] = p.delta[stat + c * 32 + lane];
       }
       if (!mbar_wait(&bars->st_full, ph)) { ATTN_FAIL(216); break; }
       tc_fence_after();
       const bool diag = qi == kt;
-      // P^T = exp(S^T * scale - lse[q]); columns are queries
-      uint32_t pk[2][32];
-      float pf[128];
+      uint32_t pk[32];
+      float pf[64];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t raw[32];
-        tmem_ld_32x32(t_st + lane_base + c * 32, raw);
+        tmem_ld_32x32(t_st + lane_base + col0 + c * 32, raw);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int q = c * 32 + i;
           const float lq = __shfl_sync(0xffffffffu, lse_reg[c], i);
-          const float x = fmaf(__uint_as_float(raw[i]), p.scale_log2, -lq);
-          pf[q] = ex2(x);
+          pf[c * 32 + i] = ex2(fmaf(__uint_as_float(raw[i]), p.scale_log2, -lq));
         }
       }
       if (diag) {                                           // key after query
 #pragma unroll
-        for (int q = 0; q < 128; ++q)
-          if (r > q) pf[q] = 0.f;
+        for (int q = 0; q < 64; ++q)
+          if (r > col0 + q) pf[q] = 0.f;
       }
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16(pf[c * 32 + i], pf[c * 32 + i + 1]);
-      tmem_st_32x32(t_st + lane_base, pk[0]);
-      tmem_st_32x32(t_st + lane_base + 32, pk[1]);
+      for (int i = 0; i < 64; i += 2) pk[i >> 1] = pack_bf16(pf[i], pf[i + 1]);
+      // P^T as bf16 pairs, written over the columns this thread has just read: queries 0-63 land in columns
+      // [0,32), queries 64-127 in [64,96)
+      tmem_st_32x32(t_st + lane_base + col0, pk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -459,9 +477,9 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_bwd_dkv_kernel(const __g
       if (!mbar_wait(&bars->dpt_full, ph)) { ATTN_FAIL(217); break; }
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t raw[32];
-        tmem_ld_32x32(t_dpt + lane_base + c * 32, raw);
+        tmem_ld_32x32(t_dpt + lane_base + col0 + c * 32, raw);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -469,19 +487,17 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_bwd_dkv_kernel(const __g
           const float dq0 = __shfl_sync(0xffffffffu, dl_reg[c], i), dq1 = __shfl_sync(0xffffffffu, dl_reg[c], i + 1);
           const float d0 = pf[q] * (__uint_as_float(raw[i]) - dq0) * p.scale;
           const float d1 = pf[q + 1] * (__uint_as_float(raw[i + 1]) - dq1) * p.scale;
-          pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16(d0, d1);
+          pk[q >> 1] = pack_bf16(d0, d1);
         }
       }
-      tmem_st_32x32(t_dpt + lane_base, pk[0]);
-      tmem_st_32x32(t_dpt + lane_base + 32, pk[1]);
+      tmem_st_32x32(t_dpt + lane_base + col0, pk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->ds_ready);
-      // S^T / dP^T are rewritten by the next iteration's MMAs only after this iteration's dV/dK MMAs
-      if (!mbar_wait(&bars->acc_done, ph)) { ATTN_FAIL(218); break; }
     }
-    if (!*abort_flag) {
+    if (!*abort_flag && half == 0) {
+      if (!mbar_wait(&bars->acc_done, (iters - 1) & 1)) ATTN_FAIL(218);
       tc_fence_after();
       const size_t token = static_cast<size_t>(row_k + r);
       __nv_bfloat16* dvp = p.dv + token * p.dv_pitch + hk * HD;
@@ -518,11 +534,13 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_bwd_dkv_kernel(const __g
 
 // ================================================================= backward: dQ
 struct DqBars {
-  uint64_t qd_full, kv_full[2], kv_empty[2], s_full, dp_full, ds_ready, acc_done;
+  uint64_t qd_full, kv_full[2], kv_empty[2], s_full, s_taken, dp_full, ds_ready, acc_done;
 };
 
-// TMEM: S [0,128), dP / dS [128,256), dQ [256,384).
-__global__ void __launch_bounds__(ATTN_THREADS, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnParams p) {
+// TMEM: S [0,128), dP / dS [128,256), dQ [256,384).  320 threads like the dK/dV kernel: softmax group g
+// handles key columns [64 g, 64 g + 64).  P stays in registers, so S of the next key tile is issued as soon
+// as both groups have read S (s_taken) and runs under the dS computation.
+__global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -548,8 +566,9 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_bwd_dq_kernel(const __gr
       mbar_init(&bars->kv_empty[s], 1);
     }
     mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->s_taken, 8);
     mbar_init(&bars->dp_full, 1);
-    mbar_init(&bars->ds_ready, 4);
+    mbar_init(&bars->ds_ready, 8);
     mbar_init(&bars->acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -583,35 +602,56 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_bwd_dq_kernel(const __gr
       constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_tn = umma_idesc_bf16(128, 128, 0, 1);
       const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
-      bool ok = mbar_wait(&bars->qd_full, 0);
+      auto issue_s = [&](int j) {           // S[q, key] = Q K^T
+        const uint32_t k_addr = smem_u32(sK + (j & 1) * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16_ss(t_s, desc_kmajor(q_addr, ks), desc_kmajor(k_addr, ks), idesc_kk, ks != 0);
+        umma_commit(&bars->s_full);
+      };
+      auto issue_dp = [&](int j) {          // dP[q, key] = dO V^T
+        const uint32_t v_addr = smem_u32(sV + (j & 1) * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16_ss(t_dp, desc_kmajor(do_addr, ks), desc_kmajor(v_addr, ks), idesc_kk, ks != 0);
+        umma_commit(&bars->dp_full);
+      };
+      bool ok = mbar_wait(&bars->qd_full, 0) && mbar_wait(&bars->kv_full[0], 0);
       if (!ok) ATTN_FAIL(222);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        issue_dp(0);
+      }
       for (int j = 0; j < n_kv && ok && !*abort_flag; ++j) {
         const int s = j & 1;
         const uint32_t ph = j & 1;
-        if (!mbar_wait(&bars->kv_full[s], (j >> 1) & 1)) { ATTN_FAIL(223); break; }
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK + s * TILE_BYTES), v_addr = smem_u32(sV + s * TILE_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)      // S[q, key] = Q K^T
-          umma_bf16_ss(t_s, desc_kmajor(q_addr, ks), desc_kmajor(k_addr, ks), idesc_kk, ks != 0);
-        umma_commit(&bars->s_full);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)      // dP[q, key] = dO V^T
-          umma_bf16_ss(t_dp, desc_kmajor(do_addr, ks), desc_kmajor(v_addr, ks), idesc_kk, ks != 0);
-        umma_commit(&bars->dp_full);
+        const bool more = j + 1 < n_kv;
+        if (more) {
+          if (!mbar_wait(&bars->kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1) || !mbar_wait(&bars->s_taken, ph)) {
+            ATTN_FAIL(223);
+            break;
+          }
+          tc_fence_after();
+          issue_s(j + 1);
+        }
         if (!mbar_wait(&bars->ds_ready, ph)) { ATTN_FAIL(224); break; }
         tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + s * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)      // dQ[q, d] += dS[q, key] K[key, d]
-          umma_bf16_ts(t_dq, t_dp + ks * 8, desc_mnmajor(k_addr, ks), idesc_tn, (j | ks) != 0);
+          umma_bf16_ts(t_dq, t_dp + (ks >> 2) * 64 + (ks & 3) * 8, desc_mnmajor(k_addr, ks), idesc_tn, (j | ks) != 0);
         umma_commit(&bars->kv_empty[s]);
         umma_commit(&bars->acc_done);
+        if (more) issue_dp(j + 1);          // overwrites dS only after dQ above
       }
     }
   } else {
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;
+    const int half = (warp - 2) >> 2;
+    const int r = quad * 32 + lane;                        // query row inside the tile
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const int col0 = half * 64;
     const size_t stat = (static_cast<size_t>(b) * p.Hq + h) * p.S + qt * TQ + r;
     const float lse2 = p.lse[stat] * 1.4426950408889634f;
     const float dl = p.delta[stat];
@@ -619,49 +659,47 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_bwd_dq_kernel(const __gr
       const uint32_t ph = j & 1;
       if (!mbar_wait(&bars->s_full, ph)) { ATTN_FAIL(225); break; }
       tc_fence_after();
-      const bool diag = j == qt;
-      float pf[128];
+      float pf[64];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t raw[32];
-        tmem_ld_32x32(t_s + lane_base + c * 32, raw);
+        tmem_ld_32x32(t_s + lane_base + col0 + c * 32, raw);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float x = fmaf(__uint_as_float(raw[i]), p.scale_log2, -lse2);
-          pf[c * 32 + i] = ex2(x);
-        }
+        for (int i = 0; i < 32; ++i) pf[c * 32 + i] = ex2(fmaf(__uint_as_float(raw[i]), p.scale_log2, -lse2));
       }
-      if (diag) {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->s_taken);
+      if (j == qt) {                                        // diagonal tile: keys after the query
 #pragma unroll
-        for (int k = 0; k < 128; ++k)
-          if (k > r) pf[k] = 0.f;
+        for (int k = 0; k < 64; ++k)
+          if (col0 + k > r) pf[k] = 0.f;
       }
       if (!mbar_wait(&bars->dp_full, ph)) { ATTN_FAIL(226); break; }
       tc_fence_after();
-      uint32_t pk[2][32];
+      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t raw[32];
-        tmem_ld_32x32(t_dp + lane_base + c * 32, raw);
+        tmem_ld_32x32(t_dp + lane_base + col0 + c * 32, raw);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const int k = c * 32 + i;
           const float d0 = pf[k] * (__uint_as_float(raw[i]) - dl) * p.scale;
           const float d1 = pf[k + 1] * (__uint_as_float(raw[i + 1]) - dl) * p.scale;
-          pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16(d0, d1);
+          pk[k >> 1] = pack_bf16(d0, d1);
         }
       }
-      tmem_st_32x32(t_dp + lane_base, pk[0]);
-      tmem_st_32x32(t_dp + lane_base + 32, pk[1]);
+      tmem_st_32x32(t_dp + lane_base + col0, pk);          // dS pairs over the columns just read
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->ds_ready);
-      if (!mbar_wait(&bars->acc_done, ph)) { ATTN_FAIL(227); break; }
     }
-    if (!*abort_flag) {
+    if (!*abort_flag && half == 0) {
+      if (!mbar_wait(&bars->acc_done, (n_kv - 1) & 1)) ATTN_FAIL(227);
       tc_fence_after();
       const size_t token = static_cast<size_t>(row_q + r);
       __nv_bfloat16* dst = p.dq + token * p.dq_pitch + h * HD;
@@ -775,8 +813,8 @@ int b2_attention_bwd(const void* dout, const void* q, const void* k, const void*
   const long long warps = tokens * Hq;
   attn_delta_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(out), delta, B, S, Hq);
-  attn_bwd_dkv_kernel<<<dim3(S / TK, Hkv, B), ATTN_THREADS, BWD_SMEM, stream>>>(p);
-  attn_bwd_dq_kernel<<<dim3(S / TQ, Hq, B), ATTN_THREADS, BWD_SMEM, stream>>>(p);
+  attn_bwd_dkv_kernel<<<dim3(S / TK, Hkv, B), ATTN_BWD_THREADS, BWD_SMEM, stream>>>(p);
+  attn_bwd_dq_kernel<<<dim3(S / TQ, Hq, B), ATTN_BWD_THREADS, BWD_SMEM, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
