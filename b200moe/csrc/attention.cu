@@ -8,9 +8,9 @@
 // it into bf16 P in place, and P feeds the next MMA straight from TMEM (A operand in
 // tensor memory), so P never touches shared memory.
 //
-// Forward, one CTA per (128 queries, head, batch), 192 threads:
-//   warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax / correction / epilogue
-//   (one query row per thread).  Two S buffers let QK^T of tile j+1 run under the
+// Forward, one CTA per (128 queries, head, batch), 320 threads:
+//   warp 0 TMA producer, warp 1 MMA issuer, warps 2-9 softmax / correction / epilogue
+//   (two threads per query row, 64 key columns each).  Two S buffers let QK^T of tile j+1 run under the
 //   softmax of tile j; O is rescaled only when a row maximum grew by more than 2^8.
 // Backward kernels run 320 threads: two softmax groups split the 128 columns of a tile.
 // Backward dK/dV, one CTA per (128 keys, kv head, batch): loops over the 4 query heads
@@ -53,6 +53,21 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// 2^x on the FMA and integer pipes (x <= ~9): round to the nearest integer with the 1.5*2^23 trick, a degree-4
+// polynomial for the fraction in [-0.5, 0.5], and the integer part added into the exponent field.  Relative
+// error ~4e-5.  The special-function unit does 16 ex2 (and 16 bf16 packs) per clock per SM, which bounds the
+// softmax; sending part of the exponentials here relieves it.
+__device__ __forceinline__ float ex2_fma(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float poly = fmaf(0.00961813f, f, 0.0555041f);
+  poly = fmaf(poly, f, 0.240227f);
+  poly = fmaf(poly, f, 0.693147f);
+  poly = fmaf(poly, f, 1.0f);
+  return __int_as_float(__float_as_int(poly) + (__float_as_int(t) << 23));
+}
+
 // K-major operand inside a [128 x 128] tile stored as two atoms: 16-element k-step ks (0..7).
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int ks) {
   return umma_smem_desc(tile + (ks >> 2) * ATOM_BYTES + (ks & 3) * 32, 16, 1024);
@@ -76,16 +91,17 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, 
 
 // ================================================================= forward
 struct FwdBars {
-  uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], o_done;
+  uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], o_done, mx_ready;
 };
 
-__global__ void __launch_bounds__(ATTN_THREADS, 1) attn_fwd_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_fwd_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + TILE_BYTES;            // 2 stages
   uint8_t* sV = sK + 2 * TILE_BYTES;        // 2 stages
-  FwdBars* bars = reinterpret_cast<FwdBars*>(sV + 2 * TILE_BYTES);
+  float* s_rowmax = reinterpret_cast<float*>(sV + 2 * TILE_BYTES);   // [2 buffers][2 halves][128] + [2][128] sums
+  FwdBars* bars = reinterpret_cast<FwdBars*>(s_rowmax + 6 * TQ);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -105,9 +121,10 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_fwd_kernel(const __grid_
       mbar_init(&bars->k_empty[s], 1);
       mbar_init(&bars->v_empty[s], 1);
       mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->p_full[s], 4);
+      mbar_init(&bars->p_full[s], 8);
     }
     mbar_init(&bars->o_done, 1);
+    mbar_init(&bars->mx_ready, 8);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -168,43 +185,54 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_fwd_kernel(const __grid_
         const uint32_t v_addr = smem_u32(sV + s * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_bf16_ts(tmem_o, tmem + s * 128 + ks * 8, desc_mnmajor(v_addr, ks), idesc_pv, (j | ks) != 0);
+          umma_bf16_ts(tmem_o, tmem + s * 128 + (ks >> 2) * 64 + (ks & 3) * 8, desc_mnmajor(v_addr, ks), idesc_pv,
+                       (j | ks) != 0);
         umma_commit(&bars->v_empty[s]);
         umma_commit(&bars->o_done);
         if (j + 2 < n_kv && !issue_s(j + 2)) { ATTN_FAIL(204); break; }
       }
     }
   } else {
+    // Two softmax groups of four warps; group ``half`` owns key columns [64 half, 64 half + 64) of every
+    // score tile.  The two threads that share a query row exchange their partial row maxima through shared
+    // memory (one bounded mbarrier phase per tile) and keep separate partial row sums until the end.
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;                       // query row inside the tile
+    const int col0 = half * 64;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     float m_ref = -INFINITY, l = 0.f;
     for (int j = 0; j < n_kv && !*abort_flag; ++j) {
       const int s = j & 1;
       if (!mbar_wait(&bars->s_full[s], (j >> 1) & 1)) { ATTN_FAIL(206); break; }
       tc_fence_after();
-      const uint32_t ts = tmem + s * 128 + lane_base;
-      uint32_t raw[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(ts + c * 32, raw[c]);
+      const uint32_t ts = tmem + s * 128 + lane_base + col0;
+      uint32_t raw[2][32];
+      tmem_ld_32x32(ts, raw[0]);
+      tmem_ld_32x32(ts + 32, raw[1]);
       tmem_ld_wait();
-      float mx = m_ref;
       if (j == qt) {                       // diagonal tile: keys after the query are masked
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i > r) raw[c][i] = 0xff800000u;   // -inf
+            if (col0 + c * 32 + i > r) raw[c][i] = 0xff800000u;   // -inf
       }
       float mpart[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) mpart[i] = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) mpart[i & 7] = fmaxf(mpart[i & 7], __uint_as_float(raw[c][i]));
-      mx = fmaxf(mx, fmaxf(fmaxf(fmaxf(mpart[0], mpart[1]), fmaxf(mpart[2], mpart[3])),
-                           fmaxf(fmaxf(mpart[4], mpart[5]), fmaxf(mpart[6], mpart[7]))));
+      float mx = fmaxf(fmaxf(fmaxf(mpart[0], mpart[1]), fmaxf(mpart[2], mpart[3])),
+                       fmaxf(fmaxf(mpart[4], mpart[5]), fmaxf(mpart[6], mpart[7])));
+      // exchange with the thread that owns the other 64 columns of this row
+      s_rowmax[(s * 2 + half) * TQ + r] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->mx_ready);
+      if (!mbar_wait(&bars->mx_ready, j & 1)) { ATTN_FAIL(209); break; }
+      mx = fmaxf(fmaxf(mx, s_rowmax[(s * 2 + (half ^ 1)) * TQ + r]), m_ref);
       const bool need = (mx - m_ref) * p.scale_log2 > 8.f;      // also true on the first tile (m_ref = -inf)
       const bool any = __any_sync(0xffffffffu, need);
       float alpha = 1.f;
@@ -213,35 +241,36 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_fwd_kernel(const __grid_
         m_ref = mx;
       }
       const float neg = -m_ref * p.scale_log2;
-      float part[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // independent partial sums: no 128-long add chain
-      uint32_t packed[2][32];
+      float part[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // independent partial sums: no long add chain
+      uint32_t packed[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const float x0 = fmaf(__uint_as_float(raw[c][i]), p.scale_log2, neg);
           const float x1 = fmaf(__uint_as_float(raw[c][i + 1]), p.scale_log2, neg);
-          const float p0 = ex2(x0), p1 = ex2(x1);
+          const bool fma_path = ((i >> 1) & 1) != 0;          // every second pair goes to the FMA pipe
+          const float p0 = fma_path ? ex2_fma(x0) : ex2(x0);
+          const float p1 = fma_path ? ex2_fma(x1) : ex2(x1);
           part[(i >> 1) & 7] += p0 + p1;
-          packed[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16(p0, p1);
+          packed[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
         }
       const float sum = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
       l = l * alpha + sum;
-      // P (bf16 pairs) overwrites the first 64 columns of this S buffer
-      tmem_st_32x32(ts, packed[0]);
-      tmem_st_32x32(ts + 32, packed[1]);
+      // P (bf16 pairs) overwrites the first 32 of the 64 columns this thread has just read
+      tmem_st_32x32(ts, packed);
       if (j > 0) {
         if (!mbar_wait(&bars->o_done, (j - 1) & 1)) { ATTN_FAIL(207); break; }
         tc_fence_after();
         if (any) {
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t o[32];
-            tmem_ld_32x32(tmem_o + lane_base + c * 32, o);
+            tmem_ld_32x32(tmem_o + lane_base + col0 + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x32(tmem_o + lane_base + c * 32, o);
+            tmem_st_32x32(tmem_o + lane_base + col0 + c * 32, o);
           }
         }
       }
@@ -250,17 +279,22 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_fwd_kernel(const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full[s]);
     }
-    // epilogue
+    // epilogue: combine the two partial row sums, normalise, store this thread's 64 output columns
     if (!*abort_flag) {
+      s_rowmax[(4 + half) * TQ + r] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->mx_ready);
+      if (!mbar_wait(&bars->mx_ready, n_kv & 1)) ATTN_FAIL(210);
+      l += s_rowmax[(4 + (half ^ 1)) * TQ + r];
       if (!mbar_wait(&bars->o_done, (n_kv - 1) & 1)) ATTN_FAIL(208);
       tc_fence_after();
       const float inv = 1.f / l;
       const size_t token = static_cast<size_t>(row_q + r);
-      __nv_bfloat16* dst = p.out + (token * p.Hq + h) * HD;
+      __nv_bfloat16* dst = p.out + (token * p.Hq + h) * HD + col0;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t o[32];
-        tmem_ld_32x32(tmem_o + lane_base + c * 32, o);
+        tmem_ld_32x32(tmem_o + lane_base + col0 + c * 32, o);
         tmem_ld_wait();
         uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
 #pragma unroll
@@ -270,7 +304,7 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_fwd_kernel(const __grid_
                              pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv),
                              pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv));
       }
-      p.lse[(static_cast<size_t>(b) * p.Hq + h) * p.S + qt * TQ + r] = m_ref * p.scale + logf(l);
+      if (half == 0) p.lse[(static_cast<size_t>(b) * p.Hq + h) * p.S + qt * TQ + r] = m_ref * p.scale + logf(l);
     }
   }
   tc_fence_before();
@@ -756,7 +790,7 @@ static int attn_map(CUtensorMap* map, const void* base, long long tokens, int he
              : -2;
 }
 
-constexpr int FWD_SMEM = 5 * TILE_BYTES + 1024 + 512;
+constexpr int FWD_SMEM = 5 * TILE_BYTES + 1024 + 6 * TQ * 4 + 512;
 constexpr int BWD_SMEM = 6 * TILE_BYTES + 1024 + 512;
 
 }  // namespace b2
@@ -783,7 +817,7 @@ int b2_attention_fwd(const void* q, const void* k, const void* v, long long q_pi
       return -3;
     set = true;
   }
-  attn_fwd_kernel<<<dim3(S / TQ, Hq, B), ATTN_THREADS, FWD_SMEM, stream>>>(p);
+  attn_fwd_kernel<<<dim3(S / TQ, Hq, B), ATTN_BWD_THREADS, FWD_SMEM, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
