@@ -9,7 +9,7 @@ Times, with CUDA events on each rank and the maximum over ranks:
     peer-copy bandwidth per direction);
   * the replica all-reduce kernels (one-shot, two-shot, NVLS) against ``dist.all_reduce`` at several sizes;
   * the FSDP end-of-step kernel (reduce-scatter + AdamW + all-gather) against the NCCL + separate-kernel sequence.
-Rank 0 prints one JSON line per measurement and writes them to ``gpurun_out/comm_N.json``.
+Rank 0 prints one JSON line per measurement and writes them to ``$B200MOE_BENCH_OUT/comm_N.json`` (default: the current directory).
 """
 import argparse
 import json
@@ -20,6 +20,7 @@ import torch
 import torch.distributed as dist
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+OUT_DIR = os.environ.get("B200MOE_BENCH_OUT", os.getcwd())
 sys.path.insert(0, ROOT)
 NVLINK_GBS = 770.0
 
@@ -132,8 +133,8 @@ def main():
             emit(case="allreduce NCCL", floats=n, ms=round(ms, 4), busbw_gbs=round(2 * (world - 1) / world * n * 4 / ms / 1e6, 1))
     native.check_status()
     if rank == 0:
-        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-        with open(os.path.join(ROOT, "gpurun_out", f"comm_{world}.json"), "w") as f:
+        os.makedirs(OUT_DIR, exist_ok=True)
+        with open(os.path.join(OUT_DIR, f"comm_{world}.json"), "w") as f:
             json.dump(rows, f, indent=1)
     dist.destroy_process_group()
 

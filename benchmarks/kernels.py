@@ -13,6 +13,7 @@ import sys
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+OUT_DIR = os.environ.get("B200MOE_BENCH_OUT", os.getcwd())
 sys.path.insert(0, ROOT)
 
 from b200moe.ops import native  # noqa: E402
@@ -139,8 +140,8 @@ def main():
     bw_case("moe_gather 32768x4096", 2 * R * D * 2, lambda: native.moe_gather(x, row_slot, meta, cap))
     wts = torch.rand(T, 2, device="cuda")
     bw_case("moe_combine 16384x4096", 3 * T * D * 2, lambda: native.moe_combine(xp, slot_row, wts, T))
-    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    with open(os.path.join(ROOT, "gpurun_out", f"kernels_mode{args.tile_mode}.json"), "w") as f:
+    os.makedirs(OUT_DIR, exist_ok=True)
+    with open(os.path.join(OUT_DIR, f"kernels_mode{args.tile_mode}.json"), "w") as f:
         json.dump(rows, f, indent=1)
 
 

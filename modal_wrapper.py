@@ -18,7 +18,7 @@ import yaml
 
 APP_NAME = "b200moe-train"
 GPU_SPEC = os.environ.get("B200MOE_MODAL_GPU", "B200:8")
-REMOTE_ROOT = "/root/b200moe"
+REMOTE_ROOT = "/workspace/b200moe"
 VOLUMES = {"/mnt/dataset": "b200moe-datasets", "/mnt/checkpoints": "b200moe-checkpoints",
            "/mnt/profile-data": "b200moe-profiles"}
 
