@@ -53,21 +53,6 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// 2^x on the FMA and integer pipes (x <= ~9): round to the nearest integer with the 1.5*2^23 trick, a degree-4
-// polynomial for the fraction in [-0.5, 0.5], and the integer part added into the exponent field.  Relative
-// error ~4e-5.  The special-function unit does 16 ex2 (and 16 bf16 packs) per clock per SM, which bounds the
-// softmax; sending part of the exponentials here relieves it.
-__device__ __forceinline__ float ex2_fma(float x) {
-  x = fmaxf(x, -125.f);
-  const float t = x + 12582912.f;
-  const float f = x - (t - 12582912.f);
-  float poly = fmaf(0.00961813f, f, 0.0555041f);
-  poly = fmaf(poly, f, 0.240227f);
-  poly = fmaf(poly, f, 0.693147f);
-  poly = fmaf(poly, f, 1.0f);
-  return __int_as_float(__float_as_int(poly) + (__float_as_int(t) << 23));
-}
-
 // K-major operand inside a [128 x 128] tile stored as two atoms: 16-element k-step ks (0..7).
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int ks) {
   return umma_smem_desc(tile + (ks >> 2) * ATOM_BYTES + (ks & 3) * 32, 16, 1024);
@@ -249,9 +234,7 @@ __global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_fwd_kernel(const __g
         for (int i = 0; i < 32; i += 2) {
           const float x0 = fmaf(__uint_as_float(raw[c][i]), p.scale_log2, neg);
           const float x1 = fmaf(__uint_as_float(raw[c][i + 1]), p.scale_log2, neg);
-          const bool fma_path = ((i >> 1) & 1) != 0;          // every second pair goes to the FMA pipe
-          const float p0 = fma_path ? ex2_fma(x0) : ex2(x0);
-          const float p1 = fma_path ? ex2_fma(x1) : ex2(x1);
+          const float p0 = ex2(x0), p1 = ex2(x1);
           part[(i >> 1) & 7] += p0 + p1;
           packed[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
         }
