@@ -455,17 +455,19 @@ static int launch_mt(const GemmParams& p, int sms, cudaStream_t stream) {
 static int g_tile_mode = 0;   // 0 auto, 1 force 128x256, 2 force 256x256 where legal
 
 // 256x256 tiles need whole 256-row tiles of one expert (the caller says whether its segments are padded to
-// 256 rows) and enough tiles to fill the machine.  Grouped weight gradients stay on 128x256: their K extent per
-// expert is short, so losing the epilogue/main-loop overlap costs more than the operand traffic saves.
+// 256 rows), enough tiles to fill the machine and a long K: with a short K, losing the epilogue/main-loop
+// overlap costs more than the operand traffic saves.
 template <int A_MN, int B_MN, int EPI, int SCHED>
 static int launch(const GemmParams& p, int sms, cudaStream_t stream) {
-  const bool legal = SCHED == SCHED_FLAT &&
+  // grouped weight gradients: K is the row count of one expert, known to the host only on average
+  const long long k_eff = SCHED == SCHED_WGRAD ? p.K / (p.num_experts > 0 ? p.num_experts : 1) : p.K;
+  const bool legal = SCHED == SCHED_WGRAD ||
                      (p.tile_expert == nullptr ? p.num_m_tiles == nullptr : p.group_align256 != 0);
   const long long tiles256 = static_cast<long long>((p.M + 255) / 256) * ((p.N + BN - 1) / BN) *
                              (SCHED == SCHED_WGRAD ? p.num_experts : 1);
   // measured: 256x256 wins from K ~ 6144 up (+14 % at K = 14336 and 28672); at K = 4096 the exposed epilogue
   // costs more than the operand traffic saves
-  const bool big = g_tile_mode == 2 || (g_tile_mode == 0 && tiles256 >= 2LL * sms && p.K >= 6144);
+  const bool big = g_tile_mode == 2 || (g_tile_mode == 0 && tiles256 >= 2LL * sms && k_eff >= 6144);
   if (legal && big) return launch_mt<A_MN, B_MN, EPI, SCHED, 2>(p, sms, stream);
   return launch_mt<A_MN, B_MN, EPI, SCHED, 1>(p, sms, stream);
 }

@@ -111,7 +111,8 @@ def run_config(args):
             "microbatches": args.microbatches, "seq": args.seq, "experts_per_rank": MODEL["experts"] // fsdp}
 
 
-def init_dist(args):
+def init_dist(args, timeout_s=None):
+    import datetime
     import torch
     import torch.distributed as dist
     rank = int(os.environ.get("RANK", "0"))
@@ -123,7 +124,8 @@ def init_dist(args):
     os.environ.setdefault("MASTER_PORT", "29511")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    extra = {"timeout": datetime.timedelta(seconds=timeout_s)} if timeout_s else {}
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device, **extra)
     return rank, world, local, device
 
 
@@ -300,7 +302,7 @@ def bench_reference(args):
         import numpy as np
         import torch
         import torch.distributed as dist
-        rank, world, local, device = init_dist(args)
+        rank, world, local, device = init_dist(args, timeout_s=240)   # a rank that dies ends the others quickly
         from implementation.distributed.ddp_modules import FSDPWrapperPipelined
         from implementation.layers import TransformerLMPipelined
         from implementation.nnfunctions import cross_entropy
@@ -363,8 +365,11 @@ def bench_reference(args):
         dist.destroy_process_group()
     except Exception as error:  # report instead of failing the driver's run
         reason = f"{type(error).__name__}: {str(error).splitlines()[0][:300] if str(error) else ''}"
-        if int(os.environ.get("RANK", "0")) == 0:
-            print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
+        rank = int(os.environ.get("RANK", "0"))
+        print(f"[reference arm, rank {rank}] {reason}", file=sys.stderr, flush=True)
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": reason, "n_gpus": args.gpus}), flush=True)
+        os._exit(0)      # do not wait in collective teardown for ranks that are gone
 
 
 if __name__ == "__main__":

@@ -51,12 +51,13 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--compare", action="store_true", help="also time the PyTorch library op")
+    ap.add_argument("--experts", type=int, default=8, help="local experts of the grouped cases")
     ap.add_argument("--tile-mode", type=int, default=0, help="GEMM CTA tile: 0 auto, 1 128x256, 2 256x256")
     args = ap.parse_args()
     native.require()
     native.set_gemm_tile_mode(args.tile_mode)
     tf_peak, bw_peak, tag = peaks()
-    T, D, Fd, E = args.tokens, 4096, 14336, 8
+    T, D, Fd, E = args.tokens, 4096, 14336, args.experts
     rows = []
 
     def gemm_case(name, flops, fn, ref=None):
