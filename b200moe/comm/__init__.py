@@ -112,7 +112,9 @@ class Comm:
         self.status = native.status_word(device)
         self.fsdp = GroupComm(mesh.group("fsdp"), device) if mesh.fsdp > 1 else None
         self.ddp = GroupComm(mesh.group("ddp"), device) if mesh.ddp > 1 else None
-        self.capacity_mode = "exact"
+        import os
+        self.capacity_mode = os.environ.get("B200MOE_EP_CAPACITY", "exact")
+        self.capacity_bucket = int(os.environ.get("B200MOE_EP_BUCKET", "4096"))
         self._symm = {}
         self._ep = {}
         self._ar_stage = {}
@@ -288,7 +290,8 @@ class EPContext:
     def _sized(self, needed: int, factor: float | None = None) -> int:
         factor = self.capacity_factor if factor is None else factor
         want = int(needed * factor) + (self.e_local * 256 if factor > 1.0 else 0)
-        return min(self.cap, (want + 1023) // 1024 * 1024)
+        bucket = self.comm.capacity_bucket
+        return min(self.cap, (want + bucket - 1) // bucket * bucket)
 
     def _capacity_for(self, key):
         """Capacity from the layer's previous call, or ``None`` when no readback has
