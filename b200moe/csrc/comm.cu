@@ -201,7 +201,19 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const EpPushArgs a) {
     if (dest < 0 || row < 0 || row >= a.dest_capacity) continue;   // padding rows / overflow are not sent
     const __nv_bfloat16* src = a.src + static_cast<size_t>(i >> a.src_shift) * a.D;
     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.land.ptr[dest]) + static_cast<size_t>(row) * a.D;
-    for (int c = lane * 8; c < a.D; c += 256) *reinterpret_cast<vec16*>(dst + c) = *reinterpret_cast<const vec16*>(src + c);
+    // four 16-byte loads in flight per lane before the (possibly remote) stores
+    int c = lane * 8;
+    for (; c + 768 < a.D; c += 1024) {
+      const vec16 v0 = *reinterpret_cast<const vec16*>(src + c);
+      const vec16 v1 = *reinterpret_cast<const vec16*>(src + c + 256);
+      const vec16 v2 = *reinterpret_cast<const vec16*>(src + c + 512);
+      const vec16 v3 = *reinterpret_cast<const vec16*>(src + c + 768);
+      *reinterpret_cast<vec16*>(dst + c) = v0;
+      *reinterpret_cast<vec16*>(dst + c + 256) = v1;
+      *reinterpret_cast<vec16*>(dst + c + 512) = v2;
+      *reinterpret_cast<vec16*>(dst + c + 768) = v3;
+    }
+    for (; c < a.D; c += 256) *reinterpret_cast<vec16*>(dst + c) = *reinterpret_cast<const vec16*>(src + c);
     if (lane == 0) {
       if (a.tag_of) static_cast<int*>(a.land_tag.ptr[dest])[row] = a.tag_of[i];
       if (a.land_src.ptr[0]) static_cast<int*>(a.land_src.ptr[dest])[row] = a.rank;
@@ -511,7 +523,7 @@ int b2_ep_push(const void* src, const int* row_of, const int* dest_of, const int
   a.dest_capacity = dest_capacity; a.rank = rank; a.n = n; a.seq = seq; a.sig_slot = sig_slot;
   a.land = table(land); a.land_tag = table(land_tag); a.land_src = table(land_src);
   a.land_scalar = table(land_scalar); a.sig = table(sig); a.counter = counter;
-  ep_push_kernel<<<148 * 4, 256, 0, s>>>(a);
+  ep_push_kernel<<<148 * 8, 256, 0, s>>>(a);
   return launched();
 }
 

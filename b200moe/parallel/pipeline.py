@@ -19,6 +19,8 @@ fused reduce-scatter/AdamW/all-gather kernel (``fused_optimizer_step``).
 from __future__ import annotations
 
 import collections
+import os
+import time
 
 import torch
 import torch.distributed as dist
@@ -99,6 +101,23 @@ def pipelined_train_overlap(model, optimizer, x, x_label, x_spec: list[int], spl
     model.clear_grad_accumulators()
     forward_count = 0
 
+    timing = os.environ.get("B200MOE_PIPELINE_TIMING") == "1" and torch.cuda.is_available()
+    spans, host = [], {"fwd": 0.0, "bwd": 0.0, "xchg": 0.0}
+
+    def timed(kind, fn, *args):
+        """Optional instrumentation: device time of each forward/backward (CUDA events) and host time spent
+        issuing it; printed per rank at the end of the step."""
+        if not timing:
+            return fn(*args)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        begin.record()
+        out = fn(*args)
+        end.record()
+        host[kind] += time.perf_counter() - t0
+        spans.append((kind, begin, end))
+        return out
+
     def forward_microbatch(x_in):
         nonlocal forward_count
         if not first:
@@ -131,22 +150,23 @@ def pipelined_train_overlap(model, optimizer, x, x_label, x_spec: list[int], spl
 
     warmup = min(stages - pipeline_stage_this - 1, split_num)
     steady = split_num - warmup
+    step_t0 = time.perf_counter()
     for i in range(warmup):
         x_in = data_chunks[i] if first else link.exchange(receive=True, downstream=False)
-        link.exchange(send_tensor=forward_microbatch(x_in))
+        link.exchange(send_tensor=timed("fwd", forward_microbatch, x_in))
     if steady:
         x_in = data_chunks[warmup] if first else link.exchange(receive=True, downstream=False)
     for i in range(steady):
-        out = forward_microbatch(x_in)
+        out = timed("fwd", forward_microbatch, x_in)
         grad = None if last else link.exchange(send_tensor=out, receive=True)
-        input_grad = backward_microbatch(grad)
+        input_grad = timed("bwd", backward_microbatch, grad)
         more = i + 1 < steady
         if not first:
             x_in = link.exchange(send_tensor=input_grad, receive=more, downstream=False)
         elif more:
             x_in = data_chunks[warmup + i + 1]
     for _ in range(steady, split_num):
-        input_grad = backward_microbatch(link.exchange(receive=True))
+        input_grad = timed("bwd", backward_microbatch, link.exchange(receive=True))
         if not first:
             link.exchange(send_tensor=input_grad, downstream=False)
 
@@ -157,6 +177,15 @@ def pipelined_train_overlap(model, optimizer, x, x_label, x_spec: list[int], spl
         refresh = getattr(model, "after_optimizer_step", None)
         if refresh is not None:
             refresh()
+    if timing:
+        torch.cuda.synchronize()
+        total = {"fwd": 0.0, "bwd": 0.0}
+        for kind, begin, end in spans:
+            total[kind] += begin.elapsed_time(end)
+        print(f"[pipeline timing] rank {dist.get_rank() if dist.is_initialized() else 0} stage {pipeline_stage_this}: "
+              f"device fwd {total['fwd']:.0f} ms, bwd {total['bwd']:.0f} ms over {split_num} microbatches; "
+              f"host issue fwd {host['fwd'] * 1e3:.0f} ms, bwd {host['bwd'] * 1e3:.0f} ms; "
+              f"step wall {(time.perf_counter() - step_t0) * 1e3:.0f} ms", flush=True)
     if return_metrics:
         return router_loss_metrics(loss_total, aux_total, router_aux_loss_coef, pp_group, dp_group)
     return loss_total

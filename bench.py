@@ -282,9 +282,19 @@ def bench_b200moe(args):
     dist.all_reduce(loss, op=dist.ReduceOp.MAX)
     peak = torch.tensor([torch.cuda.max_memory_allocated() / 2 ** 30], device=device)
     dist.all_reduce(peak, op=dist.ReduceOp.MAX)
+    # expert load of the last microbatch: rows the busiest rank of any layer had to process, relative to a
+    # perfectly balanced split (random-init routers collapse with depth, which slows the deeper stages)
+    worst_rows = 0
+    if comm is not None:
+        for ctx in comm._ep.values():
+            for hint in ctx._hints.values():
+                worst_rows = max(worst_rows, int(hint[0][3]) / ctx.slots)
+    load = torch.tensor([float(worst_rows)], device=device)
+    dist.all_reduce(load, op=dist.ReduceOp.MAX)
     if rank == 0:
         report(args, cfg, device_ms, e2e_ms, clocks, launches, float(loss), stager.h2d_bytes if edge else 0, 4,
                "b200moe", {"peak_mem_gib": float(peak), "activation_recompute": recompute,
+                           "ep_max_rows_over_balanced": round(float(load), 3),
                            "comm_backend": "fused" if comm is not None else "nccl",
                            "native_ops": native.available_ops()})
     dist.destroy_process_group()
