@@ -38,6 +38,7 @@ _U64x8 = ctypes.c_ulonglong * MAX_RANKS
 SIG_EP_COUNTS, SIG_EP_FWD_DATA, SIG_EP_FWD_RET, SIG_EP_BWD_DATA, SIG_EP_BWD_RET = 0, 1, 2, 3, 4
 SIG_FSDP = 8      # +1
 SIG_AR = 12       # +1
+SIG_AG_GEMM = 14
 NUM_SLOTS = 32
 
 
@@ -118,6 +119,7 @@ class Comm:
         self._symm = {}
         self._ep = {}
         self._ar_stage = {}
+        self._ag_state = {}
         self._entries = {}
 
     # -- allocation ----------------------------------------------------------------------
@@ -166,6 +168,47 @@ class Comm:
         """AdamW on the owned shards and push of the new bf16 weights to every rank;
         with ``reduce`` the gradient reduce-scatter happens in the same kernel."""
         self._fsdp_launch(flat, 1 if reduce else 2, lr, beta1, beta2, eps, wd, a_t)
+
+    # -- all-gather fused with the consuming GEMM ---------------------------------------------
+    def _locate(self, tensor):
+        """Symmetric buffer that contains ``tensor`` and the byte offset of the tensor inside it."""
+        addr = tensor.data_ptr()
+        for buf in self._symm.values():
+            base = buf.tensor.data_ptr()
+            if base <= addr < base + buf.tensor.numel() * buf.tensor.element_size():
+                return buf, addr - base
+        raise KeyError("tensor does not live in a symmetric buffer of this Comm")
+
+    def allgather_gemm(self, x, w):
+        """``x [M,K] @ w [N,K]ᵀ`` for a weight that is row-sharded over the FSDP group: ``w`` is this rank's
+        full-size copy inside a symmetric flat buffer (``alloc_flat``) in which only the own rows
+        ``[rank·N/n, (rank+1)·N/n)`` need to be current.  One kernel pulls the other rows from the peers and
+        multiplies; afterwards all of ``w`` is current on this rank.  A rank must not rewrite its rows before the
+        group has synchronised again (the end-of-step kernel does).  Takes the place of the reference's
+        per-module ``all_gather_into_tensor`` + einsum (implementation/distributed/ddp_modules.py:24-49)."""
+        g = self.fsdp
+        if g is None:
+            return native.gemm_nt(x, w)
+        N, K = w.shape
+        if not w.is_contiguous() or N % g.world:
+            raise ValueError("weight must be contiguous with rows divisible by the group size")
+        buf, off = self._locate(w)
+        ptrs = _U64x8(*[(buf.ptrs[r] + off) if r < g.world else 0 for r in range(MAX_RANKS)])
+        key = ("ag", w.data_ptr(), N, K)
+        state = self._ag_state.get(key)
+        if state is None:
+            state = {"flags": torch.zeros((N + 255) // 256, dtype=torch.int32, device=self.device), "epoch": 0}
+            self._ag_state[key] = state
+        state["epoch"] += 1
+        seq = g.next_seq(SIG_AG_GEMM)
+        y = native.ag_gemm_nt(x, ptrs, N, N // g.world, g.world, g.rank, g.sig.table(), SIG_AG_GEMM, seq,
+                              state["flags"], state["epoch"])
+        if y is None:      # no cooperative launch on this device: gather with NCCL, multiply
+            state["epoch"] -= 1
+            shard = N // g.world
+            dist.all_gather_into_tensor(w, w[g.rank * shard:(g.rank + 1) * shard].clone(), group=g.group)
+            return native.gemm_nt(x, w)
+        return y
 
     # -- replica all-reduce -----------------------------------------------------------------
     ONE_SHOT_MAX = 1 << 18      # floats: below 1 MiB latency dominates, every rank reads everything

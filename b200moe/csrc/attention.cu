@@ -35,6 +35,7 @@ constexpr int ATTN_BWD_THREADS = 320;   // TMA warp, MMA warp, two softmax group
 struct AttnParams {
   CUtensorMap map_q, map_k, map_v, map_do;
   int B, S, Hq, Hkv;
+  int causal;             // 1: keys after the query are masked; 0: every query sees every key
   float scale;            // 1/sqrt(head_dim)
   float scale_log2;       // scale * log2(e)
   __nv_bfloat16* out;     // forward: [B,S,Hq,128] contiguous
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_fwd_kernel(const __g
   const int qt = q_tiles - 1 - blockIdx.x;      // long tiles first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
-  const int n_kv = qt + 1;
+  const int n_kv = p.causal ? qt + 1 : q_tiles;
   const int row_q = b * p.S + qt * TQ;
 
   if (threadIdx.x == 0) {
@@ -196,7 +197,7 @@ __global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_fwd_kernel(const __g
       tmem_ld_32x32(ts, raw[0]);
       tmem_ld_32x32(ts + 32, raw[1]);
       tmem_ld_wait();
-      if (j == qt) {                       // diagonal tile: keys after the query are masked
+      if (p.causal && j == qt) {                       // diagonal tile: keys after the query are masked
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
@@ -348,7 +349,8 @@ __global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_bwd_dkv_kernel(const
   const int q_tiles = p.S / TQ;
   const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int group = p.Hq / p.Hkv;
-  const int per_head = q_tiles - kt;               // causal: query tiles kt .. q_tiles-1
+  const int q_first = p.causal ? kt : 0;           // causal: query tiles kt .. q_tiles-1
+  const int per_head = q_tiles - q_first;
   const int iters = group * per_head;
   const int row_k = b * p.S + kt * TK;
 
@@ -384,7 +386,7 @@ __global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_bwd_dkv_kernel(const
       for (int it = 0; it < iters && !*abort_flag; ++it) {
         const int s = it & 1;
         const int hq = hk * group + it / per_head;
-        const int qi = kt + it % per_head;
+        const int qi = q_first + it % per_head;
         const int row_q = b * p.S + qi * TQ;
         if (!mbar_wait(&bars->qd_empty[s], ((it >> 1) & 1) ^ 1)) { ATTN_FAIL(211); break; }
         mbar_expect_tx(&bars->qd_full[s], 2 * TILE_BYTES);
@@ -451,7 +453,7 @@ __global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_bwd_dkv_kernel(const
     const int col0 = half * 64;
     for (int it = 0; it < iters && !*abort_flag; ++it) {
       const int hq = hk * group + it / per_head;
-      const int qi = kt + it % per_head;
+      const int qi = q_first + it % per_head;
       const uint32_t ph = it & 1;
       const size_t stat = (static_cast<size_t>(b) * p.Hq + hq) * p.S + qi * TQ + col0;
       // statistics of my 64 query columns: lane i keeps those of columns 32c + i and the warp shuffles them
@@ -463,7 +465,7 @@ __global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_bwd_dkv_kernel(const
       }
       if (!mbar_wait(&bars->st_full, ph)) { ATTN_FAIL(216); break; }
       tc_fence_after();
-      const bool diag = qi == kt;
+      const bool diag = p.causal && qi == kt;
       uint32_t pk[32];
       float pf[64];
 #pragma unroll
@@ -573,7 +575,7 @@ __global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_bwd_dq_kernel(const 
   const int qt = q_tiles - 1 - blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
-  const int n_kv = qt + 1;
+  const int n_kv = p.causal ? qt + 1 : q_tiles;
   const int row_q = b * p.S + qt * TQ;
 
   if (threadIdx.x == 0) {
@@ -688,7 +690,7 @@ __global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_bwd_dq_kernel(const 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_taken);
-      if (j == qt) {                                        // diagonal tile: keys after the query
+      if (p.causal && j == qt) {                                        // diagonal tile: keys after the query
 #pragma unroll
         for (int k = 0; k < 64; ++k)
           if (col0 + k > r) pf[k] = 0.f;
@@ -783,9 +785,9 @@ using namespace b2;
 extern "C" {
 
 // q: [B,S,Hq,128], k, v: [B,S,Hkv,128] bf16 with token pitches (elements); out [B,S,Hq,128] contiguous; lse [B,Hq,S].
-int b2_attention_fwd(const void* q, const void* k, const void* v, long long q_pitch, long long k_pitch,
-                     long long v_pitch, void* out, float* lse, int B, int S, int Hq, int Hkv, float scale, int* status,
-                     cudaStream_t stream) {
+int b2_attention_fwd_ex(const void* q, const void* k, const void* v, long long q_pitch, long long k_pitch,
+                        long long v_pitch, void* out, float* lse, int B, int S, int Hq, int Hkv, float scale,
+                        int causal, int* status, cudaStream_t stream) {
   if (S % 128 || Hq % Hkv || q_pitch % 8 || k_pitch % 8 || v_pitch % 8) return -10;
   AttnParams p{};
   const long long tokens = static_cast<long long>(B) * S;
@@ -793,6 +795,7 @@ int b2_attention_fwd(const void* q, const void* k, const void* v, long long q_pi
       attn_map(&p.map_v, v, tokens, Hkv, v_pitch))
     return -11;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal != 0;
   p.out = static_cast<__nv_bfloat16*>(out); p.lse = lse; p.status = status;
   static bool set = false;
   if (!set) {
@@ -804,12 +807,19 @@ int b2_attention_fwd(const void* q, const void* k, const void* v, long long q_pi
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+// Causal form (the one the model uses).
+int b2_attention_fwd(const void* q, const void* k, const void* v, long long q_pitch, long long k_pitch,
+                     long long v_pitch, void* out, float* lse, int B, int S, int Hq, int Hkv, float scale, int* status,
+                     cudaStream_t stream) {
+  return b2_attention_fwd_ex(q, k, v, q_pitch, k_pitch, v_pitch, out, lse, B, S, Hq, Hkv, scale, 1, status, stream);
+}
+
 // dout, out: [B,S,Hq,128] contiguous; delta: fp32 [B,Hq,S] scratch; dq [B,S,Hq,128], dk, dv [B,S,Hkv,128] with
 // token pitches dq_pitch, dk_pitch, dv_pitch (they may be views into one fused gradient buffer).
-int b2_attention_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse,
-                     long long q_pitch, long long k_pitch, long long v_pitch, float* delta, void* dq, void* dk,
-                     void* dv, long long dq_pitch, long long dk_pitch, long long dv_pitch, int B, int S, int Hq,
-                     int Hkv, float scale, int* status, cudaStream_t stream) {
+int b2_attention_bwd_ex(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                        const float* lse, long long q_pitch, long long k_pitch, long long v_pitch, float* delta,
+                        void* dq, void* dk, void* dv, long long dq_pitch, long long dk_pitch, long long dv_pitch,
+                        int B, int S, int Hq, int Hkv, float scale, int causal, int* status, cudaStream_t stream) {
   if (S % 128 || Hq % Hkv) return -10;
   AttnParams p{};
   const long long tokens = static_cast<long long>(B) * S;
@@ -817,6 +827,7 @@ int b2_attention_bwd(const void* dout, const void* q, const void* k, const void*
       attn_map(&p.map_v, v, tokens, Hkv, v_pitch) || attn_map(&p.map_do, dout, tokens, Hq, static_cast<long long>(Hq) * HD))
     return -11;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal != 0;
   p.lse = const_cast<float*>(lse); p.delta = delta; p.dq = static_cast<__nv_bfloat16*>(dq);
   p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv); p.status = status;
   p.dq_pitch = dq_pitch; p.dk_pitch = dk_pitch; p.dv_pitch = dv_pitch;
@@ -833,6 +844,14 @@ int b2_attention_bwd(const void* dout, const void* q, const void* k, const void*
   attn_bwd_dkv_kernel<<<dim3(S / TK, Hkv, B), ATTN_BWD_THREADS, BWD_SMEM, stream>>>(p);
   attn_bwd_dq_kernel<<<dim3(S / TQ, Hq, B), ATTN_BWD_THREADS, BWD_SMEM, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int b2_attention_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse,
+                     long long q_pitch, long long k_pitch, long long v_pitch, float* delta, void* dq, void* dk,
+                     void* dv, long long dq_pitch, long long dk_pitch, long long dv_pitch, int B, int S, int Hq,
+                     int Hkv, float scale, int* status, cudaStream_t stream) {
+  return b2_attention_bwd_ex(dout, q, k, v, out, lse, q_pitch, k_pitch, v_pitch, delta, dq, dk, dv, dq_pitch, dk_pitch,
+                             dv_pitch, B, S, Hq, Hkv, scale, 1, status, stream);
 }
 
 }  // extern "C"

@@ -122,3 +122,54 @@ def rope_attention(q, k, v, cos, sin):
         out = F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, enable_gqa=True)
         return out.transpose(1, 2)
     return Fn.attention_ref(q, k, v, cos, sin, causal=True)
+
+
+class _PlainAttention(torch.autograd.Function):
+    """Attention without rotation, causal or not, on ``[B, S, H, 128]`` bf16 tensors (tcgen05 kernels)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal):
+        out, lse, _, _ = _native().attention_fwd(q, k, v, None, None, causal=causal)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.causal = causal
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = _native().attention_bwd(dout, q, k, v, out, lse, causal=ctx.causal)
+        return dq, dk, dv, None
+
+
+def _native_shape_ok(q, k) -> bool:
+    from . import use_native
+    return (use_native(q, "attention") and q.dtype == torch.bfloat16 and q.shape[-1] == 128
+            and q.shape[1] % 128 == 0 and k.shape[1] == q.shape[1])
+
+
+def attention(q, k, v, causal: bool = True):
+    """Differentiable attention on ``[B, S, H, hd]`` tensors (``Hq`` a multiple of ``Hkv``); no rotation.  Runs the
+    tcgen05 kernels for bf16, head_dim 128, ``S % 128 == 0`` on a GPU and the PyTorch formula otherwise."""
+    if _native_shape_ok(q, k):
+        return _PlainAttention.apply(q, k, v, bool(causal))
+    return Fn.attention_ref(q, k, v, causal=causal)
+
+
+def flash_attention_forward(q, k, v, causal: bool = False):
+    """Forward-only multi-head attention on contiguous ``[B, H, S, head_dim]`` tensors, non-causal by default: the
+    entry point of the reference's hand-written kernel (implementation/kernels/flash_attention.cu:390-448, fp16,
+    ``mma.sync``/``wmma``, 32 queries per CTA).  Here every (batch, head) pair is a batch entry of the tcgen05
+    forward kernel with one head — ``[B, H, S, 128]`` is read in place as ``[B·H, S, 1, 128]`` — so no transposed
+    copy is made.  fp16 inputs are computed in bf16 and returned as fp16; shapes the kernel does not cover
+    (head_dim ≠ 128, ``S % 128 ≠ 0``, CPU) take the PyTorch formula, like the reference's scalar fallback kernel."""
+    B, H, S, hd = q.shape
+    want = q.dtype
+    if q.is_cuda and want in (torch.float16, torch.bfloat16):
+        q, k, v = (t.to(torch.bfloat16).contiguous().view(B * H, S, 1, hd) for t in (q, k, v))
+        if _native_shape_ok(q, k):
+            with torch.no_grad():
+                out, _, _, _ = _native().attention_fwd(q, k, v, None, None, causal=causal)
+            return out.view(B, H, S, hd).to(want)
+        q, k, v = (t.view(B, H, S, hd) for t in (q, k, v))
+    with torch.no_grad():
+        return F.scaled_dot_product_attention(q.float(), k.float(), v.float(), is_causal=causal).to(want)

@@ -294,6 +294,35 @@ def rope_inplace(buf, first_elem_offset, tokens, seq, heads, head_dim, pitch, co
     _call("b2_rope", ptr, _p(cos), _p(sin), _I(tokens), _I(seq), _I(heads), _I(head_dim), _L(pitch), _F(sign), _stream())
 
 
+# ------------------------------------------------------------------------------ all-gather fused with its GEMM
+def ag_gemm_grid() -> int:
+    """CTAs per launch of ``ag_gemm_nt`` (its per-block counters advance by this much per launch)."""
+    return int(require().b2_ag_gemm_grid())
+
+
+def ag_gemm_nt(x, w_ptrs, n_rows: int, shard_rows: int, world: int, rank: int, sig_ptrs, sig_slot: int, seq: int,
+               block_flags, flag_epoch: int):
+    """``x [M,K] @ W [n_rows,K]ᵀ`` where ``W`` is row-sharded over ``world`` ranks: ``w_ptrs`` holds every rank's
+    copy of ``W`` (a ctypes array of ``MAX_RANKS`` addresses; in copy ``r`` the rows of rank ``r`` are current).
+    The kernel pulls the peers' rows into this rank's copy while the tensor cores work on the local rows.
+    ``block_flags``: int32 ``[ceil(n_rows/256)]``, zero at first use; ``flag_epoch``: 1, 2, ... per launch with
+    those counters.  Returns ``None`` when the device cannot co-schedule the kernel (gather and multiply instead)."""
+    M, K = x.shape
+    if x.stride(1) != 1:
+        raise ValueError("x must have unit inner stride")
+    y = torch.empty(M, n_rows, dtype=torch.bfloat16, device=x.device)
+    rc = require().b2_ag_gemm_nt(_p(_bf16(x)), w_ptrs, _p(y), _I(M), _I(n_rows), _I(K), _L(x.stride(0)), _L(n_rows),
+                                 _I(shard_rows), _I(world), _I(rank), sig_ptrs, _I(sig_slot), _I(seq),
+                                 _p(block_flags), _I(flag_epoch), _p(status_word(x.device)), _stream())
+    if rc == -20:
+        return None
+    if rc != 0:
+        raise RuntimeError(f"b2_ag_gemm_nt failed with code {rc}")
+    global _launches
+    _launches += 1
+    return y
+
+
 # ------------------------------------------------------------------------------ attention
 def _token_pitch(t):
     B, S, H, hd = t.shape
@@ -302,8 +331,8 @@ def _token_pitch(t):
     return t.stride(1)
 
 
-def attention_fwd(q, k, v, cos=None, sin=None):
-    """Causal GQA attention.  ``q [B,S,Hq,128]``, ``k, v [B,S,Hkv,128]`` bf16 (views of a fused projection are
+def attention_fwd(q, k, v, cos=None, sin=None, causal=True):
+    """GQA attention, causal by default.  ``q [B,S,Hq,128]``, ``k, v [B,S,Hkv,128]`` bf16 (views of a fused projection are
     fine).  With ``cos``/``sin`` the rotation is applied to copies of q and k first.  Returns
     ``(out [B,S,Hq,128], lse fp32 [B,Hq,S], q_used, k_used)``."""
     B, S, Hq, hd = q.shape
@@ -314,13 +343,13 @@ def attention_fwd(q, k, v, cos=None, sin=None):
         rope_inplace(k, 0, B * S, S, Hkv, hd, Hkv * hd, cos, sin, 1.0)
     out = torch.empty(B, S, Hq, hd, dtype=torch.bfloat16, device=q.device)
     lse = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
-    _call("b2_attention_fwd", _p(_bf16(q)), _p(_bf16(k)), _p(_bf16(v)), _L(_token_pitch(q)), _L(_token_pitch(k)),
-          _L(_token_pitch(v)), _p(out), _p(lse), _I(B), _I(S), _I(Hq), _I(Hkv), _F(hd ** -0.5),
+    _call("b2_attention_fwd_ex", _p(_bf16(q)), _p(_bf16(k)), _p(_bf16(v)), _L(_token_pitch(q)), _L(_token_pitch(k)),
+          _L(_token_pitch(v)), _p(out), _p(lse), _I(B), _I(S), _I(Hq), _I(Hkv), _F(hd ** -0.5), _I(int(causal)),
           _p(status_word(q.device)), _stream())
     return out, lse, q, k
 
 
-def attention_bwd(dout, q, k, v, out, lse, cos=None, sin=None, grads=None):
+def attention_bwd(dout, q, k, v, out, lse, cos=None, sin=None, grads=None, causal=True):
     """Gradients of ``attention_fwd`` w.r.t. the (rotated) q, k and v.  ``grads`` may give three preallocated
     ``[B,S,H,128]`` views (for instance slices of one fused buffer) to write into."""
     B, S, Hq, hd = q.shape
@@ -332,10 +361,10 @@ def attention_bwd(dout, q, k, v, out, lse, cos=None, sin=None, grads=None):
     dq, dk, dv = grads
     delta = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
     dout = _bf16(dout).contiguous()
-    _call("b2_attention_bwd", _p(dout), _p(q), _p(k), _p(v), _p(_bf16(out)), _p(lse), _L(_token_pitch(q)),
+    _call("b2_attention_bwd_ex", _p(dout), _p(q), _p(k), _p(v), _p(_bf16(out)), _p(lse), _L(_token_pitch(q)),
           _L(_token_pitch(k)), _L(_token_pitch(v)), _p(delta), _p(dq), _p(dk), _p(dv), _L(_token_pitch(dq)),
           _L(_token_pitch(dk)), _L(_token_pitch(dv)), _I(B), _I(S), _I(Hq), _I(Hkv), _F(hd ** -0.5),
-          _p(status_word(q.device)), _stream(), n=3)
+          _I(int(causal)), _p(status_word(q.device)), _stream(), n=3)
     if cos is not None:
         rope_inplace(dq, 0, B * S, S, Hq, hd, _token_pitch(dq), cos, sin, -1.0)
         rope_inplace(dk, 0, B * S, S, Hkv, hd, _token_pitch(dk), cos, sin, -1.0)

@@ -160,6 +160,38 @@ def _train_parity(rank, world, port, out_dir, pp):
     native.check_status()
 
 
+def _allgather_gemm(rank, world, port, out_dir):
+    """All-gather fused with its GEMM against NCCL all_gather + fp32 matmul, over several "steps"."""
+    import torch
+    import torch.distributed as dist
+    from b200moe.comm import make_comm
+    from b200moe.ops import native
+    from b200moe.topology import build_groups
+    device = _setup(rank, world, port)
+    mesh = build_groups({"fsdp_parallel_num": world, "data_parallel_num": 1, "pipeline_parallel_stages": 1},
+                        rank, world, world)
+    comm = make_comm(mesh, device)
+    for M, N, K in ((4096, 6144, 4096), (1000, 1984, 512)):
+        shard = N // world
+        flat = comm.alloc_flat(N * K, torch.bfloat16)
+        w = flat.view(N, K)
+        for step in range(3):
+            torch.manual_seed(1000 * step + rank)
+            own = (torch.randn(shard, K, device=device) * 0.05).bfloat16()
+            x = (torch.randn(M, K, device=device) * 0.5).bfloat16()
+            w.fill_(float("nan"))
+            w[rank * shard:(rank + 1) * shard] = own
+            full = torch.empty(N, K, dtype=torch.bfloat16, device=device)
+            dist.all_gather_into_tensor(full, own, group=mesh.group("fsdp"))
+            y = comm.allgather_gemm(x, w)
+            assert torch.equal(w, full), "gathered weight differs"
+            assert _rel(y, x.float() @ full.float().t()) < 1e-2
+            # nobody rewrites its rows before every rank has finished reading them
+            torch.cuda.synchronize()
+            dist.barrier()
+    native.check_status()
+
+
 def run_allreduce(rank, world, port, out_dir):
     _guarded(_allreduce, rank, world, port, out_dir)
 
@@ -170,3 +202,7 @@ def run_moe_ep(rank, world, port, out_dir):
 
 def run_train_parity(rank, world, port, out_dir, pp):
     _guarded(_train_parity, rank, world, port, out_dir, pp)
+
+
+def run_allgather_gemm(rank, world, port, out_dir):
+    _guarded(_allgather_gemm, rank, world, port, out_dir)

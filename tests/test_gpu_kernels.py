@@ -326,6 +326,43 @@ def test_attention_forward_backward(native, B, S, Hq, Hkv):
     native.check_status()
 
 
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 256, 2, 2), (2, 512, 4, 1)])
+def test_attention_non_causal(native, B, S, Hq, Hkv):
+    """Every query sees every key (the form of the reference's own flash kernel): forward and backward."""
+    from b200moe.ops import functional as Fn
+    from b200moe.ops.attention import attention
+    torch.manual_seed(4)
+    hd = 128
+    q, k, v = (_rand(B, S, h, hd).requires_grad_(True) for h in (Hq, Hkv, Hkv))
+    out = attention(q, k, v, causal=False)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = Fn.attention_ref(qf, kf, vf, None, None, causal=False)
+    assert _rel(out, ref) < 1e-2
+    dout = _rand(B, S, Hq, hd)
+    out.backward(dout)
+    ref.backward(dout.float())
+    assert _rel(q.grad, qf.grad) < 2e-2 and _rel(k.grad, kf.grad) < 2e-2 and _rel(v.grad, vf.grad) < 2e-2
+    native.check_status()
+
+
+def test_flash_attention_forward_entry(native):
+    """``[B, H, S, 128]`` forward-only entry point, fp16 in and out, against an fp32 softmax(QK^T)V."""
+    from b200moe.ops.attention import flash_attention_forward
+    torch.manual_seed(5)
+    B, H, S, hd = 2, 3, 384, 128
+    q, k, v = (torch.randn(B, H, S, hd, device="cuda").half() for _ in range(3))
+    before = native.launch_count()
+    out = flash_attention_forward(q, k, v)
+    assert native.launch_count() > before and out.dtype == torch.float16 and out.shape == (B, H, S, hd)
+    ref = torch.softmax(q.float() @ k.float().transpose(-1, -2) / math.sqrt(hd), -1) @ v.float()
+    assert _rel(out, ref) < 2e-2
+    causal = flash_attention_forward(q, k, v, causal=True)
+    mask = torch.triu(torch.ones(S, S, dtype=torch.bool, device="cuda"), 1)
+    ref = torch.softmax((q.float() @ k.float().transpose(-1, -2) / math.sqrt(hd)).masked_fill(mask, float("-inf")), -1) @ v.float()
+    assert _rel(causal, ref) < 2e-2
+    native.check_status()
+
+
 def test_fused_qkv_attention_with_rope(native):
     from b200moe.ops import functional as Fn
     from b200moe.ops.attention import fused_qkv_attention
@@ -343,3 +380,46 @@ def test_fused_qkv_attention_with_rope(native):
     ref.backward(g.float())
     assert _rel(base.grad, ref_in.grad) < 2e-2
     native.check_status()
+
+
+@pytest.mark.parametrize("M,N,K,world", [(1000, 1536, 512, 2), (300, 1984, 256, 2), (2048, 2048, 1024, 4)])
+def test_allgather_gemm_emulated_ranks(native, M, N, K, world):
+    """The all-gather + GEMM kernel of every rank of a group, run one after the other on this GPU: each "rank" has
+    its own full-size copy of W in which only its own rows are valid (the rest is NaN), the "peers" are the other
+    copies, and the peers' ready signals are written by the host so that no launch waits for another one."""
+    import ctypes
+    torch.manual_seed(11)
+    shard = N // world
+    W = _rand(N, K)
+    x = _rand(M, K)
+    copies = []
+    for r in range(world):
+        c = torch.full((N, K), float("nan"), dtype=torch.bfloat16, device="cuda")
+        c[r * shard:(r + 1) * shard] = W[r * shard:(r + 1) * shard]
+        copies.append(c)
+    table = ctypes.c_ulonglong * 8
+    w_ptrs = table(*([c.data_ptr() for c in copies] + [0] * (8 - world)))
+    pads = [torch.zeros(32 * 8, dtype=torch.int32, device="cuda") for _ in range(world)]
+    sig_ptrs = table(*([s.data_ptr() for s in pads] + [0] * (8 - world)))
+    slot = 14
+    flags = [torch.zeros((N + 255) // 256, dtype=torch.int32, device="cuda") for _ in range(world)]
+    ref = x.float() @ W.float().t()
+    for epoch in (1, 2):
+        if epoch == 2:      # a second step: rows change, every copy is stale again outside its own shard
+            W = _rand(N, K)
+            ref = x.float() @ W.float().t()
+            for r, c in enumerate(copies):
+                c.fill_(float("nan"))
+                c[r * shard:(r + 1) * shard] = W[r * shard:(r + 1) * shard]
+        originals = [c.clone() for c in copies]
+        for r in range(world):
+            # what the peers hold when rank r runs: their own rows (later ranks have not gathered yet)
+            for q in range(world):
+                if q != r:
+                    copies[q].copy_(originals[q])
+            pads[r].view(32, 8)[slot].fill_(epoch)      # "every peer has announced its rows"
+            y = native.ag_gemm_nt(x, w_ptrs, N, shard, world, r, sig_ptrs, slot, epoch, flags[r], epoch)
+            assert y is not None, "cooperative launch unavailable"
+            native.check_status()
+            assert _rel(y, ref) < 1e-2
+            assert torch.equal(copies[r], W), "gathered weight differs from the sharded original"

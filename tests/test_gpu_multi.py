@@ -25,6 +25,11 @@ def test_replica_allreduce_kernels(tmp_path, free_port):
     _run(W.run_allreduce, 2, tmp_path, free_port)
 
 
+def test_allgather_fused_with_gemm(tmp_path, free_port):
+    _need(2)
+    _run(W.run_allgather_gemm, 2, tmp_path, free_port)
+
+
 def test_expert_parallel_dispatch_matches_nccl(tmp_path, free_port):
     _need(2)
     _run(W.run_moe_ep, 2, tmp_path, free_port)
