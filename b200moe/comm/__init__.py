@@ -141,11 +141,11 @@ class Comm:
     def _entry_table(self, flat):
         key = id(flat)
         if key not in self._entries:
-            rows = [[e["full_off"], e["shard_off"], e["shard_numel"]] for e in flat.entries]
+            rows = [[e["full_off"], e["shard_off"], e["shard_numel"], int(bool(e.get("lazy")))] for e in flat.entries]
             self._entries[key] = torch.tensor(rows, dtype=torch.int64, device=self.device)
         return self._entries[key]
 
-    def _fsdp_launch(self, flat, mode, lr=0.0, beta1=0.0, beta2=0.0, eps=0.0, wd=0.0, a_t=0.0):
+    def _fsdp_launch(self, flat, mode, lr=0.0, beta1=0.0, beta2=0.0, eps=0.0, wd=0.0, a_t=0.0, push_all=False):
         g = self.fsdp
         entries = self._entry_table(flat)
         if flat.m is None:
@@ -156,10 +156,13 @@ class Comm:
                      g.sig.table(), _ptr(entries), _i(len(flat.entries)), _i(g.rank), _i(g.world), _i(seq),
                      _i(SIG_FSDP), _ptr(flat.master), _ptr(flat.m), _ptr(flat.v), _ptr(flat.shard_grad),
                      ctypes.c_float(lr), ctypes.c_float(beta1), ctypes.c_float(beta2), ctypes.c_float(eps),
-                     ctypes.c_float(wd), ctypes.c_float(a_t), _i(mode), _ptr(g.counter), _ptr(self.status), _stream())
+                     ctypes.c_float(wd), ctypes.c_float(a_t), _i(mode), _i(push_all), _ptr(g.counter),
+                     _ptr(self.status), _stream())
 
     def allgather_cast(self, flat):
-        self._fsdp_launch(flat, 3)
+        """bf16 cast of every master shard pushed to every rank (also the entries that are normally gathered
+        by their first consumer)."""
+        self._fsdp_launch(flat, 3, push_all=True)
 
     def reduce_scatter_avg(self, flat):
         self._fsdp_launch(flat, 0)
@@ -179,10 +182,11 @@ class Comm:
                 return buf, addr - base
         raise KeyError("tensor does not live in a symmetric buffer of this Comm")
 
-    def allgather_gemm(self, x, w):
+    def allgather_gemm(self, x, w, segments=None):
         """``x [M,K] @ w [N,K]ᵀ`` for a weight that is row-sharded over the FSDP group: ``w`` is this rank's
         full-size copy inside a symmetric flat buffer (``alloc_flat``) in which only the own rows
-        ``[rank·N/n, (rank+1)·N/n)`` need to be current.  One kernel pulls the other rows from the peers and
+        ``[rank·N/n, (rank+1)·N/n)`` need to be current (``segments``: row counts of stacked parts that are
+        sharded one by one, e.g. the q, k and v rows of a fused projection).  One kernel pulls the other rows from the peers and
         multiplies; afterwards all of ``w`` is current on this rank.  A rank must not rewrite its rows before the
         group has synchronised again (the end-of-step kernel does).  Takes the place of the reference's
         per-module ``all_gather_into_tensor`` + einsum (implementation/distributed/ddp_modules.py:24-49)."""
@@ -190,8 +194,9 @@ class Comm:
         if g is None:
             return native.gemm_nt(x, w)
         N, K = w.shape
-        if not w.is_contiguous() or N % g.world:
-            raise ValueError("weight must be contiguous with rows divisible by the group size")
+        segments = [N] if segments is None else [int(v) for v in segments]
+        if not w.is_contiguous() or sum(segments) != N or any(v % g.world for v in segments):
+            raise ValueError("weight must be contiguous, its parts divisible by the group size")
         buf, off = self._locate(w)
         ptrs = _U64x8(*[(buf.ptrs[r] + off) if r < g.world else 0 for r in range(MAX_RANKS)])
         key = ("ag", w.data_ptr(), N, K)
@@ -201,12 +206,16 @@ class Comm:
             self._ag_state[key] = state
         state["epoch"] += 1
         seq = g.next_seq(SIG_AG_GEMM)
-        y = native.ag_gemm_nt(x, ptrs, N, N // g.world, g.world, g.rank, g.sig.table(), SIG_AG_GEMM, seq,
+        y = native.ag_gemm_nt(x, ptrs, N, segments, g.world, g.rank, g.sig.table(), SIG_AG_GEMM, seq,
                               state["flags"], state["epoch"])
         if y is None:      # no cooperative launch on this device: gather with NCCL, multiply
             state["epoch"] -= 1
-            shard = N // g.world
-            dist.all_gather_into_tensor(w, w[g.rank * shard:(g.rank + 1) * shard].clone(), group=g.group)
+            begin = 0
+            for rows in segments:
+                shard = rows // g.world
+                part = w[begin:begin + rows]
+                dist.all_gather_into_tensor(part, part[g.rank * shard:(g.rank + 1) * shard].clone(), group=g.group)
+                begin += rows
             return native.gemm_nt(x, w)
         return y
 

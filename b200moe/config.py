@@ -13,6 +13,9 @@ are optional and default to the reference's behaviour:
 ``train.expert_state_dtype``    ``float32`` | ``bfloat16`` AdamW m/v of experts
 ``train.expert_grad_dtype``     ``float32`` | ``bfloat16`` expert grad accumulators
 ``comm.backend``                ``fused`` (peer-memory kernels) | ``nccl``
+``train.fsdp_gather``           ``step``: the end-of-step kernel pushes every new weight to the peers;
+                                ``first_use``: the attention projections are gathered by the first GEMM
+                                that uses them (all-gather and GEMM in one kernel)
 ``general.device``              ``gpu`` or ``cpu`` (cpu runs the gloo plumbing tier)
 """
 from __future__ import annotations
@@ -112,6 +115,8 @@ def validate_config(config: dict, *, check_data: bool = False, check_cuda: bool 
     for key in ("expert_state_dtype", "expert_grad_dtype"):
         if train.get(key, "float32") not in ("float32", "bfloat16"):
             raise ValueError(f"train.{key} must be float32 or bfloat16")
+    if train.get("fsdp_gather", "step") not in ("step", "first_use"):
+        raise ValueError("train.fsdp_gather must be step or first_use")
     if (config.get("comm") or {}).get("backend", "fused") not in ("fused", "nccl"):
         raise ValueError("comm.backend must be fused or nccl")
     if check_data:

@@ -1,6 +1,8 @@
 // All-gather fused with the GEMM that consumes the gathered weight:  y[M,N] = x[M,K] * W[N,K]^T  where the rows
-// of W are sharded over the ranks of a group (rank r owns rows [r * shard_rows, (r + 1) * shard_rows)) and every
-// rank holds a full-size copy of W in symmetric memory in which only its own rows are current.
+// of W are sharded over the ranks of a group and every rank holds a full-size copy of W in symmetric memory in
+// which only its own rows are current.  W is a stack of up to four row segments, each sharded evenly (inside a
+// segment of S rows rank r owns rows [r S/n, (r + 1) S/n)); one segment is a plain linear layer, three are the
+// fused q/k/v projection whose parts are sharded one by one.
 //
 // One kernel per rank does both jobs.  Each CTA (one per SM, launched cooperatively so that all of them are
 // resident) has
@@ -35,13 +37,19 @@ constexpr int THREADS = 320;
 constexpr int COPY_THREADS = 128;
 constexpr int COPY_UNROLL = 8;      // 16-byte peer loads in flight per copier thread
 constexpr int GROUP_M = 8;
+constexpr int MAX_SEG = 4;
+constexpr int MAX_BLOCKS = 192;     // column blocks of 256 rows of W: N <= 49152
 
 struct Params {
   CUtensorMap map_a;      // x [M, K]
   CUtensorMap map_b;      // this rank's full copy of W [N, K]
   int M, N, K;
   int n, rank;            // group size, my index
-  int shard_rows;         // rows of W per rank
+  int num_seg;            // row segments of W
+  int seg_begin[MAX_SEG + 1];   // first row of each segment; seg_begin[num_seg] = N
+  int seg_shard[MAX_SEG];       // rows per rank inside the segment
+  int n_local;            // column blocks whose rows are all mine: order[0 .. n_local)
+  unsigned char order[MAX_BLOCKS];   // column blocks in the order they are computed (mine first) and copied
   Peers w;                // every rank's copy of W (same layout); ptr[rank] is map_b's base
   Peers sig;              // signal pads
   int sig_slot, seq;
@@ -56,29 +64,27 @@ struct Tile {
   int m_tile, n_tile;
 };
 
-__device__ __forceinline__ bool block_is_local(const Params& p, int n_tile) {
-  const int first = n_tile * BN, last = min(first + BN, p.N) - 1;
-  return first / p.shard_rows == p.rank && last / p.shard_rows == p.rank;
+__host__ __device__ __forceinline__ int owner_of_row(const Params& p, int row) {
+  int s = 0;
+  while (s + 1 < p.num_seg && row >= p.seg_begin[s + 1]) ++s;
+  return (row - p.seg_begin[s]) / p.seg_shard[s];
 }
 
-// Column blocks are visited in rotated order, starting with the first block that lies wholly in my own shard.
-__device__ __forceinline__ int first_block(const Params& p) { return (p.rank * p.shard_rows + BN - 1) / BN; }
-
-// Tiles are grouped in ``n`` phases of consecutive (rotated) column blocks; inside a phase the usual grouped
-// raster (8 row tiles share their column blocks) keeps operands in L2.
-__device__ __forceinline__ Tile decode(const Params& p, long long tile, int m_tiles, int n_tiles) {
-  const int phase_len = (n_tiles + p.n - 1) / p.n;
-  const long long per_phase = static_cast<long long>(m_tiles) * phase_len;
-  const int ph = static_cast<int>(tile / per_phase);
-  const int rest = static_cast<int>(tile - ph * per_phase);
-  const int len = min(phase_len, n_tiles - ph * phase_len);
+// Tiles come in two phases: first the column blocks whose weight rows are all local, then the others; inside a
+// phase the usual grouped raster (8 row tiles share their column blocks) keeps operands in L2.
+__device__ __forceinline__ Tile decode(const Params& p, long long tile, int m_tiles, int n_tiles, bool* local) {
+  const long long first = static_cast<long long>(m_tiles) * p.n_local;
+  const bool ph = tile >= first;
+  const int rest = static_cast<int>(ph ? tile - first : tile);
+  const int len = ph ? n_tiles - p.n_local : p.n_local;
   const int group = rest / (GROUP_M * len);
   const int first_m = group * GROUP_M;
   const int rows_in_group = min(GROUP_M, m_tiles - first_m);
   const int in_group = rest - group * GROUP_M * len;
   Tile t;
   t.m_tile = first_m + in_group % rows_in_group;
-  t.n_tile = (first_block(p) + ph * phase_len + in_group / rows_in_group) % n_tiles;
+  t.n_tile = p.order[(ph ? p.n_local : 0) + in_group / rows_in_group];
+  *local = !ph;
   return t;
 }
 
@@ -141,8 +147,9 @@ __global__ void __launch_bounds__(THREADS, 1) ag_gemm_kernel(const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       for (long long tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-        const Tile t = decode(p, tile, m_tiles, n_tiles);
-        if (!block_is_local(p, t.n_tile)) {
+        bool local;
+        const Tile t = decode(p, tile, m_tiles, n_tiles, &local);
+        if (!local) {
           // rows of this block came (or are coming) from a peer: wait until every CTA has stored its slice
           const int* flag = p.block_flags + t.n_tile;
           bool ok = ld_acquire_gpu(flag) - flag_target >= 0;
@@ -234,7 +241,8 @@ __global__ void __launch_bounds__(THREADS, 1) ag_gemm_kernel(const __grid_consta
     uint32_t acc_phase = 0;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.d);
     for (long long tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-      const Tile t = decode(p, tile, m_tiles, n_tiles);
+      bool local;
+      const Tile t = decode(p, tile, m_tiles, n_tiles, &local);
       bool got = false;
       for (int tries = 0; tries < 8 && !got && !*abort_flag; ++tries) got = mbar_wait(&tmem_full[acc], acc_phase);
       if (!got) {
@@ -289,10 +297,8 @@ __global__ void __launch_bounds__(THREADS, 1) ag_gemm_kernel(const __grid_consta
     if (*copy_ok) {
       const long long vec_per_row = p.K / 8;                    // 16-byte vectors per row of W
       uint4* mine = static_cast<uint4*>(p.w.ptr[p.rank]);
-      const int start_block = first_block(p);
-      for (int i = 0; i < n_tiles; ++i) {
-        const int nb = (start_block + i) % n_tiles;
-        if (block_is_local(p, nb)) continue;
+      for (int i = p.n_local; i < n_tiles; ++i) {
+        const int nb = p.order[i];
         const int row0 = nb * BN;
         const long long vecs = static_cast<long long>(min(BN, p.N - row0)) * vec_per_row;
         const long long lo = vecs * blockIdx.x / gridDim.x, hi = vecs * (blockIdx.x + 1) / gridDim.x;
@@ -305,7 +311,7 @@ __global__ void __launch_bounds__(THREADS, 1) ag_gemm_kernel(const __grid_consta
             const long long v = v0 + static_cast<long long>(u) * COPY_THREADS;
             live[u] = false;
             if (v < hi) {
-              const int owner = static_cast<int>((row0 + v / vec_per_row) / p.shard_rows);
+              const int owner = owner_of_row(p, row0 + static_cast<int>(v / vec_per_row));
               if (owner != p.rank) {
                 live[u] = true;
                 r[u] = __ldcg(static_cast<const uint4*>(p.w.ptr[owner]) + base + v);
@@ -339,25 +345,55 @@ using namespace b2;
 
 extern "C" {
 
-// y[M,N] = x[M,K] * W[N,K]^T with W row-sharded over ``n`` ranks.  ``w_peers``/``sig``: MAX_RANKS device addresses
+// y[M,N] = x[M,K] * W[N,K]^T with W row-sharded over ``n`` ranks.  ``seg_rows``: rows of each of the ``num_seg``
+// stacked segments of W (their sum is N; each a multiple of n).  ``w_peers``/``sig``: MAX_RANKS device addresses
 // (each rank's copy of W, each rank's signal pad).  ``block_flags``: int32 [ceil(N/256)] in local memory, zeroed
 // once at allocation; ``flag_epoch`` counts the launches that used it (1 for the first).  Every launch with the
 // same counters must use the same grid, which is the SM count.  Returns -20 when the device cannot co-schedule
 // one CTA per SM (the caller then gathers and multiplies separately).
 int b2_ag_gemm_nt(const void* x, const unsigned long long* w_peers, void* y, int M, int N, int K, long long ldx,
-                  long long ldy, int shard_rows, int n, int rank, const unsigned long long* sig, int sig_slot,
-                  int seq, int* block_flags, int flag_epoch, int* status, cudaStream_t stream) {
-  if (N % 32 || K % 8 || n < 1 || n > MAX_RANKS || rank < 0 || rank >= n || shard_rows <= 0 ||
-      static_cast<long long>(shard_rows) * n < N)
+                  long long ldy, const int* seg_rows, int num_seg, int n, int rank, const unsigned long long* sig,
+                  int sig_slot, int seq, int* block_flags, int flag_epoch, int* status, cudaStream_t stream) {
+  if (N % 32 || K % 8 || n < 1 || n > MAX_RANKS || rank < 0 || rank >= n || num_seg < 1 || num_seg > ag::MAX_SEG ||
+      (N + ag::BN - 1) / ag::BN > ag::MAX_BLOCKS)
     return -10;
   ag::Params p{};
+  p.M = M; p.N = N; p.K = K; p.n = n; p.rank = rank; p.num_seg = num_seg;
+  int row = 0;
+  for (int s = 0; s < num_seg; ++s) {
+    if (seg_rows[s] <= 0 || seg_rows[s] % n) return -10;
+    p.seg_begin[s] = row;
+    p.seg_shard[s] = seg_rows[s] / n;
+    row += seg_rows[s];
+  }
+  if (row != N) return -10;
+  p.seg_begin[num_seg] = N;
+  // column blocks whose rows are all mine first, then the others starting after my last own block, so that the
+  // ranks do not all read the same peer rows at the same time
+  const int n_tiles = (N + ag::BN - 1) / ag::BN;
+  int others[ag::MAX_BLOCKS], n_others = 0, last_local = -1;
+  for (int b = 0; b < n_tiles; ++b) {
+    const int lo = b * ag::BN, hi = (lo + ag::BN < N ? lo + ag::BN : N) - 1;
+    bool mine = true;
+    // ownership changes only at shard boundaries: checking every row of a 256-row block is cheap on the host
+    for (int r = lo; r <= hi && mine; ++r) mine = ag::owner_of_row(p, r) == rank;
+    if (mine) {
+      p.order[p.n_local++] = static_cast<unsigned char>(b);
+      last_local = b;
+    } else {
+      others[n_others++] = b;
+    }
+  }
+  int start = 0;
+  while (start < n_others && others[start] < last_local) ++start;
+  for (int i = 0; i < n_others; ++i) p.order[p.n_local + i] = static_cast<unsigned char>(others[(start + i) % n_others]);
   for (int i = 0; i < MAX_RANKS; ++i) {
     p.w.ptr[i] = i < n ? reinterpret_cast<void*>(w_peers[i]) : nullptr;
     p.sig.ptr[i] = i < n ? reinterpret_cast<void*>(sig[i]) : nullptr;
   }
   if (make_map(&p.map_a, x, K, M, ldx, ag::BM)) return -11;
   if (make_map(&p.map_b, p.w.ptr[rank], K, N, K, ag::BN)) return -12;
-  p.M = M; p.N = N; p.K = K; p.n = n; p.rank = rank; p.shard_rows = shard_rows; p.sig_slot = sig_slot; p.seq = seq;
+  p.sig_slot = sig_slot; p.seq = seq;
   p.block_flags = block_flags; p.flag_epoch = flag_epoch; p.d = y; p.ldd = ldy; p.status = status;
   static int sms = 0;
   static bool usable = false;

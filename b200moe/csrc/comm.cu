@@ -373,6 +373,7 @@ struct FsdpEntry {
   long long full_off;    // offset of the full tensor in the flat full buffers (elements)
   long long shard_off;   // offset of the shard in the flat shard buffers
   long long shard_numel;
+  long long local_only;  // 1: the new bf16 rows are written to my own copy only (a later kernel gathers them)
 };
 
 struct FsdpArgs {
@@ -388,6 +389,7 @@ struct FsdpArgs {
   float lr, beta1, beta2, eps, wd, a_t;
   int do_update;         // 0: only reduce-scatter into shard_grad; 1: also AdamW + weight push
   int do_reduce;         // 0: shard_grad already holds the gradient (after a replica all-reduce)
+  int push_all;          // 1: ignore FsdpEntry::local_only (initial materialisation)
   unsigned int* counter;
   int* status;
 };
@@ -421,7 +423,11 @@ __global__ void __launch_bounds__(512) fsdp_step_kernel(const FsdpArgs a) {
         a.m[si] = mv;
         a.v[si] = vv;
         const __nv_bfloat16 wb = __float2bfloat16_rn(pv);
-        for (int p = 0; p < a.n; ++p) static_cast<__nv_bfloat16*>(a.full_w.ptr[p])[full_base + i] = wb;
+        if (ent.local_only && !a.push_all) {
+          static_cast<__nv_bfloat16*>(a.full_w.ptr[a.rank])[full_base + i] = wb;
+        } else {
+          for (int p = 0; p < a.n; ++p) static_cast<__nv_bfloat16*>(a.full_w.ptr[p])[full_base + i] = wb;
+        }
       }
     }
   }
@@ -439,7 +445,11 @@ __global__ void __launch_bounds__(512) fsdp_allgather_kernel(const FsdpArgs a) {
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < ent.shard_numel;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
       const __nv_bfloat16 wb = __float2bfloat16_rn(a.master[ent.shard_off + i]);
-      for (int p = 0; p < a.n; ++p) static_cast<__nv_bfloat16*>(a.full_w.ptr[p])[full_base + i] = wb;
+      if (ent.local_only && !a.push_all) {
+        static_cast<__nv_bfloat16*>(a.full_w.ptr[a.rank])[full_base + i] = wb;
+      } else {
+        for (int p = 0; p < a.n; ++p) static_cast<__nv_bfloat16*>(a.full_w.ptr[p])[full_base + i] = wb;
+      }
     }
   }
   gpu_barrier_leave(bar, a.sig_slot + 1);
@@ -543,7 +553,7 @@ int b2_comm_allreduce(const unsigned long long* buf, const unsigned long long* s
 int b2_fsdp_step(const unsigned long long* full_g, const unsigned long long* full_w, const unsigned long long* sig,
                  const void* entries, int num_entries, int rank, int n, int seq, int sig_slot, float* master, float* m,
                  float* v, float* shard_grad, float lr, float beta1, float beta2, float eps, float wd, float a_t,
-                 int mode, unsigned int* counter, int* status, cudaStream_t s) {
+                 int mode, int push_all, unsigned int* counter, int* status, cudaStream_t s) {
   FsdpArgs a{};
   a.full_g = table(full_g); a.full_w = table(full_w); a.sig = table(sig);
   a.entries = static_cast<const FsdpEntry*>(entries); a.num_entries = num_entries; a.rank = rank; a.n = n;
@@ -551,6 +561,7 @@ int b2_fsdp_step(const unsigned long long* full_g, const unsigned long long* ful
   a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.wd = wd; a.a_t = a_t; a.counter = counter; a.status = status;
   a.do_reduce = mode == 0 || mode == 1;
   a.do_update = mode == 1 || mode == 2;
+  a.push_all = push_all;
   if (mode == 3) fsdp_allgather_kernel<<<148 * 2, 512, 0, s>>>(a);
   else fsdp_step_kernel<<<148 * 2, 512, 0, s>>>(a);
   return launched();

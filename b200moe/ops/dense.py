@@ -32,7 +32,13 @@ class _Linear(torch.autograd.Function):
         ctx.weight = weight
         ctx.save_for_backward(x)
         x2d = x.reshape(-1, x.shape[-1])
-        if _use_native(x, "gemm"):
+        # a weight whose peer rows have not arrived yet carries the call that gathers them and multiplies in one
+        # kernel (set by the FSDP wrapper after an optimizer step, consumed by the first use)
+        gather = getattr(weight, "pending_gather", None)
+        if gather is not None:
+            weight.pending_gather = None
+            y = gather(x2d if x2d.is_contiguous() else x2d.contiguous())
+        elif _use_native(x, "gemm"):
             y = _native().gemm_nt(x2d, weight)
         else:
             w = weight if weight.dtype == x.dtype else weight.to(x.dtype)

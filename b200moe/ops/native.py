@@ -300,19 +300,26 @@ def ag_gemm_grid() -> int:
     return int(require().b2_ag_gemm_grid())
 
 
-def ag_gemm_nt(x, w_ptrs, n_rows: int, shard_rows: int, world: int, rank: int, sig_ptrs, sig_slot: int, seq: int,
+def ag_gemm_nt(x, w_ptrs, n_rows: int, segments, world: int, rank: int, sig_ptrs, sig_slot: int, seq: int,
                block_flags, flag_epoch: int):
     """``x [M,K] @ W [n_rows,K]ᵀ`` where ``W`` is row-sharded over ``world`` ranks: ``w_ptrs`` holds every rank's
     copy of ``W`` (a ctypes array of ``MAX_RANKS`` addresses; in copy ``r`` the rows of rank ``r`` are current).
-    The kernel pulls the peers' rows into this rank's copy while the tensor cores work on the local rows.
-    ``block_flags``: int32 ``[ceil(n_rows/256)]``, zero at first use; ``flag_epoch``: 1, 2, ... per launch with
-    those counters.  Returns ``None`` when the device cannot co-schedule the kernel (gather and multiply instead)."""
+    ``segments``: row counts of the stacked parts of ``W`` that are sharded one by one (``[n_rows]`` for a plain
+    layer, ``[q, k, v]`` rows for a fused projection); inside a part of ``S`` rows rank ``r`` owns rows
+    ``[r·S/world, (r+1)·S/world)``.  The kernel pulls the peers' rows into this rank's copy while the tensor cores
+    work on the local rows.  ``block_flags``: int32 ``[ceil(n_rows/256)]``, zero at first use; ``flag_epoch``:
+    1, 2, ... per launch with those counters.  Returns ``None`` when the device cannot co-schedule the kernel
+    (gather and multiply instead)."""
     M, K = x.shape
     if x.stride(1) != 1:
         raise ValueError("x must have unit inner stride")
+    segments = [int(v) for v in segments]
+    if sum(segments) != n_rows:
+        raise ValueError("segments must add up to the rows of W")
+    seg = (ctypes.c_int * len(segments))(*segments)
     y = torch.empty(M, n_rows, dtype=torch.bfloat16, device=x.device)
     rc = require().b2_ag_gemm_nt(_p(_bf16(x)), w_ptrs, _p(y), _I(M), _I(n_rows), _I(K), _L(x.stride(0)), _L(n_rows),
-                                 _I(shard_rows), _I(world), _I(rank), sig_ptrs, _I(sig_slot), _I(seq),
+                                 seg, _I(len(segments)), _I(world), _I(rank), sig_ptrs, _I(sig_slot), _I(seq),
                                  _p(block_flags), _I(flag_epoch), _p(status_word(x.device)), _stream())
     if rc == -20:
         return None

@@ -90,7 +90,7 @@ class FSDPWrapperPipelined(nn.Module):
     def __init__(self, module: nn.Module, FSDP_communication_group=None, DDP_communication_group=None,
                  compute_dtype: torch.dtype = torch.float32, moe_compute_dtype: torch.dtype = torch.bfloat16,
                  *, prefetch_weights: bool = True, backend: str = "nccl", expert_grad_dtype=torch.float32,
-                 expert_state_dtype=torch.float32, comm=None):
+                 expert_state_dtype=torch.float32, comm=None, gather: str = "step"):
         super().__init__()
         self.module = module
         self.compute_dtype = compute_dtype
@@ -101,6 +101,9 @@ class FSDPWrapperPipelined(nn.Module):
         self.ddp_size = 1 if DDP_communication_group is None else _group_size(DDP_communication_group)
         self.backend = backend
         self.comm = comm
+        if gather not in ("step", "first_use"):
+            raise ValueError("gather must be 'step' or 'first_use'")
+        self.gather = gather
         self.sharded_params, self.replicated_params, self.expert_params = [], [], []
         device = next(module.parameters()).device
         distributed = dist.is_available() and dist.is_initialized()
@@ -170,6 +173,9 @@ class FSDPWrapperPipelined(nn.Module):
                     sub.comm = comm
         if device.type == "cuda":
             self.flat.fused_update = self._fused_update
+        self._lazy = []
+        if self.fused and self.group_size > 1 and gather == "first_use":
+            self._mark_lazy(module)
         self._gain_flat = None
         self._seen_versions = None
         self.materialize()
@@ -212,6 +218,32 @@ class FSDPWrapperPipelined(nn.Module):
             fused.main_grad = self.flat.full_g[lo:hi].view(rows, eq["full_shape"][1])
             sub.qkv_weight = fused
 
+    def _mark_lazy(self, module):
+        """``gather="first_use"``: the attention projections are not pushed to the peers by the end-of-step
+        kernel; the first GEMM that uses them after an optimizer step pulls the peers' rows itself
+        (``Comm.allgather_gemm``), so their all-gather runs under tensor-core work of the next step."""
+        by_module = {id(e["module"]): e for e in self.flat.entries}
+        for sub in module.modules():
+            if not isinstance(sub, MultiHeadLayerLL):
+                continue
+            trio = [by_module[id(m)] for m in (sub.q_proj, sub.k_proj, sub.v_proj)]
+            if sub.qkv_weight is not None:
+                for e in trio:
+                    e["lazy"] = True
+                self._lazy.append((sub.qkv_weight, [e["full_shape"][0] for e in trio]))
+            out = by_module[id(sub.output_proj)]
+            out["lazy"] = True
+            self._lazy.append((sub.output_proj.compute_weight, [out["full_shape"][0]]))
+
+    def _arm_lazy(self):
+        import functools
+        for weight, segments in self._lazy:
+            weight.pending_gather = functools.partial(self.comm.allgather_gemm, w=weight, segments=segments)
+
+    def _disarm_lazy(self):
+        for weight, _ in self._lazy:
+            weight.pending_gather = None
+
     # -- weights -------------------------------------------------------------------------
     @torch.no_grad()
     def materialize(self):
@@ -219,6 +251,7 @@ class FSDPWrapperPipelined(nn.Module):
         flat = self.flat
         if getattr(self, "fused", False) and self.group_size > 1:
             self.comm.allgather_cast(flat)
+            self._disarm_lazy()
         else:
             for e in flat.entries:
                 full = flat.full_view(flat.full_w, e)
@@ -252,6 +285,7 @@ class FSDPWrapperPipelined(nn.Module):
         self.comm.fused_update(flat, self._pending_reduce, lr, beta1, beta2, eps, decay, a_t)
         self._pending_reduce = False
         self._weights_fresh = True
+        self._arm_lazy()
         return True
 
     def after_optimizer_step(self):

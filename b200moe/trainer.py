@@ -77,7 +77,8 @@ def build_model(config: dict, mesh, device, fsdp_group, ddp_group, compute_dtype
         DDP_communication_group=ddp_group if mesh.ddp > 1 else None, compute_dtype=compute_dtype,
         moe_compute_dtype=moe_dtype, backend=backend if comm is not None else "nccl", comm=comm,
         expert_grad_dtype=_DTYPES[train_cfg.get("expert_grad_dtype", "float32")],
-        expert_state_dtype=_DTYPES[train_cfg.get("expert_state_dtype", "float32")])
+        expert_state_dtype=_DTYPES[train_cfg.get("expert_state_dtype", "float32")],
+        gather=os.environ.get("B200MOE_FSDP_GATHER") or train_cfg.get("fsdp_gather", "step"))
     opt_cfg = train_cfg["optimizer"]
     optimizer = AdamW(wrapped.parameters(), lr=train_cfg["learning_rate"],
                       betas=(opt_cfg["beta1"], opt_cfg["beta2"]), weight_decay=opt_cfg["lambda"])

@@ -135,8 +135,10 @@ def _train_parity(rank, world, port, out_dir, pp):
     comm = make_comm(mesh, device)
     losses = {}
     weights = {}
-    for backend in ("fused", "nccl"):
+    for variant, backend, gather in (("fused", "fused", "step"), ("first_use", "fused", "first_use"),
+                                     ("nccl", "nccl", "step")):
         config["comm"] = {"backend": backend}
+        config["train"]["fsdp_gather"] = gather
         torch.manual_seed(77 + mesh.stage)
         model, opt = build_model(config, mesh, device, mesh.group("fsdp"), mesh.group("ddp"), torch.bfloat16,
                                  comm if backend == "fused" else None)
@@ -144,6 +146,7 @@ def _train_parity(rank, world, port, out_dir, pp):
         torch.manual_seed(1000 + mesh.dp_idx)
         ids = torch.randint(0, 2048, (4, 257), device=device)
         run = []
+        before = native.launch_count()
         for _ in range(3):
             x = ids[:, :-1] if mesh.stage == 0 else None
             y = ids[:, 1:] if mesh.stage == pp - 1 else None
@@ -151,12 +154,20 @@ def _train_parity(rank, world, port, out_dir, pp):
                                            dtype=torch.bfloat16, device=device, pp_group=mesh.group("pp"),
                                            dp_group=mesh.group("data"))
             run.append(float(loss))
-        losses[backend] = run
-        weights[backend] = model.flat.full_w.clone()
+        losses[variant] = run
+        weights[variant] = model.flat.master.clone()
+        if gather == "first_use":
+            # steps 2 and 3 gathered q/k/v and the output projection of both blocks inside their first GEMM
+            epochs = [state["epoch"] for state in comm._ag_state.values()]
+            assert len(epochs) == 4 and all(e == 2 for e in epochs), epochs
+            assert all(w.pending_gather is not None for w, _ in model._lazy)
+        assert native.launch_count() > before
     if mesh.stage == pp - 1:
-        for a, b in zip(losses["fused"], losses["nccl"]):
-            assert abs(a - b) < 5e-2, losses
+        for other in ("first_use", "nccl"):
+            for a, b in zip(losses["fused"], losses[other]):
+                assert abs(a - b) < 5e-2, losses
     assert _rel(weights["fused"], weights["nccl"]) < 2e-2
+    assert _rel(weights["fused"], weights["first_use"]) < 2e-3
     native.check_status()
 
 
@@ -171,19 +182,20 @@ def _allgather_gemm(rank, world, port, out_dir):
     mesh = build_groups({"fsdp_parallel_num": world, "data_parallel_num": 1, "pipeline_parallel_stages": 1},
                         rank, world, world)
     comm = make_comm(mesh, device)
-    for M, N, K in ((4096, 6144, 4096), (1000, 1984, 512)):
-        shard = N // world
+    for M, segments, K in ((4096, [6144], 4096), (1000, [1984], 512), (2048, [4096, 1024, 1024], 4096)):
+        N = sum(segments)
+        owner = torch.cat([torch.arange(rows) // (rows // world) for rows in segments]).to(device)
+        mine = owner == rank
         flat = comm.alloc_flat(N * K, torch.bfloat16)
         w = flat.view(N, K)
         for step in range(3):
+            torch.manual_seed(1000 * step)
+            full = (torch.randn(N, K, device=device) * 0.05).bfloat16()      # same on every rank
             torch.manual_seed(1000 * step + rank)
-            own = (torch.randn(shard, K, device=device) * 0.05).bfloat16()
             x = (torch.randn(M, K, device=device) * 0.5).bfloat16()
             w.fill_(float("nan"))
-            w[rank * shard:(rank + 1) * shard] = own
-            full = torch.empty(N, K, dtype=torch.bfloat16, device=device)
-            dist.all_gather_into_tensor(full, own, group=mesh.group("fsdp"))
-            y = comm.allgather_gemm(x, w)
+            w[mine] = full[mine]
+            y = comm.allgather_gemm(x, w, segments)
             assert torch.equal(w, full), "gathered weight differs"
             assert _rel(y, x.float() @ full.float().t()) < 1e-2
             # nobody rewrites its rows before every rank has finished reading them

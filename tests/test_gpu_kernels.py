@@ -382,43 +382,52 @@ def test_fused_qkv_attention_with_rope(native):
     native.check_status()
 
 
-@pytest.mark.parametrize("M,N,K,world", [(1000, 1536, 512, 2), (300, 1984, 256, 2), (2048, 2048, 1024, 4)])
-def test_allgather_gemm_emulated_ranks(native, M, N, K, world):
+@pytest.mark.parametrize("M,K,world,segments", [(1000, 512, 2, [1536]), (300, 256, 2, [1984]),
+                                                (2048, 1024, 4, [2048]), (700, 512, 2, [1024, 256, 256]),
+                                                (513, 256, 4, [1024, 512, 512, 96 * 4])])
+def test_allgather_gemm_emulated_ranks(native, M, K, world, segments):
     """The all-gather + GEMM kernel of every rank of a group, run one after the other on this GPU: each "rank" has
     its own full-size copy of W in which only its own rows are valid (the rest is NaN), the "peers" are the other
-    copies, and the peers' ready signals are written by the host so that no launch waits for another one."""
+    copies, and the peers' ready signals are written by the host so that no launch waits for another one.
+    ``segments``: stacked parts of W sharded one by one (a fused q/k/v projection has three)."""
     import ctypes
     torch.manual_seed(11)
-    shard = N // world
-    W = _rand(N, K)
+    N = sum(segments)
+    owner = torch.empty(N, dtype=torch.long)
+    begin = 0
+    for rows in segments:
+        owner[begin:begin + rows] = torch.arange(rows) // (rows // world)
+        begin += rows
+    owner = owner.cuda()
     x = _rand(M, K)
-    copies = []
-    for r in range(world):
-        c = torch.full((N, K), float("nan"), dtype=torch.bfloat16, device="cuda")
-        c[r * shard:(r + 1) * shard] = W[r * shard:(r + 1) * shard]
-        copies.append(c)
+
+    def fresh():
+        full = _rand(N, K)
+        parts = []
+        for r in range(world):
+            c = torch.full((N, K), float("nan"), dtype=torch.bfloat16, device="cuda")
+            c[owner == r] = full[owner == r]
+            parts.append(c)
+        return full, parts
+
+    W, filled = fresh()
+    copies = [c.clone() for c in filled]
     table = ctypes.c_ulonglong * 8
     w_ptrs = table(*([c.data_ptr() for c in copies] + [0] * (8 - world)))
     pads = [torch.zeros(32 * 8, dtype=torch.int32, device="cuda") for _ in range(world)]
     sig_ptrs = table(*([s.data_ptr() for s in pads] + [0] * (8 - world)))
     slot = 14
     flags = [torch.zeros((N + 255) // 256, dtype=torch.int32, device="cuda") for _ in range(world)]
-    ref = x.float() @ W.float().t()
     for epoch in (1, 2):
-        if epoch == 2:      # a second step: rows change, every copy is stale again outside its own shard
-            W = _rand(N, K)
-            ref = x.float() @ W.float().t()
-            for r, c in enumerate(copies):
-                c.fill_(float("nan"))
-                c[r * shard:(r + 1) * shard] = W[r * shard:(r + 1) * shard]
-        originals = [c.clone() for c in copies]
+        if epoch == 2:      # a second step: rows change, every copy is stale again outside its own rows
+            W, filled = fresh()
+        ref = x.float() @ W.float().t()
         for r in range(world):
-            # what the peers hold when rank r runs: their own rows (later ranks have not gathered yet)
+            # what the ranks hold when rank r runs: their own rows only (nobody else has gathered yet)
             for q in range(world):
-                if q != r:
-                    copies[q].copy_(originals[q])
+                copies[q].copy_(filled[q])
             pads[r].view(32, 8)[slot].fill_(epoch)      # "every peer has announced its rows"
-            y = native.ag_gemm_nt(x, w_ptrs, N, shard, world, r, sig_ptrs, slot, epoch, flags[r], epoch)
+            y = native.ag_gemm_nt(x, w_ptrs, N, segments, world, r, sig_ptrs, slot, epoch, flags[r], epoch)
             assert y is not None, "cooperative launch unavailable"
             native.check_status()
             assert _rel(y, ref) < 1e-2
