@@ -17,10 +17,13 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "csrc")
-OUT = os.path.join(HERE, "_C")
-LIB = os.path.join(OUT, "libb200moe.so")
+# B200MOE_DEBUG=1 selects the checked build: -DB200MOE_DEBUG (range checks on data-dependent indices, see
+# csrc/debug.cuh), its own object directory and library name, loaded by b200moe.ops.native under the same variable.
+DEBUG = os.environ.get("B200MOE_DEBUG", "0") not in ("", "0")
+OUT = os.path.join(HERE, "_C", "debug") if DEBUG else os.path.join(HERE, "_C")
+LIB = os.path.join(OUT, "libb200moe_debug.so" if DEBUG else "libb200moe.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+              "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v"] + (["-DB200MOE_DEBUG"] if DEBUG else [])
 
 
 def nvcc() -> str:

@@ -297,6 +297,14 @@ class _Landing:
         self.tag = SymmBuffer(rows, torch.int32, device, group)
         self.src = SymmBuffer(rows, torch.int32, device, group)
         self.scalar = SymmBuffer(rows, torch.float32, device, group) if with_scalar else None
+        if native._DEBUG:
+            # checked build: rows nobody wrote are NaN and their tags out of range, so a read of a row that was
+            # never pushed shows up in the loss or in the kernels' range checks instead of passing silently
+            self.rows.tensor.fill_(float("nan"))
+            self.tag.tensor.fill_(-(1 << 30))
+            self.src.tensor.fill_(-(1 << 30))
+            torch.cuda.synchronize(device)
+            dist.barrier(group=group)
 
 
 class EPContext:

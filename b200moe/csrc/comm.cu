@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "debug.cuh"
 #include "peer.cuh"
 
 namespace b2 {
@@ -172,6 +173,7 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const EpPushArgs a) {
     const int dest = a.dest_of[i];
     const int row = a.row_of[i];
     if (dest < 0 || row < 0 || row >= a.dest_capacity) continue;   // padding rows / overflow are not sent
+    if (!dbg_in_range(dest, 0, a.n, 401)) continue;
     const __nv_bfloat16* src = a.src + static_cast<size_t>(i >> a.src_shift) * a.D;
     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.land.ptr[dest]) + static_cast<size_t>(row) * a.D;
     // four 16-byte loads in flight per lane before the (possibly remote) stores
@@ -229,6 +231,7 @@ __global__ void __launch_bounds__(256) ep_consume_kernel(const EpConsumeArgs a) 
   const int live_rows = min(a.meta[1], a.capacity);
   for (int r = blockIdx.x * 8 + warp; r < live_rows; r += gridDim.x * 8) {
     const int expert = a.tile_expert[r / TILE_ROWS];
+    if (!dbg_in_range(expert, 0, MAX_EXPERTS, 403)) continue;
     const bool live = r < a.seg_live_end[expert];
     __nv_bfloat16* dst = a.out + static_cast<size_t>(r) * a.D;
     if (!live) {
@@ -248,6 +251,7 @@ __global__ void __launch_bounds__(256) ep_consume_kernel(const EpConsumeArgs a) 
       }
       continue;
     }
+    if (!dbg_in_range(a.land_src[r], 0, a.n, 402) || !dbg_in_range(a.land_tag[r], 0, 1 << 30, 404)) continue;
     const float w = a.land_scalar[r];
     float dot = 0.f;
     for (int c = lane * 8; c < a.D; c += 256) {
@@ -568,3 +572,5 @@ int b2_fsdp_step(const unsigned long long* full_g, const unsigned long long* ful
 }
 
 }  // extern "C"
+
+B2_DEFINE_DEBUG_READER(b2_comm_debug_read)

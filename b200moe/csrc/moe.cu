@@ -14,6 +14,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "debug.cuh"
+
 namespace b2 {
 
 constexpr int PLAN_THREADS = 1024;
@@ -104,7 +106,8 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const __nv_bfloat16* __
                                                          const float* __restrict__ scale,
                                                          const __nv_bfloat16* __restrict__ y_perm,
                                                          float* __restrict__ dweights,
-                                                         __nv_bfloat16* __restrict__ x_perm, int D, int capacity_rows) {
+                                                         __nv_bfloat16* __restrict__ x_perm, int D, int capacity_rows,
+                                                         int slots) {
   const int live_rows = min(meta[1], capacity_rows);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int r = blockIdx.x * 8 + warp; r < live_rows; r += gridDim.x * 8) {
@@ -114,6 +117,7 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const __nv_bfloat16* __
       for (int c = lane * 8; c < D; c += 256) *reinterpret_cast<vec16*>(dst + c) = vec16{{0, 0, 0, 0}};
       continue;
     }
+    if (!dbg_in_range(slot, 0, slots, 411)) continue;
     const __nv_bfloat16* src = x + static_cast<size_t>(slot >> 1) * D;
     if (!scale) {
       for (int c = lane * 8; c < D; c += 256) *reinterpret_cast<vec16*>(dst + c) = *reinterpret_cast<const vec16*>(src + c);
@@ -149,10 +153,11 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
                                                           const int* __restrict__ slot_row,
                                                           const float* __restrict__ weights,
                                                           const __nv_bfloat16* __restrict__ residual,
-                                                          __nv_bfloat16* __restrict__ out, int T, int D) {
+                                                          __nv_bfloat16* __restrict__ out, int T, int D, int rows) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int t = blockIdx.x * 8 + warp; t < T; t += gridDim.x * 8) {
     const int r0 = slot_row[2 * t], r1 = slot_row[2 * t + 1];
+    if (!dbg_in_range(r0, 0, rows, 412) || !dbg_in_range(r1, 0, rows, 412)) continue;
     const float w0 = weights ? weights[2 * t] : 1.f, w1 = weights ? weights[2 * t + 1] : 1.f;
     const __nv_bfloat16* a = y_perm + static_cast<size_t>(r0) * D;
     const __nv_bfloat16* b = y_perm + static_cast<size_t>(r1) * D;
@@ -200,19 +205,21 @@ int b2_moe_plan(const long long* idx, int slots, int E, int* slot_row, int* row_
 }
 
 int b2_moe_gather(const void* x, const int* row_slot, const int* meta, const float* scale, const void* y_perm,
-                  float* dweights, void* x_perm, int D, int capacity_rows, cudaStream_t s) {
+                  float* dweights, void* x_perm, int D, int capacity_rows, int slots, cudaStream_t s) {
   if (D % 8) return -10;
   moe_gather_kernel<<<148 * 8, 256, 0, s>>>((const bf16*)x, row_slot, meta, scale, (const bf16*)y_perm, dweights,
-                                            (bf16*)x_perm, D, capacity_rows);
+                                            (bf16*)x_perm, D, capacity_rows, slots);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 int b2_moe_combine(const void* y_perm, const int* slot_row, const float* weights, const void* residual, void* out,
-                   int T, int D, cudaStream_t s) {
+                   int T, int D, int rows, cudaStream_t s) {
   if (D % 8) return -10;
   moe_combine_kernel<<<min((T + 7) / 8, 148 * 8), 256, 0, s>>>((const bf16*)y_perm, slot_row, weights,
-                                                               (const bf16*)residual, (bf16*)out, T, D);
+                                                               (const bf16*)residual, (bf16*)out, T, D, rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 }  // extern "C"
+
+B2_DEFINE_DEBUG_READER(b2_moe_debug_read)

@@ -14,7 +14,11 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-_LIB_PATH = os.path.join(_HERE, "_C", "libb200moe.so")
+# B200MOE_DEBUG=1 loads the checked build (``B200MOE_DEBUG=1 python -m b200moe.build``): data-dependent indices
+# are range-checked in the kernels and ``check_status`` also raises on a recorded violation.
+_DEBUG = os.environ.get("B200MOE_DEBUG", "0") not in ("", "0")
+_LIB_PATH = (os.path.join(_HERE, "_C", "debug", "libb200moe_debug.so") if _DEBUG
+             else os.path.join(_HERE, "_C", "libb200moe.so"))
 _lib = None
 _load_error = None
 _launches = 0
@@ -83,11 +87,33 @@ def status_word(device=None) -> torch.Tensor:
     return word
 
 
+def debug_records(clear: bool = False) -> dict:
+    """Checked build only: the first range violation recorded by each source file, as
+    ``{file: (code, value, bound, block)}``; empty in the normal build."""
+    lib = _load()
+    found = {}
+    if lib is None:
+        return found
+    for name in ("moe", "comm"):
+        reader = getattr(lib, f"b2_{name}_debug_read", None) if _DEBUG else None
+        if reader is None:
+            continue
+        record = (ctypes.c_int * 4)()
+        if reader(record, ctypes.c_int(int(clear))) == 0 and record[0]:
+            found[name] = tuple(record)
+    return found
+
+
 def check_status() -> int:
-    """Synchronising read of the status word; raises if a kernel gave up."""
+    """Synchronising read of the status word; raises if a kernel gave up (or, in the checked build, if a kernel
+    recorded an out-of-range index)."""
     value = int(status_word().item())
     if value:
         raise RuntimeError(f"b200moe kernel reported wait timeout code {value}")
+    if _DEBUG:
+        bad = debug_records()
+        if bad:
+            raise RuntimeError(f"b200moe checked build recorded out-of-range indices: {bad}")
     return value
 
 
@@ -399,7 +425,7 @@ def moe_gather(x, row_slot, meta, capacity_rows, scale=None, y_perm=None, dweigh
     if out is None:
         out = torch.empty(capacity_rows, D, dtype=torch.bfloat16, device=x.device)
     _call("b2_moe_gather", _p(_bf16(x)), _p(row_slot), _p(meta), _p(scale), _p(y_perm), _p(dweights), _p(out), _I(D),
-          _I(capacity_rows), _stream())
+          _I(capacity_rows), _I(2 * x.shape[0]), _stream())
     return out
 
 
@@ -407,7 +433,7 @@ def moe_combine(y_perm, slot_row, weights, tokens, residual=None):
     D = y_perm.shape[1]
     out = torch.empty(tokens, D, dtype=torch.bfloat16, device=y_perm.device)
     _call("b2_moe_combine", _p(_bf16(y_perm)), _p(slot_row), _p(weights), _p(residual), _p(out), _I(tokens), _I(D),
-          _stream())
+          _I(y_perm.shape[0]), _stream())
     return out
 
 

@@ -148,3 +148,21 @@ def test_helm_values_hold_a_valid_run_config():
     run["general"]["gpu_per_node"] = values["gpusPerNode"]
     run["train"].setdefault("validation_interval", 1)
     cfg.validate_config(run)
+
+
+def test_checked_build_compiles_and_exports_its_readers():
+    """``B200MOE_DEBUG=1 python -m b200moe.build`` gives a second library with the debug-record readers."""
+    import ctypes
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    subprocess.run([sys.executable, "-m", "b200moe.build"], check=True, cwd=root,
+                   env={**os.environ, "B200MOE_DEBUG": "1"})
+    path = os.path.join(root, "b200moe", "_C", "debug", "libb200moe_debug.so")
+    assert os.path.exists(path)
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as error:          # no CUDA runtime on this machine: the build itself is what was checked
+        pytest.skip(str(error))
+    assert hasattr(lib, "b2_moe_debug_read") and hasattr(lib, "b2_comm_debug_read") and hasattr(lib, "b2_gemm_nt")
