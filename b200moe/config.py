@@ -16,6 +16,10 @@ are optional and default to the reference's behaviour:
 ``train.fsdp_gather``           ``step``: the end-of-step kernel pushes every new weight to the peers;
                                 ``first_use``: the attention projections are gathered by the first GEMM
                                 that uses them (all-gather and GEMM in one kernel)
+``recovery.status_poll_seconds``, ``recovery.status_grace_seconds``
+                                watchdog on the kernels' status word: poll period (default 1) and how long
+                                the training thread may take to react before the process exits for a
+                                group restart (default 30)
 ``general.device``              ``gpu`` or ``cpu`` (cpu runs the gloo plumbing tier)
 """
 from __future__ import annotations

@@ -756,3 +756,18 @@ int b2_rope(void* x, const float* cos_t, const float* sin_t, int tokens, int S, 
 }
 
 }  // extern "C"
+
+namespace b2 {
+// The device-wide nanosecond clock, stored when the stream reaches this launch: two of these bracket a region
+// with one clock for every SM (CUDA events measure the same span; this form can be read by other kernels too).
+__global__ void timestamp_kernel(unsigned long long* out) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  *out = t;
+}
+}  // namespace b2
+
+extern "C" int b2_device_timestamp(unsigned long long* out, cudaStream_t s) {
+  b2::timestamp_kernel<<<1, 1, 0, s>>>(out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}

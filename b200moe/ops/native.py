@@ -117,9 +117,26 @@ def check_status() -> int:
     return value
 
 
+_nvtx = False
+
+
+def set_nvtx(enabled: bool) -> None:
+    """Wrap every launch of this library in an NVTX range named after its entry point (for Nsight Systems
+    timelines; the trainer switches it on with ``profile.enabled``)."""
+    global _nvtx
+    _nvtx = bool(enabled)
+
+
 def _call(name, *args, n: int = 1):
     global _launches
-    rc = getattr(require(), name)(*args)
+    if _nvtx:
+        torch.cuda.nvtx.range_push(name)
+        try:
+            rc = getattr(require(), name)(*args)
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        rc = getattr(require(), name)(*args)
     if rc != 0:
         raise RuntimeError(f"{name} failed with code {rc}")
     _launches += n
@@ -318,6 +335,16 @@ def embedding_bwd(flat_ids, dy2d, main_grad):
 def rope_inplace(buf, first_elem_offset, tokens, seq, heads, head_dim, pitch, cos, sin, sign):
     ptr = ctypes.c_void_p(buf.data_ptr() + first_elem_offset * buf.element_size())
     _call("b2_rope", ptr, _p(cos), _p(sin), _I(tokens), _I(seq), _I(heads), _I(head_dim), _L(pitch), _F(sign), _stream())
+
+
+# ------------------------------------------------------------------------------ device clock
+def device_timestamp(out=None, index: int = 0):
+    """Enqueues a one-thread kernel that stores the GPU's ``globaltimer`` (nanoseconds, one clock for the whole
+    device) into ``out[index]`` (int64, allocated if not given) when the stream reaches it."""
+    if out is None:
+        out = torch.zeros(2, dtype=torch.int64, device=torch.device("cuda", torch.cuda.current_device()))
+    _call("b2_device_timestamp", ctypes.c_void_p(out.data_ptr() + 8 * index), _stream())
+    return out
 
 
 # ------------------------------------------------------------------------------ all-gather fused with its GEMM

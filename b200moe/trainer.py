@@ -163,11 +163,23 @@ def train(local_rank: int, cluster_rank: int, world_size: int, config: dict):
                                 model_cfg["num_expert_per_node"] * fsdp_size, vocab,
                                 model_cfg["num_layers"] * mesh.pp, ctx_len)
     timer = DeviceStepTimer(device)
+    watchdog = None
+    if device.type == "cuda":
+        from .ops import native as _native
+        if _native.has("gemm"):
+            from .utils.watchdog import StatusWatchdog, device_status_reader
+            recovery = config.get("recovery", {}) or {}
+            watchdog = StatusWatchdog(device_status_reader(device),
+                                      interval_s=float(recovery.get("status_poll_seconds", 1.0)),
+                                      grace_s=float(recovery.get("status_grace_seconds", 30.0))).start()
+            _native.set_nvtx(bool(profiling))
     pp_ranks = dist.get_process_group_ranks(pp_group)
     loss_acc, span_s, span_dev_ms, span_tokens = 0.0, 0.0, 0.0, 0
     pending: list = []
 
     while iteration < target:
+        if watchdog is not None:
+            watchdog.raise_if_failed()
         with nvtx_range(f"train_iteration_{iteration}|rank={rank}|pp={stage}|dp={dp_idx}"):
             x = y = None
             with nvtx_range("batch_preparation"):
@@ -234,6 +246,9 @@ def train(local_rank: int, cluster_rank: int, world_size: int, config: dict):
                 chaos.trigger()
     ckpt.verify_pending_checkpoints(pending, iteration, rank, info_src, device, drain=True)
     release_leaks()
+    if watchdog is not None:
+        watchdog.stop()
+        watchdog.raise_if_failed()
     return iteration
 
 

@@ -111,20 +111,28 @@ def make_module_step(module, inputs, mode: str, loss_fn=None):
 
 
 class DeviceStepTimer:
-    """CUDA-event timing of a region, reduced as max over the ranks of a group."""
+    """Device-side timing of a region, reduced as max over the ranks of a group.  ``clock="event"`` uses CUDA
+    events; ``clock="globaltimer"`` brackets the region with two one-thread kernels of this framework that store
+    the GPU's nanosecond ``globaltimer`` (same span, readable by other kernels and comparable across streams)."""
 
-    def __init__(self, device, group=None):
+    def __init__(self, device, group=None, clock: str = "event"):
         self.device = torch.device(device)
         self.group = group
         self.cuda = self.device.type == "cuda"
+        self.clock = clock if self.cuda else "host"
         if self.cuda:
             self._begin = torch.cuda.Event(enable_timing=True)
             self._end = torch.cuda.Event(enable_timing=True)
+        if self.clock == "globaltimer":
+            self._stamps = torch.zeros(2, dtype=torch.int64, device=self.device)
         self._t0 = 0.0
 
     def start(self) -> None:
         import time
-        if self.cuda:
+        if self.clock == "globaltimer":
+            from ..ops import native
+            native.device_timestamp(self._stamps, 0)
+        elif self.cuda:
             self._begin.record()
         else:
             self._t0 = time.perf_counter()
@@ -132,7 +140,12 @@ class DeviceStepTimer:
     def stop_ms(self) -> float:
         import time
         import torch.distributed as dist
-        if self.cuda:
+        if self.clock == "globaltimer":
+            from ..ops import native
+            native.device_timestamp(self._stamps, 1)
+            begin, end = self._stamps.tolist()      # synchronises with the stream
+            elapsed = (end - begin) / 1e6
+        elif self.cuda:
             self._end.record()
             self._end.synchronize()
             elapsed = self._begin.elapsed_time(self._end)

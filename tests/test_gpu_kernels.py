@@ -432,3 +432,26 @@ def test_allgather_gemm_emulated_ranks(native, M, K, world, segments):
             native.check_status()
             assert _rel(y, ref) < 1e-2
             assert torch.equal(copies[r], W), "gathered weight differs from the sharded original"
+
+
+def test_device_timestamp_and_step_timer(native):
+    """``globaltimer`` stamps bracket the same span as CUDA events; NVTX wrapping of launches does not change results."""
+    from b200moe.utils.profiling import DeviceStepTimer
+    a, b = _rand(4096, 4096), _rand(4096, 4096)
+    native.gemm_nt(a, b)
+    torch.cuda.synchronize()
+    by_event, by_clock = DeviceStepTimer("cuda"), DeviceStepTimer("cuda", clock="globaltimer")
+    by_event.start()
+    by_clock.start()
+    for _ in range(20):
+        native.gemm_nt(a, b)
+    t_clock = by_clock.stop_ms()
+    t_event = by_event.stop_ms()
+    assert t_clock > 0 and abs(t_clock - t_event) < 0.25 * t_event + 0.05, (t_clock, t_event)
+    native.set_nvtx(True)
+    try:
+        with_ranges = native.gemm_nt(a, b)
+    finally:
+        native.set_nvtx(False)
+    assert torch.equal(with_ranges, native.gemm_nt(a, b))
+    native.check_status()

@@ -166,3 +166,45 @@ def test_checked_build_compiles_and_exports_its_readers():
     except OSError as error:          # no CUDA runtime on this machine: the build itself is what was checked
         pytest.skip(str(error))
     assert hasattr(lib, "b2_moe_debug_read") and hasattr(lib, "b2_comm_debug_read") and hasattr(lib, "b2_gemm_nt")
+
+
+def test_status_watchdog_reports_to_the_loop_and_exits_when_the_loop_is_stuck():
+    import threading
+    import time
+    from b200moe.utils.watchdog import WATCHDOG_EXIT_CODE, StatusWatchdog
+    # healthy: nothing happens
+    dog = StatusWatchdog(lambda: 0, interval_s=0.01, grace_s=0.2, exit_process=lambda code: None, log=lambda *a, **k: None).start()
+    time.sleep(0.1)
+    dog.raise_if_failed()
+    dog.stop()
+    # a timed-out device wait is picked up by the loop: the process is not killed
+    exits, seen = [], []
+    code = {"value": 0}
+    dog = StatusWatchdog(lambda: code["value"], interval_s=0.01, grace_s=1.0, exit_process=exits.append,
+                         on_failure=seen.append, log=lambda *a, **k: None).start()
+    code["value"] = 105
+    deadline = time.monotonic() + 2.0
+    while not dog.code and time.monotonic() < deadline:
+        time.sleep(0.01)
+    with pytest.raises(RuntimeError, match="105"):
+        dog.raise_if_failed()
+    time.sleep(0.2)
+    dog.stop()
+    assert seen == [105] and exits == []
+    # the loop never comes back (stuck in a host-side wait): the watchdog ends the process for the launcher
+    gone = threading.Event()
+    dog = StatusWatchdog(lambda: 301, interval_s=0.01, grace_s=0.1,
+                         exit_process=lambda c: (exits.append(c), gone.set()), log=lambda *a, **k: None).start()
+    assert gone.wait(3.0)
+    dog.stop()
+    assert exits == [WATCHDOG_EXIT_CODE]
+    # a reader that raises (lost context) counts as a failure too
+    def broken():
+        raise OSError("context lost")
+    dog = StatusWatchdog(broken, interval_s=0.01, grace_s=5.0, exit_process=exits.append, log=lambda *a, **k: None).start()
+    deadline = time.monotonic() + 2.0
+    while not dog.code and time.monotonic() < deadline:
+        time.sleep(0.01)
+    with pytest.raises(RuntimeError):
+        dog.raise_if_failed()
+    dog.stop()
