@@ -31,11 +31,17 @@ constexpr int GEMM_THREADS = 192;
 // MT = 128-row sub-tiles of A per CTA tile.  MT=1: 128x256 tile, 4 stages, accumulator double-buffered in
 // TMEM (epilogue overlaps the next main loop).  MT=2: 256x256 tile (two MMAs per k-step share the B tile in
 // shared memory, a third fewer operand bytes per FLOP), 3 stages, both accumulators fill TMEM.
-template <int MT> struct Cfg {
-  static constexpr int STAGES = MT == 2 ? 3 : 4;
+// PAIR = 1 (with MT = 1): two CTAs of a cluster share a 256x256 tile (tcgen05 cta_group::2).  Each CTA stages its
+// own 128 rows of A and 128 rows/columns of B (32 KiB per stage, 6 stages), the even CTA issues the MMAs for both,
+// and each CTA's tensor memory holds its 128 rows x 256 columns, double-buffered: the operand traffic of a 256x256
+// tile with the epilogue overlap of a 128x256 one.
+template <int MT, int PAIR = 0> struct Cfg {
+  static constexpr int STAGES = PAIR ? 6 : (MT == 2 ? 3 : 4);
   static constexpr int A_BYTES = MT * A_SUB_BYTES;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int B_STAGE_BYTES = PAIR ? B_BYTES / 2 : B_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_STAGE_BYTES;
   static constexpr int NACC = MT == 2 ? 1 : 2;
+  static constexpr int TM = PAIR ? 2 : MT;     // 128-row units per output tile
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 constexpr int GROUP_M = 8;
@@ -111,13 +117,15 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, long long 
   return t;
 }
 
-template <int A_MN, int B_MN, int EPI, int SCHED, int MT>
+template <int A_MN, int B_MN, int EPI, int SCHED, int MT, int PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
-  constexpr int STAGES = Cfg<MT>::STAGES;
-  constexpr int A_BYTES = Cfg<MT>::A_BYTES;
-  constexpr int STAGE_BYTES = Cfg<MT>::STAGE_BYTES;
-  constexpr int NACC = Cfg<MT>::NACC;
-  constexpr int TILE_M = BM * MT;
+  static_assert(!PAIR || MT == 1, "a CTA of a pair holds one 128-row sub-tile");
+  constexpr int STAGES = Cfg<MT, PAIR>::STAGES;
+  constexpr int A_BYTES = Cfg<MT, PAIR>::A_BYTES;
+  constexpr int STAGE_BYTES = Cfg<MT, PAIR>::STAGE_BYTES;
+  constexpr int NACC = Cfg<MT, PAIR>::NACC;
+  constexpr int TM = Cfg<MT, PAIR>::TM;
+  constexpr int TILE_M = BM * TM;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -130,7 +138,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int m_tiles = p.num_m_tiles ? (*p.num_m_tiles + MT - 1) / MT : (p.M + TILE_M - 1) / TILE_M;
+  // pair mode: ``cta`` is this CTA's half of the tile (0 = leader), a "worker" is a CTA pair
+  const uint32_t cta = PAIR ? cluster_ctarank() : 0;
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int num_workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int m_tiles = p.num_m_tiles ? (*p.num_m_tiles + TM - 1) / TM : (p.M + TILE_M - 1) / TILE_M;
   const int n_tiles = (p.N + BN - 1) / BN;
   const long long total_tiles = static_cast<long long>(m_tiles) * n_tiles * (SCHED == SCHED_WGRAD ? p.num_experts : 1);
 
@@ -141,7 +153,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);
+      mbar_init(&tmem_empty[a], PAIR ? 8 : 4);   // epilogue warps (of both CTAs of a pair)
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -149,9 +161,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     tma_prefetch_desc(&p.map_b);
     if (EPI == EPI_SWIGLU || p.k_split > 0) tma_prefetch_desc(&p.map_b2);
   }
+  if (PAIR) {
+    __syncthreads();
+    cluster_sync_all();      // both CTAs' barriers exist before a remote arrive or a remote completion can reach them
+  }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_slot, 512);     // one collective allocation by one warp of each CTA
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -159,14 +180,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA producer (every CTA)
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
-      for (long long tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-        const TileCoord t = decode_tile<SCHED, MT>(p, tile, m_tiles, n_tiles);
-        const int m0 = t.m_tile * TILE_M;
-        const int n0 = t.n_tile * BN;
+      for (long long tile = worker; tile < total_tiles && !*abort_flag; tile += num_workers) {
+        const TileCoord t = decode_tile<SCHED, TM>(p, tile, m_tiles, n_tiles);
+        const int m0 = t.m_tile * TILE_M + (PAIR ? static_cast<int>(cta) * BM : 0);
+        const int n0 = t.n_tile * BN + (PAIR ? static_cast<int>(cta) * (BN / 2) : 0);
         for (int kb = 0; kb < t.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             *abort_flag = 1;
@@ -175,33 +196,45 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
-          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          // pair: the leader's barrier counts the bytes of both CTAs; every load names that barrier
+          uint64_t* const full = &full_bar[stage];
+          const uint32_t full_on_leader = PAIR ? mapa_u32(smem_u32(full), 0) : 0;
+          if (!PAIR) mbar_expect_tx(full, STAGE_BYTES);
+          else if (cta == 0) mbar_expect_tx(full, 2 * STAGE_BYTES);
+          auto load = [&](void* dst, const CUtensorMap* map, int c0, int c1) {
+            if (PAIR) tma_load_2d_pair(dst, map, full_on_leader, c0, c1);
+            else tma_load_2d(dst, map, full, c0, c1);
+          };
           const int k0 = t.k_begin + kb * BK;
           // ---- A
 #pragma unroll
           for (int i = 0; i < MT; ++i) {
             if (A_MN) {
               // MN-major: two boxes of [64 (m) x 64 (k)]; inner coordinate = m, outer = k row
-              tma_load_2d(sa + i * A_SUB_BYTES, &p.map_a, &full_bar[stage], m0 + i * BM, k0);
-              tma_load_2d(sa + i * A_SUB_BYTES + 8192, &p.map_a, &full_bar[stage], m0 + i * BM + 64, k0);
+              load(sa + i * A_SUB_BYTES, &p.map_a, m0 + i * BM, k0);
+              load(sa + i * A_SUB_BYTES + 8192, &p.map_a, m0 + i * BM + 64, k0);
             } else {
-              tma_load_2d(sa + i * A_SUB_BYTES, &p.map_a, &full_bar[stage], k0, m0 + i * BM);
+              load(sa + i * A_SUB_BYTES, &p.map_a, k0, m0 + i * BM);
             }
           }
           // ---- B
           if (EPI == EPI_SWIGLU) {
             // gate rows then up rows of the same 128 output features (K-major)
             const int row = t.expert * p.b_expert_rows + t.n_tile * 128;
-            tma_load_2d(sb, &p.map_b, &full_bar[stage], k0, row);
-            tma_load_2d(sb + 16384, &p.map_b2, &full_bar[stage], k0, row);
+            if (PAIR) {
+              load(sb, cta == 0 ? &p.map_b : &p.map_b2, k0, row);      // leader: gate rows, peer: up rows
+            } else {
+              load(sb, &p.map_b, k0, row);
+              load(sb + 16384, &p.map_b2, k0, row);
+            }
           } else if (B_MN) {
             const bool second = p.k_split > 0 && k0 >= p.k_split;
             const CUtensorMap* map = second ? &p.map_b2 : &p.map_b;
             const int krow = (SCHED == SCHED_WGRAD ? 0 : t.expert * p.b_expert_rows) + (second ? k0 - p.k_split : k0);
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, map, &full_bar[stage], n0 + c * 64, krow);
+            for (int c = 0; c < (PAIR ? BN / 128 : BN / 64); ++c) load(sb + c * 8192, map, n0 + c * 64, krow);
           } else {
-            tma_load_2d(sb, &p.map_b, &full_bar[stage], k0, t.expert * p.b_expert_rows + n0);
+            load(sb, &p.map_b, k0, t.expert * p.b_expert_rows + n0);     // box of 256 rows (128 in pair mode)
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -211,15 +244,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+    // ------------------------------------------------------------ MMA issuer (the leader of a pair)
+    if (cta == 0 && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(PAIR ? 2 * BM : BM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      for (long long tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-        const TileCoord t = decode_tile<SCHED, MT>(p, tile, m_tiles, n_tiles);
+      // arrive on the same barrier of every CTA of the pair once the MMAs issued so far have retired
+      auto commit = [&](uint64_t* bar) {
+        if (PAIR) {
+          umma_commit_pair(mapa_u32(smem_u32(bar), 0));
+          umma_commit_pair(mapa_u32(smem_u32(bar), 1));
+        } else {
+          umma_commit(bar);
+        }
+      };
+      for (long long tile = worker; tile < total_tiles && !*abort_flag; tile += num_workers) {
+        const TileCoord t = decode_tile<SCHED, TM>(p, tile, m_tiles, n_tiles);
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
           *abort_flag = 1;
           atomicExch(p.status, 2);
@@ -243,10 +285,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
             for (int i = 0; i < MT; ++i) {
               const uint32_t sai = sa + i * A_SUB_BYTES;
               const uint64_t da = A_MN ? umma_smem_desc(sai + k * 2048, 8192, 1024) : umma_smem_desc(sai + k * 32, 16, 1024);
-              umma_bf16_ss(d_tmem + i * BN, da, db, idesc, (kb | k) != 0);
+              if (PAIR) umma_bf16_ss_pair(d_tmem + i * BN, da, db, idesc, (kb | k) != 0);
+              else umma_bf16_ss(d_tmem + i * BN, da, db, idesc, (kb | k) != 0);
             }
           }
-          umma_commit(&empty_bar[stage]);   // frees the stage once these MMAs have read it
+          commit(&empty_bar[stage]);   // frees the stage once these MMAs have read it
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -257,7 +300,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           atomicExch(p.status, 3);
           break;
         }
-        umma_commit(&tmem_full[acc]);
+        commit(&tmem_full[acc]);
         if (++acc == NACC) {
           acc = 0;
           acc_phase ^= 1;
@@ -270,8 +313,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     const int row_in_tile = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (long long tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-      const TileCoord t = decode_tile<SCHED, MT>(p, tile, m_tiles, n_tiles);
+    for (long long tile = worker; tile < total_tiles && !*abort_flag; tile += num_workers) {
+      const TileCoord t = decode_tile<SCHED, TM>(p, tile, m_tiles, n_tiles);
       if (!mbar_wait(&tmem_full[acc], acc_phase)) {
         *abort_flag = 1;
         atomicExch(p.status, 4);
@@ -282,7 +325,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
 #pragma unroll 1
       for (int sub = 0; sub < MT; ++sub) {
       const uint32_t taddr = tmem_base + (MT == 2 ? sub * BN : acc * BN) + (static_cast<uint32_t>(quad * 32) << 16);
-      const long long row = static_cast<long long>(t.m_tile) * TILE_M + sub * BM + row_in_tile;
+      const long long row = static_cast<long long>(t.m_tile) * TILE_M + (PAIR ? static_cast<int>(cta) : sub) * BM + row_in_tile;
       const bool row_ok = row < p.M;
       if (EPI == EPI_SWIGLU) {
         __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(p.d);
@@ -392,7 +435,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       }  // sub
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[acc]), 0));
+        else mbar_arrive(&tmem_empty[acc]);
+      }
       if (++acc == NACC) {
         acc = 0;
         acc_phase ^= 1;
@@ -402,16 +448,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
 
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's shared memory, barriers and tensor memory are idle as well
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if (PAIR) tmem_dealloc_pair(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
   }
 }
 
 // ------------------------------------------------------------------ host side
 template <int A_MN, int B_MN, int EPI, int SCHED, int MT>
 static int launch_mt(const GemmParams& p, int sms, cudaStream_t stream) {
-  auto kernel = gemm_tcgen05_kernel<A_MN, B_MN, EPI, SCHED, MT>;
+  auto kernel = gemm_tcgen05_kernel<A_MN, B_MN, EPI, SCHED, MT, 0>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MT>::SMEM) != cudaSuccess)
@@ -422,24 +470,88 @@ static int launch_mt(const GemmParams& p, int sms, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-static int g_tile_mode = 0;   // 0 auto, 1 force 128x256, 2 force 256x256 where legal
-
-// 256x256 tiles need whole 256-row tiles of one expert (the caller says whether its segments are padded to
-// 256 rows), enough tiles to fill the machine and a long K: with a short K, losing the epilogue/main-loop
-// overlap costs more than the operand traffic saves.
+// CTA pairs: a cluster of two CTAs per 256x256 tile, as many pairs as the device keeps resident.
+// Returns -20 when clusters of two with this much shared memory cannot be scheduled.
 template <int A_MN, int B_MN, int EPI, int SCHED>
-static int launch(const GemmParams& p, int sms, cudaStream_t stream) {
-  // grouped weight gradients: K is the row count of one expert, known to the host only on average
+static int pairs_resident(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int sms) {
+  auto kernel = gemm_tcgen05_kernel<A_MN, B_MN, EPI, SCHED, 1, 1>;
+  attr->id = cudaLaunchAttributeClusterDimension;
+  attr->val.clusterDim.x = 2;
+  attr->val.clusterDim.y = 1;
+  attr->val.clusterDim.z = 1;
+  cfg->blockDim = dim3(GEMM_THREADS);
+  cfg->dynamicSmemBytes = Cfg<1, 1>::SMEM;
+  cfg->attrs = attr;
+  cfg->numAttrs = 1;
+  static int max_pairs = -1;
+  if (max_pairs < 0) {
+    max_pairs = 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1, 1>::SMEM) == cudaSuccess) {
+      int clusters = 0;
+      cfg->gridDim = dim3(sms / 2 * 2);
+      if (cudaOccupancyMaxActiveClusters(&clusters, kernel, cfg) == cudaSuccess) max_pairs = clusters;
+      else cudaGetLastError();
+    }
+  }
+  return max_pairs;
+}
+
+template <int A_MN, int B_MN, int EPI, int SCHED>
+static int launch_pair(const GemmParams& p, int sms, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr;
+  const int pairs = pairs_resident<A_MN, B_MN, EPI, SCHED>(&cfg, &attr, sms);
+  if (pairs < 1) return -20;
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.stream = stream;
+  if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<A_MN, B_MN, EPI, SCHED, 1, 1>, p) != cudaSuccess) {
+    cudaGetLastError();
+    return -4;
+  }
+  return 0;
+}
+
+static int g_tile_mode = 0;   // 0 auto, 1 force 128x256, 2 force 256x256 on one CTA, 3 force CTA pairs where legal
+
+enum TileKind : int { TILE_128 = 0, TILE_256 = 1, TILE_PAIR = 2 };
+
+// 256-row tiles (one CTA with two sub-tiles, or a CTA pair) need whole 256-row tiles of one expert: the caller says
+// whether its segments are padded to 256 rows.  Measured on 16384 x 6144 x 4096: 128x256 tiles 1351 TFLOP/s,
+// CTA pairs 1494; on K = 14336: single-CTA 256x256 1449, CTA pairs 1539.  So pairs are used wherever they are
+// legal and there are enough tiles to occupy every pair; small problems keep the 128x256 tiles.
+template <int SCHED>
+static TileKind choose_tile(const GemmParams& p, int sms, bool pair_available) {
   const long long k_eff = SCHED == SCHED_WGRAD ? p.K / (p.num_experts > 0 ? p.num_experts : 1) : p.K;
   const bool legal = SCHED == SCHED_WGRAD ||
                      (p.tile_expert == nullptr ? p.num_m_tiles == nullptr : p.group_align256 != 0);
   const long long tiles256 = static_cast<long long>((p.M + 255) / 256) * ((p.N + BN - 1) / BN) *
                              (SCHED == SCHED_WGRAD ? p.num_experts : 1);
-  // measured: 256x256 wins from K ~ 6144 up (+14 % at K = 14336 and 28672); at K = 4096 the exposed epilogue
-  // costs more than the operand traffic saves
-  const bool big = g_tile_mode == 2 || (g_tile_mode == 0 && tiles256 >= 2LL * sms && k_eff >= 6144);
-  if (legal && big) return launch_mt<A_MN, B_MN, EPI, SCHED, 2>(p, sms, stream);
+  if (!legal || g_tile_mode == 1) return TILE_128;
+  if (g_tile_mode == 2) return TILE_256;
+  if (pair_available && (g_tile_mode == 3 || tiles256 >= sms / 2)) return TILE_PAIR;
+  if (g_tile_mode == 3) return TILE_128;
+  return tiles256 >= 2LL * sms && k_eff >= 6144 ? TILE_256 : TILE_128;
+}
+
+template <int A_MN, int B_MN, int EPI, int SCHED>
+static bool pair_available(int sms) {
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr;
+  return pairs_resident<A_MN, B_MN, EPI, SCHED>(&cfg, &attr, sms) >= sms / 2 - 8;   // (nearly) every SM in a pair
+}
+
+template <int A_MN, int B_MN, int EPI, int SCHED>
+static int launch(const GemmParams& p, TileKind kind, int sms, cudaStream_t stream) {
+  if (kind == TILE_PAIR) return launch_pair<A_MN, B_MN, EPI, SCHED>(p, sms, stream);
+  if (kind == TILE_256) return launch_mt<A_MN, B_MN, EPI, SCHED, 2>(p, sms, stream);
   return launch_mt<A_MN, B_MN, EPI, SCHED, 1>(p, sms, stream);
+}
+
+// Convenience for entry points whose tensor maps do not depend on the tile kind.
+template <int A_MN, int B_MN, int EPI, int SCHED>
+static int launch(const GemmParams& p, int sms, cudaStream_t stream) {
+  return launch<A_MN, B_MN, EPI, SCHED>(p, choose_tile<SCHED>(p, sms, pair_available<A_MN, B_MN, EPI, SCHED>(sms)),
+                                        sms, stream);
 }
 
 static int sm_count() {
@@ -464,7 +576,7 @@ using namespace b2;
 //   status         device int32 word, set non-zero if an in-kernel wait ran out
 extern "C" {
 
-// 0 automatic, 1 always 128x256 tiles, 2 256x256 tiles wherever they are legal.
+// 0 automatic, 1 always 128x256 tiles, 2 single-CTA 256x256 tiles wherever they are legal, 3 CTA pairs wherever legal.
 void b2_gemm_set_tile_mode(int mode) { g_tile_mode = mode; }
 
 // y[M,N] = a[M,K] * w[e][N,K]^T      (a K-major, w K-major)
@@ -474,14 +586,20 @@ int b2_gemm_nt(const void* a, const void* w, void* d, int M, int N, int K, long 
                int epi, int* status, cudaStream_t stream) {
   if (N % 32 || K % 8) return -10;
   GemmParams p{};
-  if (make_map(&p.map_a, a, K, M, lda, BM)) return -11;
-  if (make_map(&p.map_b, w, K, static_cast<long long>(num_experts) * N, ldw, BN)) return -12;
   p.M = M; p.N = N; p.K = K; p.num_experts = num_experts; p.b_expert_rows = N; p.k_split = 0;
   p.tile_expert = tile_expert; p.num_m_tiles = num_m_tiles; p.d = d; p.ldd = ldd; p.status = status; p.beta = 0.f;
   p.group_align256 = group_align256;
-  if (epi == EPI_STORE_BF16) return launch<0, 0, EPI_STORE_BF16, SCHED_FLAT>(p, sm_count(), stream);
-  if (epi == EPI_STORE_F32) return launch<0, 0, EPI_STORE_F32, SCHED_FLAT>(p, sm_count(), stream);
-  return -13;
+  if (epi != EPI_STORE_BF16 && epi != EPI_STORE_F32) return -13;
+  const int sms = sm_count();
+  const bool pairs = epi == EPI_STORE_BF16 ? pair_available<0, 0, EPI_STORE_BF16, SCHED_FLAT>(sms)
+                                           : pair_available<0, 0, EPI_STORE_F32, SCHED_FLAT>(sms);
+  const TileKind kind = choose_tile<SCHED_FLAT>(p, sms, pairs);
+  if (make_map(&p.map_a, a, K, M, lda, BM)) return -11;
+  // a CTA of a pair stages 128 of the tile's 256 weight rows
+  if (make_map(&p.map_b, w, K, static_cast<long long>(num_experts) * N, ldw, kind == TILE_PAIR ? BN / 2 : BN))
+    return -12;
+  if (epi == EPI_STORE_BF16) return launch<0, 0, EPI_STORE_BF16, SCHED_FLAT>(p, kind, sms, stream);
+  return launch<0, 0, EPI_STORE_F32, SCHED_FLAT>(p, kind, sms, stream);
 }
 
 // h[M,F] = silu(a w1[e]^T) * (a w3[e]^T); optional gate/up pre-activations [M,F].

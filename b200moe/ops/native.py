@@ -153,8 +153,8 @@ def _bf16(t):
 
 # ------------------------------------------------------------------------------ GEMM
 def set_gemm_tile_mode(mode: int) -> None:
-    """0: automatic; 1: always 128x256 CTA tiles; 2: 256x256 tiles wherever legal
-    (dense and weight-gradient problems).  For A/B measurements."""
+    """0: automatic; 1: always 128x256 CTA tiles; 2: single-CTA 256x256 tiles wherever legal; 3: 256x256 tiles on
+    CTA pairs (``cta_group::2``) wherever legal.  For A/B measurements and tests."""
     require().b2_gemm_set_tile_mode(_I(mode))
 
 

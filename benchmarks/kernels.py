@@ -52,7 +52,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--compare", action="store_true", help="also time the PyTorch library op")
     ap.add_argument("--experts", type=int, default=8, help="local experts of the grouped cases")
-    ap.add_argument("--tile-mode", type=int, default=0, help="GEMM CTA tile: 0 auto, 1 128x256, 2 256x256")
+    ap.add_argument("--ab-tiles", action="store_true",
+                    help="time every GEMM case with 128x256, single-CTA 256x256 and CTA-pair tiles, back to back")
+    ap.add_argument("--tile-mode", type=int, default=0, help="GEMM CTA tile: 0 auto, 1 128x256, 2 256x256 on one CTA, 3 CTA pairs")
     args = ap.parse_args()
     native.require()
     native.set_gemm_tile_mode(args.tile_mode)
@@ -66,6 +68,14 @@ def main():
         ms = timeit(fn, args.iters)
         line = {"kernel": name, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
                 "frac": round(flops / ms / 1e9 / tf_peak, 3), "of": tag}
+        if args.ab_tiles and "pair_nt" not in name:
+            # the clocks drift with the power cap over a long run, so the three tile kinds are timed right after
+            # one another (twice, interleaved) and only their ratios are meaningful
+            for label, mode in (("tflops_128x256", 1), ("tflops_256x256_one_cta", 2), ("tflops_cta_pair", 3)) * 2:
+                native.set_gemm_tile_mode(mode)
+                t = timeit(fn, args.iters)
+                line[label] = max(line.get(label, 0.0), round(flops / t / 1e9, 1))
+            native.set_gemm_tile_mode(args.tile_mode)
         if ref is not None and args.compare:
             rms = timeit(ref, args.iters)
             line["library_ms"] = round(rms, 4)
@@ -76,6 +86,13 @@ def main():
     wqkv, wo = rnd(6144, D, scale=0.02), rnd(D, D, scale=0.02)
     gemm_case("gemm_nt qkv 16384x6144x4096", 2 * T * 6144 * D, lambda: native.gemm_nt(x, wqkv), lambda: x @ wqkv.t())
     gemm_case("gemm_nt out 16384x4096x4096", 2 * T * D * D, lambda: native.gemm_nt(x, wo), lambda: x @ wo.t())
+    gemm_case("gemm_pair_nt qkv 16384x6144x4096 (cta_group::2)", 2 * T * 6144 * D, lambda: native.gemm_pair_nt(x, wqkv))
+    gemm_case("gemm_pair_nt out 16384x4096x4096 (cta_group::2)", 2 * T * D * D, lambda: native.gemm_pair_nt(x, wo))
+    gemm_case("gemm_pair_nt qkv, one accumulator", 2 * T * 6144 * D, lambda: native.gemm_pair_nt(x, wqkv, acc_bufs=1))
+    hk, wk = rnd(T, Fd, scale=0.1), rnd(D, Fd, scale=0.02)
+    gemm_case("gemm_nt K=14336 16384x4096x14336", 2 * T * D * Fd, lambda: native.gemm_nt(hk, wk))
+    gemm_case("gemm_pair_nt K=14336 16384x4096x14336 (cta_group::2)", 2 * T * D * Fd, lambda: native.gemm_pair_nt(hk, wk))
+    del hk, wk
     dy = rnd(T, 6144)
     gemm_case("gemm_nn dx 16384x4096x6144", 2 * T * 6144 * D, lambda: native.gemm_nn(dy, wqkv), lambda: dy @ wqkv)
     acc = torch.zeros(6144, D, device="cuda")

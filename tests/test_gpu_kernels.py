@@ -14,6 +14,14 @@ def native():
     return n
 
 
+@pytest.fixture(params=[0, 2, 3], ids=["tiles_auto", "tiles_256_one_cta", "tiles_cta_pair"])
+def tile_mode(request, native):
+    """GEMM CTA tile: automatic choice, forced single-CTA 256x256, forced CTA pairs (cta_group::2)."""
+    native.set_gemm_tile_mode(request.param)
+    yield request.param
+    native.set_gemm_tile_mode(0)
+
+
 def _rel(a, b):
     return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
 
@@ -24,7 +32,7 @@ def _rand(*shape, scale=1.0):
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 1024, 4096), (1024, 6144, 1024),
                                    (200, 384, 192), (128, 32000, 512)])
-def test_gemm_nt(native, M, N, K):
+def test_gemm_nt(native, tile_mode, M, N, K):
     x, w = _rand(M, K), _rand(N, K, scale=0.05)
     got = native.gemm_nt(x, w)
     want = x.float() @ w.float().t()
@@ -33,7 +41,7 @@ def test_gemm_nt(native, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 1024, 512), (384, 4096, 2048), (256, 320, 128)])
-def test_gemm_nn(native, M, N, K):
+def test_gemm_nn(native, tile_mode, M, N, K):
     dy, w = _rand(M, K), _rand(K, N, scale=0.05)
     got = native.gemm_nn(dy, w)
     assert _rel(got, dy.float() @ w.float()) < 6e-3
@@ -42,7 +50,7 @@ def test_gemm_nn(native, M, N, K):
 
 @pytest.mark.parametrize("R,M,N", [(128, 128, 256), (512, 256, 512), (4096, 1024, 384), (1024, 6144, 1024)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_gemm_tn_accumulates(native, R, M, N, dtype):
+def test_gemm_tn_accumulates(native, tile_mode, R, M, N, dtype):
     dy, x = _rand(R, M, scale=0.1), _rand(R, N, scale=0.1)
     base = torch.randn(M, N, device="cuda").to(dtype)
     out = base.clone()
@@ -54,8 +62,8 @@ def test_gemm_tn_accumulates(native, R, M, N, dtype):
     native.check_status()
 
 
-def _segments(counts):
-    padded = [(c + 127) // 128 * 128 for c in counts]
+def _segments(counts, pad=128):
+    padded = [(c + pad - 1) // pad * pad for c in counts]
     offs, tiles, row = [], [], 0
     for e, p in enumerate(padded):
         tiles += [e] * (p // 128)
@@ -65,11 +73,14 @@ def _segments(counts):
     return (torch.tensor(offs, **dev), torch.tensor(tiles, **dev), torch.tensor([len(tiles), row, 0, 0], **dev), row)
 
 
+@pytest.mark.parametrize("pad", [128, 256])
 @pytest.mark.parametrize("counts", [[128, 256], [100, 0, 300, 17], [0, 0, 640, 0], [384] * 4])
-def test_grouped_expert_gemms(native, counts):
+def test_grouped_expert_gemms(native, tile_mode, counts, pad):
+    """``pad`` = 256: expert segments are whole 256-row tiles, which makes the 256-row tile kinds legal."""
     torch.manual_seed(0)
     E, D, Fd = len(counts), 256, 512
-    offs, tile_expert, meta, rows = _segments(counts)
+    offs, tile_expert, meta, rows = _segments(counts, pad)
+    align = pad == 256
     cap = rows + 256                                  # rows past the live count must be ignored
     x = torch.zeros(cap, D, device="cuda", dtype=torch.bfloat16)
     start = 0
@@ -78,8 +89,8 @@ def test_grouped_expert_gemms(native, counts):
         start = int(offs[e])
     x[rows:] = float("nan")
     w1, w3, w2 = _rand(E, Fd, D, scale=0.05), _rand(E, Fd, D, scale=0.05), _rand(E, D, Fd, scale=0.05)
-    h, gate, up = native.gemm_swiglu(x, w1, w3, tile_expert, meta[0:1])
-    y = native.gemm_nt(h, w2, tile_expert=tile_expert, num_m_tiles=meta[0:1], num_experts=E)
+    h, gate, up = native.gemm_swiglu(x, w1, w3, tile_expert, meta[0:1], align256=align)
+    y = native.gemm_nt(h, w2, tile_expert=tile_expert, num_m_tiles=meta[0:1], num_experts=E, align256=align)
     start = 0
     for e in range(E):
         end = int(offs[e])
@@ -94,10 +105,11 @@ def test_grouped_expert_gemms(native, counts):
     # data gradients: dh = dy W2 ; dx = dg W1 + du W3 in one pass
     dy = torch.zeros(cap, D, device="cuda", dtype=torch.bfloat16)
     dy[:rows] = _rand(rows, D)
-    dh = native.gemm_nn(dy, w2, tile_expert=tile_expert, num_m_tiles=meta[0:1], num_experts=E)
+    dh = native.gemm_nn(dy, w2, tile_expert=tile_expert, num_m_tiles=meta[0:1], num_experts=E, align256=align)
     dgu = torch.zeros(cap, 2 * Fd, device="cuda", dtype=torch.bfloat16)
     dgu[:rows] = _rand(rows, 2 * Fd, scale=0.1)
-    dx = native.gemm_nn(dgu, w1, w2=w3, tile_expert=tile_expert, num_m_tiles=meta[0:1], num_experts=E)
+    dx = native.gemm_nn(dgu, w1, w2=w3, tile_expert=tile_expert, num_m_tiles=meta[0:1], num_experts=E,
+                        align256=align)
     acc = torch.randn(E, Fd, D, device="cuda")
     dw1 = acc.clone()
     native.gemm_tn(dgu[:, :Fd], x, out=dw1, accumulate=True, expert_offsets=offs, num_experts=E)
