@@ -511,14 +511,19 @@ static int launch_pair(const GemmParams& p, int sms, cudaStream_t stream) {
   return 0;
 }
 
-static int g_tile_mode = 0;   // 0 auto, 1 force 128x256, 2 force 256x256 on one CTA, 3 force CTA pairs where legal
+static int g_tile_mode = 0;   // 0 auto (single-CTA kinds), 1 force 128x256, 2 force 256x256 on one CTA,
+                              // 3 force CTA pairs where legal, 4 auto with CTA pairs for large problems
 
 enum TileKind : int { TILE_128 = 0, TILE_256 = 1, TILE_PAIR = 2 };
 
 // 256-row tiles (one CTA with two sub-tiles, or a CTA pair) need whole 256-row tiles of one expert: the caller says
-// whether its segments are padded to 256 rows.  Measured on 16384 x 6144 x 4096: 128x256 tiles 1351 TFLOP/s,
-// CTA pairs 1494; on K = 14336: single-CTA 256x256 1449, CTA pairs 1539.  So pairs are used wherever they are
-// legal and there are enough tiles to occupy every pair; small problems keep the 128x256 tiles.
+// whether its segments are padded to 256 rows.
+// Measured in isolation (burst clocks) CTA pairs are the fastest kind everywhere: 16384 x 6144 x 4096 runs at
+// 1351 TFLOP/s with 128x256 tiles and 1494 on pairs, grouped weight gradients gain 13-28 %.  Inside a training
+// step, which runs against the 1000 W power cap for seconds, the same kernels pull the SM clock down further
+// (median 1175 MHz against 1385 MHz with the single-CTA kinds, same power) and the step gets 7 % slower (3141 ms
+// against 2940 ms, measured twice, alternating).  So the automatic choice uses the single-CTA kinds — 256x256 for
+// long K, where the exposed epilogue is amortised, 128x256 otherwise — and pairs are opt-in (mode 3 or 4).
 template <int SCHED>
 static TileKind choose_tile(const GemmParams& p, int sms, bool pair_available) {
   const long long k_eff = SCHED == SCHED_WGRAD ? p.K / (p.num_experts > 0 ? p.num_experts : 1) : p.K;
@@ -528,7 +533,7 @@ static TileKind choose_tile(const GemmParams& p, int sms, bool pair_available) {
                              (SCHED == SCHED_WGRAD ? p.num_experts : 1);
   if (!legal || g_tile_mode == 1) return TILE_128;
   if (g_tile_mode == 2) return TILE_256;
-  if (pair_available && (g_tile_mode == 3 || tiles256 >= sms / 2)) return TILE_PAIR;
+  if (pair_available && (g_tile_mode == 3 || (g_tile_mode == 4 && tiles256 >= sms / 2))) return TILE_PAIR;
   if (g_tile_mode == 3) return TILE_128;
   return tiles256 >= 2LL * sms && k_eff >= 6144 ? TILE_256 : TILE_128;
 }
@@ -576,7 +581,8 @@ using namespace b2;
 //   status         device int32 word, set non-zero if an in-kernel wait ran out
 extern "C" {
 
-// 0 automatic, 1 always 128x256 tiles, 2 single-CTA 256x256 tiles wherever they are legal, 3 CTA pairs wherever legal.
+// 0 automatic among the single-CTA kinds, 1 always 128x256 tiles, 2 single-CTA 256x256 tiles wherever they are legal,
+// 3 CTA pairs wherever legal, 4 automatic with CTA pairs for problems that fill the machine.
 void b2_gemm_set_tile_mode(int mode) { g_tile_mode = mode; }
 
 // y[M,N] = a[M,K] * w[e][N,K]^T      (a K-major, w K-major)

@@ -44,6 +44,10 @@ def _load():
     except OSError as error:
         _load_error = str(error)
         _lib = None
+        return None
+    mode = os.environ.get("B200MOE_GEMM_TILE_MODE")
+    if mode:          # A/B runs of whole programs: see set_gemm_tile_mode
+        _lib.b2_gemm_set_tile_mode(ctypes.c_int(int(mode)))
     return _lib
 
 
@@ -153,8 +157,10 @@ def _bf16(t):
 
 # ------------------------------------------------------------------------------ GEMM
 def set_gemm_tile_mode(mode: int) -> None:
-    """0: automatic; 1: always 128x256 CTA tiles; 2: single-CTA 256x256 tiles wherever legal; 3: 256x256 tiles on
-    CTA pairs (``cta_group::2``) wherever legal.  For A/B measurements and tests."""
+    """0: automatic among the single-CTA kinds (the default: fastest under the sustained power cap of a training
+    step); 1: always 128x256 CTA tiles; 2: single-CTA 256x256 tiles wherever legal; 3: 256x256 tiles on CTA pairs
+    (``cta_group::2``) wherever legal; 4: automatic with CTA pairs for problems that fill the machine (fastest for
+    a kernel run in isolation).  The environment variable ``B200MOE_GEMM_TILE_MODE`` sets it at load time."""
     require().b2_gemm_set_tile_mode(_I(mode))
 
 

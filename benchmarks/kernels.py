@@ -54,7 +54,7 @@ def main():
     ap.add_argument("--experts", type=int, default=8, help="local experts of the grouped cases")
     ap.add_argument("--ab-tiles", action="store_true",
                     help="time every GEMM case with 128x256, single-CTA 256x256 and CTA-pair tiles, back to back")
-    ap.add_argument("--tile-mode", type=int, default=0, help="GEMM CTA tile: 0 auto, 1 128x256, 2 256x256 on one CTA, 3 CTA pairs")
+    ap.add_argument("--tile-mode", type=int, default=0, help="GEMM CTA tile: 0 auto (single-CTA kinds), 1 128x256, 2 256x256 on one CTA, 3 CTA pairs, 4 auto with pairs")
     args = ap.parse_args()
     native.require()
     native.set_gemm_tile_mode(args.tile_mode)
