@@ -343,28 +343,6 @@ def rope_inplace(buf, first_elem_offset, tokens, seq, heads, head_dim, pitch, co
     _call("b2_rope", ptr, _p(cos), _p(sin), _I(tokens), _I(seq), _I(heads), _I(head_dim), _L(pitch), _F(sign), _stream())
 
 
-# ------------------------------------------------------------------------------ GEMM on CTA pairs
-def gemm_pair_nt(x, w, acc_bufs: int = 2, probe=None):
-    """``x [M,K] @ w [N,K]ᵀ`` (bf16) with 256x256 tiles shared by two CTAs (``tcgen05`` ``cta_group::2``).  ``probe``:
-    optional int32[4] tensor that receives the tensor-memory base address seen by the two CTAs of the first pair.
-    Returns ``None`` when the device cannot run this kernel's CTA pairs."""
-    M, K = x.shape
-    N = w.shape[0]
-    if x.stride(1) != 1 or w.stride(1) != 1:
-        raise ValueError("operands must have unit inner stride")
-    y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
-    rc = require().b2_gemm_pair_nt(_p(_bf16(x)), _p(_bf16(w)), _p(y), _I(M), _I(N), _I(K), _L(x.stride(0)),
-                                   _L(w.stride(0)), _L(N), _I(acc_bufs), _p(probe), _p(status_word(x.device)),
-                                   _stream())
-    if rc == -20:
-        return None
-    if rc != 0:
-        raise RuntimeError(f"b2_gemm_pair_nt failed with code {rc}")
-    global _launches
-    _launches += 1
-    return y
-
-
 # ------------------------------------------------------------------------------ device clock
 def device_timestamp(out=None, index: int = 0):
     """Enqueues a one-thread kernel that stores the GPU's ``globaltimer`` (nanoseconds, one clock for the whole

@@ -68,7 +68,7 @@ def main():
         ms = timeit(fn, args.iters)
         line = {"kernel": name, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
                 "frac": round(flops / ms / 1e9 / tf_peak, 3), "of": tag}
-        if args.ab_tiles and "pair_nt" not in name:
+        if args.ab_tiles:
             # the clocks drift with the power cap over a long run, so the three tile kinds are timed right after
             # one another (twice, interleaved) and only their ratios are meaningful
             for label, mode in (("tflops_128x256", 1), ("tflops_256x256_one_cta", 2), ("tflops_cta_pair", 3)) * 2:
@@ -86,12 +86,8 @@ def main():
     wqkv, wo = rnd(6144, D, scale=0.02), rnd(D, D, scale=0.02)
     gemm_case("gemm_nt qkv 16384x6144x4096", 2 * T * 6144 * D, lambda: native.gemm_nt(x, wqkv), lambda: x @ wqkv.t())
     gemm_case("gemm_nt out 16384x4096x4096", 2 * T * D * D, lambda: native.gemm_nt(x, wo), lambda: x @ wo.t())
-    gemm_case("gemm_pair_nt qkv 16384x6144x4096 (cta_group::2)", 2 * T * 6144 * D, lambda: native.gemm_pair_nt(x, wqkv))
-    gemm_case("gemm_pair_nt out 16384x4096x4096 (cta_group::2)", 2 * T * D * D, lambda: native.gemm_pair_nt(x, wo))
-    gemm_case("gemm_pair_nt qkv, one accumulator", 2 * T * 6144 * D, lambda: native.gemm_pair_nt(x, wqkv, acc_bufs=1))
     hk, wk = rnd(T, Fd, scale=0.1), rnd(D, Fd, scale=0.02)
     gemm_case("gemm_nt K=14336 16384x4096x14336", 2 * T * D * Fd, lambda: native.gemm_nt(hk, wk))
-    gemm_case("gemm_pair_nt K=14336 16384x4096x14336 (cta_group::2)", 2 * T * D * Fd, lambda: native.gemm_pair_nt(hk, wk))
     del hk, wk
     dy = rnd(T, 6144)
     gemm_case("gemm_nn dx 16384x4096x6144", 2 * T * 6144 * D, lambda: native.gemm_nn(dy, wqkv), lambda: dy @ wqkv)

@@ -468,24 +468,3 @@ def test_device_timestamp_and_step_timer(native):
     assert torch.equal(with_ranges, native.gemm_nt(a, b))
     native.check_status()
 
-
-def test_gemm_on_cta_pairs(native):
-    """256x256 tiles shared by two CTAs (cta_group::2).  The first launch uses one 256-column accumulator and
-    reports the tensor-memory base of both CTAs; only if they agree (the allocation is one collective call of the
-    pair) are the double-buffered launches made."""
-    torch.manual_seed(21)
-    probe = torch.full((4,), -1, dtype=torch.int32, device="cuda")
-    x, w = _rand(512, 256), _rand(512, 256)
-    y = native.gemm_pair_nt(x, w, acc_bufs=1, probe=probe)
-    if y is None:
-        pytest.skip("clusters of two CTAs unavailable for this kernel")
-    native.check_status()
-    assert _rel(y, x.float() @ w.float().t()) < 1e-2
-    bases = probe.tolist()
-    assert bases[0] == bases[1] and bases[0] >= 0, bases
-    for M, N, K in ((512, 512, 256), (1000, 1536, 512), (130, 96, 64), (4096, 6144, 4096)):
-        x, w = _rand(M, K), _rand(N, K)
-        for bufs in (1, 2):
-            y = native.gemm_pair_nt(x, w, acc_bufs=bufs)
-            native.check_status()
-            assert _rel(y, x.float() @ w.float().t()) < 1e-2, (M, N, K, bufs)
