@@ -64,6 +64,8 @@ def test_rank_groups_reject_bad_shapes():
     (lambda c: c["train"].__setitem__("activation_recompute", "all"), "activation_recompute"),
     (lambda c: c["data"].__setitem__("vocab_size", 32001), "divisible"),
     (lambda c: c["model"].__setitem__("num_layers", 0), "positive integer"),
+    (lambda c: c["train"].__setitem__("fsdp_gather", "always"), "fsdp_gather"),
+    (lambda c: c["comm"].__setitem__("backend", "mpi"), "comm.backend"),
 ])
 def test_validation_failures(base, mutate, match):
     bad = copy.deepcopy(base)

@@ -181,3 +181,41 @@ def test_gradient_clipping_and_sampler():
     assert abs(total - 1.0) < 1e-4
     logits = torch.tensor([[0.0, 10.0, 0.0]])
     assert int(Fn.sample_output(logits, t=1.0, p=0.0)) == 1
+
+
+def test_linear_consumes_a_pending_gather_once():
+    """A weight may carry the call that gathers its peer rows and multiplies (all-gather fused with the GEMM);
+    the first ``linear`` after an optimizer step uses it, later ones and the backward pass use the weight."""
+    import torch
+    from b200moe import ops
+    torch.manual_seed(0)
+    x = torch.randn(6, 8, requires_grad=True)
+    w = torch.randn(5, 8, requires_grad=True)
+    calls = []
+
+    def gather(x2d):
+        calls.append(tuple(x2d.shape))
+        return x2d.detach() @ w.detach().t()
+
+    w.pending_gather = gather
+    y = ops.linear(x, w)
+    assert calls == [(6, 8)] and w.pending_gather is None
+    assert torch.allclose(y, x @ w.t(), atol=1e-6)
+    y.sum().backward()
+    assert torch.allclose(x.grad, torch.ones(6, 5) @ w.detach(), atol=1e-6)
+    assert torch.allclose(w.grad, torch.ones(6, 5).t() @ x.detach(), atol=1e-6)
+    ops.linear(x, w)
+    assert calls == [(6, 8)]
+
+
+def test_fsdp_first_use_gather_needs_the_fused_backend():
+    """On CPU (no peer-memory backend) ``gather="first_use"`` marks nothing lazy and training is unchanged."""
+    import torch
+    from b200moe.models import TransformerLMPipelined
+    from b200moe.parallel import FSDPWrapperPipelined
+    torch.manual_seed(0)
+    model = TransformerLMPipelined(64, 32, 32, 1, 4, 0, 1, num_expert_per_node=2, d_ff=64)
+    wrapped = FSDPWrapperPipelined(model, None, None, compute_dtype=torch.float32, gather="first_use")
+    assert wrapped._lazy == [] and not any(e.get("lazy") for e in wrapped.flat.entries)
+    with pytest.raises(ValueError):
+        FSDPWrapperPipelined(model, None, None, gather="sometimes")
