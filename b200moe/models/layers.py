@@ -28,9 +28,6 @@ __all__ = [
     "TensorExchange", "Attention_Simple", "Attention_Flash",
 ]
 
-from ..ops.moe import _AllToAllRows
-
-
 class TensorExchange(torch.autograd.Function):
     """Variable-size row exchange over the expert group, differentiable.
 

@@ -22,7 +22,6 @@ import random
 from concurrent.futures import Future, ThreadPoolExecutor
 from pathlib import Path
 
-import numpy as np
 import torch
 
 __all__ = [

@@ -42,8 +42,6 @@ def run_train(rank, world, port, config, result_dir, fail_at=None):
     torch.set_num_threads(2)
     from b200moe import trainer
     if fail_at is not None:
-        from b200moe.utils import chaos
-
         class Boom(RuntimeError):
             pass
         original = trainer.ckpt.verify_pending_checkpoints

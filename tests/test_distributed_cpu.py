@@ -3,7 +3,6 @@ single-process oracle, the full worker with checkpoint save/commit/resume, and
 recovery from a host-side failure."""
 import os
 import re
-from pathlib import Path
 
 import pytest
 import torch

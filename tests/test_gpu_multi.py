@@ -1,6 +1,4 @@
 """Multi-GPU tests of the peer-memory communication layer (one process per GPU)."""
-import os
-
 import pytest
 import torch
 import torch.multiprocessing as mp
