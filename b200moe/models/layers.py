@@ -28,6 +28,7 @@ __all__ = [
     "TensorExchange", "Attention_Simple", "Attention_Flash",
 ]
 
+
 class TensorExchange(torch.autograd.Function):
     """Variable-size row exchange over the expert group, differentiable.
 
