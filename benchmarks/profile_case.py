@@ -3,8 +3,9 @@
 ``python benchmarks/profile_case.py --case gemm_nt`` allocates only what that
 case needs (operands larger than L2, well under a few GB), runs two warm-up
 launches and three measured ones and prints the CUDA-event time.  Cases:
-gemm_nt, gemm_nn, gemm_tn, swiglu, moe_down, wgrad, rmsnorm, attention_fwd,
-attention_bwd, sdpa.
+gemm_nt, gemm_nn, gemm_tn, gemm_pair (gemm_nt on CTA pairs), ag_gemm (the all-gather + GEMM kernel as rank 0 of
+two emulated ranks: the "peer" is a second buffer on this GPU and its ready signal is written by the host, so no
+launch waits for another), swiglu, moe_down, wgrad, rmsnorm, attention_fwd, attention_bwd, sdpa.
 """
 import argparse
 import os
@@ -26,6 +27,27 @@ def build(case):
     if case == "gemm_nt":
         x, w = rnd(T, D), rnd(6144, D, scale=0.02)
         return lambda: native.gemm_nt(x, w), 2 * T * 6144 * D
+    if case == "gemm_pair":
+        x, w = rnd(T, D), rnd(6144, D, scale=0.02)
+        native.set_gemm_tile_mode(3)
+        return lambda: native.gemm_nt(x, w), 2 * T * 6144 * D
+    if case == "ag_gemm":
+        import ctypes
+        N, world = 6144, 2
+        x = rnd(T, D)
+        copies = [rnd(N, D, scale=0.02) for _ in range(world)]
+        pads = [torch.zeros(32 * 8, dtype=torch.int32, device="cuda") for _ in range(world)]
+        pads[0].fill_(1 << 20)                      # every peer "announced" its rows for all launches to come
+        table = ctypes.c_ulonglong * 8
+        w_ptrs = table(*([c.data_ptr() for c in copies] + [0] * 6))
+        sig_ptrs = table(*([s.data_ptr() for s in pads] + [0] * 6))
+        flags = torch.zeros((N + 255) // 256, dtype=torch.int32, device="cuda")
+        state = {"epoch": 0}
+
+        def launch():
+            state["epoch"] += 1
+            return native.ag_gemm_nt(x, w_ptrs, N, [N], world, 0, sig_ptrs, 14, state["epoch"], flags, state["epoch"])
+        return launch, 2 * T * N * D
     if case == "gemm_nn":
         dy, w = rnd(T, 6144), rnd(6144, D, scale=0.02)
         return lambda: native.gemm_nn(dy, w), 2 * T * 6144 * D
