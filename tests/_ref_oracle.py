@@ -24,6 +24,7 @@ from implementation.optimizer import AdamW  # noqa: E402
 from implementation.train_utils import get_batch  # noqa: E402
 from pipeline import pipelined_train_overlap  # noqa: E402
 
+mode = sys.argv[4] if len(sys.argv) > 4 else "train"
 torch.manual_seed(0)
 group = dist.new_group([0])
 model = TransformerLMPipelined(1024, 256, 128, 2, 4, 0, 1, num_expert_per_node=4, d_ff=256, dp_group=group,
@@ -33,13 +34,30 @@ wrapped = FSDPWrapperPipelined(model, FSDP_communication_group=group, compute_dt
                                moe_compute_dtype=torch.bfloat16)
 optimizer = AdamW(wrapped.parameters(), lr=3e-4, betas=(0.9, 0.999), weight_decay=0.01)
 rng = np.random.default_rng(0)
-losses, grads = [], None
-for step in range(6):
+
+
+def one_step():
     x, y = get_batch(None, 4, 256, "cpu", rng=rng, vocab_size=1024, mock_data=True)
-    loss = pipelined_train_overlap(wrapped, optimizer, x, y, [4, 256, 128], 2, 0, cross_entropy, dtype=torch.float32,
-                                   device=torch.device("cpu"), pp_group=group, dp_group=group)
-    losses.append(float(loss))
-    if grads is None:
-        grads = {n: p.grad.detach().float().clone() for n, p in wrapped.named_parameters() if p.grad is not None}
-torch.save({"init": init, "losses": losses, "grads": grads}, out_path)
+    return float(pipelined_train_overlap(wrapped, optimizer, x, y, [4, 256, 128], 2, 0, cross_entropy,
+                                         dtype=torch.float32, device=torch.device("cpu"), pp_group=group,
+                                         dp_group=group))
+
+
+if mode == "train":
+    # six steps, a checkpoint written by the reference's own (synchronous) writer, then a seventh step
+    from implementation.train_utils import save_checkpoint  # noqa: E402
+    losses, grads = [], None
+    for step in range(6):
+        losses.append(one_step())
+        if grads is None:
+            grads = {n: p.grad.detach().float().clone() for n, p in wrapped.named_parameters() if p.grad is not None}
+    save_checkpoint(wrapped, optimizer, 6, out_path + ".ckpt")
+    torch.save({"init": init, "losses": losses, "grads": grads, "loss7": one_step()}, out_path)
+else:
+    # resume from a checkpoint written by the other framework with the reference's own loader, run step seven
+    from implementation.train_utils import load_checkpoint_async_dist  # noqa: E402
+    iteration = load_checkpoint_async_dist(sys.argv[5], wrapped, optimizer)
+    for _ in range(6):
+        get_batch(None, 4, 256, "cpu", rng=rng, vocab_size=1024, mock_data=True)
+    torch.save({"iteration": iteration, "loss7": one_step()}, out_path)
 dist.destroy_process_group()

@@ -1,6 +1,6 @@
-"""Loss curve and first-step gradients against the unmodified reference package
-(CPU, tiny configuration, same weights and data).  Skipped when the reference is
-not installed under ``baseline/_ref``."""
+"""Loss curve, first-step gradients and checkpoint interchange (both directions) against the unmodified
+reference package (CPU, tiny configuration, same weights and data).  Skipped when the reference is not installed
+under ``baseline/_ref``."""
 import os
 import subprocess
 import sys
@@ -50,3 +50,48 @@ def test_tiny_model_matches_reference(tmp_path, free_port):
         assert rel < 0.1, (name, rel)      # both sides run the experts in bf16 with different op order
         checked += 1
     assert checked >= 20
+    # ---- checkpoint interchange.  The reference wrote a checkpoint after its sixth step: a fresh model of this
+    # framework loads it with its own loader and its seventh step gives the reference's seventh loss.
+    from b200moe.utils.checkpoint import load_checkpoint_async_dist, save_checkpoint
+    mine7 = float(pipelined_train_overlap(wrapped, optimizer, *get_batch(None, 4, 256, "cpu", rng=rng, vocab_size=1024,
+                                                                         mock_data=True),
+                                          [4, 256, 128], 2, 0, cross_entropy, dtype=torch.float32,
+                                          device=torch.device("cpu")))
+    assert mine7 == pytest.approx(ref["loss7"], abs=3e-3)
+    torch.manual_seed(123)
+    other = TransformerLMPipelined(1024, 256, 128, 2, 4, 0, 1, num_expert_per_node=4, d_ff=256,
+                                   moe_compute_dtype=torch.bfloat16)
+    resumed = FSDPWrapperPipelined(other, compute_dtype=torch.float32, expert_grad_dtype=torch.bfloat16,
+                                   expert_state_dtype=torch.bfloat16)
+    resumed_opt = AdamW(resumed.parameters(), lr=3e-4, betas=(0.9, 0.999), weight_decay=0.01)
+    assert load_checkpoint_async_dist(str(out) + ".ckpt", resumed, resumed_opt) == 6
+    rng2 = np.random.default_rng(0)
+    for _ in range(6):
+        get_batch(None, 4, 256, "cpu", rng=rng2, vocab_size=1024, mock_data=True)
+    x7, y7 = get_batch(None, 4, 256, "cpu", rng=rng2, vocab_size=1024, mock_data=True)
+    from_ref = float(pipelined_train_overlap(resumed, resumed_opt, x7, y7, [4, 256, 128], 2, 0, cross_entropy,
+                                             dtype=torch.float32, device=torch.device("cpu")))
+    assert from_ref == pytest.approx(ref["loss7"], abs=3e-3)
+    # ---- and the other way round: a checkpoint of this framework after six steps, loaded by the reference's loader
+    torch.manual_seed(0)
+    again = TransformerLMPipelined(1024, 256, 128, 2, 4, 0, 1, num_expert_per_node=4, d_ff=256,
+                                   moe_compute_dtype=torch.bfloat16)
+    again.load_state_dict(ref["init"])
+    w2 = FSDPWrapperPipelined(again, compute_dtype=torch.float32, expert_grad_dtype=torch.bfloat16,
+                              expert_state_dtype=torch.bfloat16)
+    o2 = AdamW(w2.parameters(), lr=3e-4, betas=(0.9, 0.999), weight_decay=0.01)
+    rng3 = np.random.default_rng(0)
+    for _ in range(6):
+        xb, yb = get_batch(None, 4, 256, "cpu", rng=rng3, vocab_size=1024, mock_data=True)
+        pipelined_train_overlap(w2, o2, xb, yb, [4, 256, 128], 2, 0, cross_entropy, dtype=torch.float32,
+                                device=torch.device("cpu"))
+    mine_ckpt = tmp_path / "mine.ckpt"
+    save_checkpoint(w2, o2, 6, str(mine_ckpt))
+    back = tmp_path / "ref_resume.pt"
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "_ref_oracle.py"), REF, str(back),
+                           str(free_port), "resume", str(mine_ckpt)], env=env, capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    resumed_by_ref = torch.load(back)
+    assert resumed_by_ref["iteration"] == 6
+    assert resumed_by_ref["loss7"] == pytest.approx(mine7, abs=3e-3)
