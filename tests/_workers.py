@@ -140,3 +140,53 @@ def run_grad_equivalence(rank, world, port, result_dir, pp):
         raise
     finally:
         dist.destroy_process_group()
+
+
+def run_reference_layout(rank, world, port, result_dir, pp, ref_dir):
+    """The run of ``_ref_oracle_multi.py`` with this framework: same per-rank initial state, data and steps."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    _env(rank, world, port)
+    torch.set_num_threads(2)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from b200moe.models import TransformerLMPipelined
+        from b200moe.ops.functional import cross_entropy
+        from b200moe.optim import AdamW
+        from b200moe.parallel import FSDPWrapperPipelined, pipelined_train_overlap
+        from b200moe.topology import build_groups
+        from b200moe.utils.data import get_batch
+        fsdp = world // pp
+        mesh = build_groups({"fsdp_parallel_num": fsdp, "data_parallel_num": 1, "pipeline_parallel_stages": pp},
+                            rank, world, world)
+        stage, shard = mesh.stage, mesh.shard_idx
+        ref = torch.load(os.path.join(ref_dir, f"ref_{rank}.pt"))
+        assert (ref["stage"], ref["shard"]) == (stage, shard)
+        V, S, D, L, H, E, FF, B, STEPS = 512, 64, 64, 2, 4, 4, 128, 4, 4
+        model = TransformerLMPipelined(V, S, D, L, H, stage, pp, num_expert_per_node=E // fsdp, d_ff=FF,
+                                       dp_group=mesh.group("fsdp"), moe_compute_dtype=torch.bfloat16)
+        model.load_state_dict(ref["init"])
+        wrapped = FSDPWrapperPipelined(model, mesh.group("fsdp"), None, compute_dtype=torch.float32,
+                                       expert_grad_dtype=torch.bfloat16, expert_state_dtype=torch.bfloat16)
+        optimizer = AdamW(wrapped.parameters(), lr=1e-3, betas=(0.9, 0.999), weight_decay=0.01)
+        rng = np.random.default_rng(shard)
+        losses = []
+        for _ in range(STEPS):
+            x = y = None
+            if stage in (0, pp - 1):
+                x, y = get_batch(None, B, S, "cpu", rng=rng, vocab_size=V, mock_data=True)
+            loss = pipelined_train_overlap(wrapped, optimizer, x if stage == 0 else None,
+                                           y if stage == pp - 1 else None, [B, S, D], 2, stage, cross_entropy,
+                                           dtype=torch.float32, device=torch.device("cpu"),
+                                           pp_group=mesh.group("pp"), dp_group=mesh.group("data"))
+            losses.append(float(loss))
+        final = {k: v.detach().float().clone() for k, v in wrapped.state_dict().items()}
+        torch.save({"losses": losses, "final": final, "ref_losses": ref["losses"], "ref_final": ref["final"],
+                    "stage": stage}, os.path.join(result_dir, f"mine_{rank}.pt"))
+    except Exception:
+        with open(os.path.join(result_dir, f"err_{rank}.txt"), "w") as f:
+            f.write(traceback.format_exc())
+        raise
+    finally:
+        dist.destroy_process_group()

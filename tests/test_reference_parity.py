@@ -95,3 +95,40 @@ def test_tiny_model_matches_reference(tmp_path, free_port):
     resumed_by_ref = torch.load(back)
     assert resumed_by_ref["iteration"] == 6
     assert resumed_by_ref["loss7"] == pytest.approx(mine7, abs=3e-3)
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "implementation")), reason="reference not installed")
+@pytest.mark.parametrize("world,pp", [(2, 1), (4, 2)])
+def test_multi_rank_training_matches_reference(tmp_path, free_port, world, pp):
+    """FSDP2 x EP2 (and PP2) on gloo: the unmodified reference and this framework start from the same per-rank
+    state, see the same batches and must produce the same losses and, after four optimizer steps, the same
+    parameter shards (same checkpoint keys) on every rank."""
+    import torch.multiprocessing as mp
+
+    import _workers as W
+    ref_dir = tmp_path / "ref"
+    ref_dir.mkdir()
+    env = {k: v for k, v in os.environ.items() if k != "PYTHONPATH"}
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "_ref_oracle_multi.py"), REF, str(ref_dir),
+                               str(free_port), str(world), str(pp), str(rank)], env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.PIPE, text=True) for rank in range(world)]
+    for proc in procs:
+        _, err = proc.communicate(timeout=900)
+        assert proc.returncode == 0, err[-3000:]
+    mine_dir = tmp_path / "mine"
+    mine_dir.mkdir()
+    mp.spawn(W.run_reference_layout, args=(world, free_port + 1, str(mine_dir), pp, str(ref_dir)), nprocs=world,
+             join=True)
+    checked = 0
+    for rank in range(world):
+        out = torch.load(mine_dir / f"mine_{rank}.pt")
+        if out["stage"] == pp - 1:
+            assert out["losses"] == pytest.approx(out["ref_losses"], abs=5e-3), (rank, out["losses"], out["ref_losses"])
+        assert set(out["final"]) == set(out["ref_final"])
+        for key, want in out["ref_final"].items():
+            got = out["final"][key]
+            assert got.shape == want.shape, key
+            rel = float((got - want).norm() / (want.norm() + 1e-12))
+            assert rel < 2e-2, (rank, key, rel)
+            checked += 1
+    assert checked >= 20 * world // pp
