@@ -53,6 +53,16 @@ if mode == "train":
             grads = {n: p.grad.detach().float().clone() for n, p in wrapped.named_parameters() if p.grad is not None}
     save_checkpoint(wrapped, optimizer, 6, out_path + ".ckpt")
     torch.save({"init": init, "losses": losses, "grads": grads, "loss7": one_step()}, out_path)
+elif mode == "aux":
+    # two steps with the router auxiliary loss switched on and the metrics dictionary returned
+    rows = []
+    for _ in range(2):
+        x, y = get_batch(None, 4, 256, "cpu", rng=rng, vocab_size=1024, mock_data=True)
+        metrics = pipelined_train_overlap(wrapped, optimizer, x, y, [4, 256, 128], 2, 0, cross_entropy,
+                                          dtype=torch.float32, device=torch.device("cpu"), pp_group=group,
+                                          dp_group=group, router_aux_loss_coef=0.05, return_metrics=True)
+        rows.append({k: float(v) for k, v in metrics.items()})
+    torch.save({"metrics": rows}, out_path)
 else:
     # resume from a checkpoint written by the other framework with the reference's own loader, run step seven
     from implementation.train_utils import load_checkpoint_async_dist  # noqa: E402

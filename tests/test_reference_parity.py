@@ -98,6 +98,39 @@ def test_tiny_model_matches_reference(tmp_path, free_port):
 
 
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "implementation")), reason="reference not installed")
+def test_router_auxiliary_loss_and_metrics_match_reference(tmp_path, free_port):
+    """``router_aux_loss_coef`` and ``return_metrics`` of the pipeline step: task, auxiliary and total loss of two
+    steps against the reference (the auxiliary term also steers the second step through its gradient)."""
+    env = {k: v for k, v in os.environ.items() if k != "PYTHONPATH"}
+    base, aux = tmp_path / "base.pt", tmp_path / "aux.pt"
+    for out, mode in ((base, "train"), (aux, "aux")):
+        proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "_ref_oracle.py"), REF, str(out),
+                               str(free_port), mode], env=env, capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+    init, want = torch.load(base)["init"], torch.load(aux)["metrics"]
+    from b200moe.models import TransformerLMPipelined
+    from b200moe.ops.functional import cross_entropy
+    from b200moe.optim import AdamW
+    from b200moe.parallel import FSDPWrapperPipelined, pipelined_train_overlap
+    from b200moe.utils.data import get_batch
+    model = TransformerLMPipelined(1024, 256, 128, 2, 4, 0, 1, num_expert_per_node=4, d_ff=256,
+                                   moe_compute_dtype=torch.bfloat16)
+    model.load_state_dict(init)
+    wrapped = FSDPWrapperPipelined(model, compute_dtype=torch.float32, expert_grad_dtype=torch.bfloat16,
+                                   expert_state_dtype=torch.bfloat16)
+    optimizer = AdamW(wrapped.parameters(), lr=3e-4, betas=(0.9, 0.999), weight_decay=0.01)
+    rng = np.random.default_rng(0)
+    for step in range(2):
+        x, y = get_batch(None, 4, 256, "cpu", rng=rng, vocab_size=1024, mock_data=True)
+        got = pipelined_train_overlap(wrapped, optimizer, x, y, [4, 256, 128], 2, 0, cross_entropy,
+                                      dtype=torch.float32, device=torch.device("cpu"), router_aux_loss_coef=0.05,
+                                      return_metrics=True)
+        assert set(got) == set(want[step])
+        for key, value in want[step].items():
+            assert float(got[key]) == pytest.approx(value, abs=3e-3), (step, key)
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "implementation")), reason="reference not installed")
 @pytest.mark.parametrize("world,pp", [(2, 1), (4, 2)])
 def test_multi_rank_training_matches_reference(tmp_path, free_port, world, pp):
     """FSDP2 x EP2 (and PP2) on gloo: the unmodified reference and this framework start from the same per-rank
