@@ -165,3 +165,101 @@ def test_multi_rank_training_matches_reference(tmp_path, free_port, world, pp):
             assert rel < 2e-2, (rank, key, rel)
             checked += 1
     assert checked >= 20 * world // pp
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "implementation")), reason="reference not installed")
+def test_host_side_utilities_match_reference(tmp_path):
+    """Data sampling (bit-exact batches and generator state), learning-rate schedule, rank layout, configuration
+    validation verdicts, elementwise statements, the AdamW rule and checkpoint discovery: the reference's outputs
+    for a fixed set of inputs against this framework's own functions."""
+    import copy
+
+    import yaml
+    out = tmp_path / "utils.pt"
+    env = {k: v for k, v in os.environ.items() if k != "PYTHONPATH"}
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "_ref_oracle_utils.py"), REF, str(out),
+                           str(tmp_path)], env=env, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    ref = torch.load(out, weights_only=False)
+    from b200moe import config as cfg
+    from b200moe.ops.functional import cross_entropy, silu, softmax
+    from b200moe.optim import AdamW
+    from b200moe.topology import parallel_rank_groups, parallel_sizes
+    from b200moe.utils.checkpoint import latest_checkpoint
+    from b200moe.utils.data import get_batch
+    from b200moe.utils.schedule import learning_rate_schedule_wrapper
+    # data
+    tokens = (np.arange(5000, dtype=np.int64) * 7) % 1000
+    rng = np.random.default_rng(11)
+    calls = (dict(mock_data=True, vocab_size=1000), dict(), dict(start_idx=100), dict(serial_sampling=True, start_idx=64),
+             dict(serial_sampling=True, start_idx=4900), dict(mock_data=True, vocab_size=17))
+    for kwargs, (want_x, want_y) in zip(calls, ref["batches"]):
+        x, y = get_batch(None if kwargs.get("mock_data") else tokens, 6, 32, "cpu", rng=rng, **kwargs)
+        assert x.dtype == want_x.dtype and torch.equal(x, want_x) and torch.equal(y, want_y), kwargs
+    mine_state, ref_state = rng.bit_generator.state, ref["rng_after"]
+    assert mine_state["state"] == ref_state["state"]
+    # schedule
+    sched = learning_rate_schedule_wrapper(0.01, 0.0001, 50, 400)
+    assert [sched(t) for t in (0, 1, 25, 49, 50, 51, 200, 399, 400, 401, 10000)] == pytest.approx(ref["lr"], rel=1e-12)
+    # rank layout
+    for (fsdp, ddp, pp, world, local), want in ref["layouts"].items():
+        train = {"fsdp_parallel_num": fsdp, "data_parallel_num": ddp, "pipeline_parallel_stages": pp}
+        try:
+            got = parallel_rank_groups(train, world, local)
+        except ValueError:
+            got = "ValueError"
+        assert got == want, (fsdp, ddp, pp, world, local)
+    assert parallel_sizes({"data_parallel_num": 4}) == tuple(ref["legacy_sizes"])
+    # validation verdicts on the same mutations of the same (reference) configuration file
+    with open(os.path.join(REF, "configs", "run_config.yaml"), encoding="utf-8") as handle:
+        base = yaml.safe_load(handle)
+    mutations = {
+        "unchanged": lambda c: None,
+        "batch_100": lambda c: c["train"].__setitem__("batch_size", 100),
+        "info_src_8": lambda c: c["general"].__setitem__("info_src", 8),
+        "d_model_4100": lambda c: c["model"].__setitem__("d_model", 4100),
+        "ctx_8190": lambda c: c["model"].__setitem__("context_len", 8190),
+        "warmup_after_cosine": lambda c: c["train"]["learning_rate_scheduler"].__setitem__("t_w", 30000),
+        "two_nodes": lambda c: c["general"].__setitem__("n_workers", 16),
+        "vocab_odd": lambda c: c["data"].__setitem__("vocab_size", 32001),
+        "layers_0": lambda c: c["model"].__setitem__("num_layers", 0),
+        "heads_24": lambda c: c["model"].__setitem__("num_head", 24),
+        "one_expert": lambda c: (c["model"].__setitem__("num_expert_per_node", 1),
+                                 c["train"].__setitem__("fsdp_parallel_num", 1),
+                                 c["train"].__setitem__("pipeline_parallel_stages", 8)),
+        "cpu_device": lambda c: c["general"].__setitem__("device", "cpu"),
+        "bool_batch": lambda c: c["train"].__setitem__("batch_size", True),
+    }
+    assert set(mutations) == set(ref["validation"])
+    for name, mutate in mutations.items():
+        config = copy.deepcopy(base)
+        mutate(config)
+        try:
+            cfg.validate_config(config, allow_cpu=False)      # the reference's GPU-only rule
+            verdict = "ok"
+        except ValueError:
+            verdict = "ValueError"
+        assert verdict == ref["validation"][name], name
+    # elementwise statements and AdamW
+    torch.manual_seed(5)
+    logits = torch.randn(7, 13) * 3
+    assert torch.allclose(softmax(logits, -1), ref["softmax"], atol=1e-7)
+    assert torch.allclose(silu(logits), ref["silu"], atol=1e-7)
+    assert torch.allclose(cross_entropy(logits, torch.randint(0, 13, (7,))), ref["cross_entropy"], atol=1e-6)
+    adam = ref["adamw"]
+    p = torch.nn.Parameter(adam["start"].clone())
+    opt = AdamW([p], lr=0.01, betas=(0.9, 0.95), weight_decay=0.1)
+    for g in adam["grads"]:
+        p.grad = g.clone()
+        opt.step()
+    assert torch.allclose(p.detach(), adam["end"], atol=1e-6)
+    state = opt.state_dict()
+    assert sorted(state["state"][0].keys()) == adam["state_keys"]
+    assert sorted(k for k in state["param_groups"][0] if k != "params") == adam["group_keys"]
+    assert state["param_groups"][0]["t"] == adam["t"]
+    # checkpoint discovery on the tree the oracle prepared
+    root = tmp_path / "checkpoint"
+    found = {"any": latest_checkpoint(root, 2, 2), "first_run": latest_checkpoint(root, 2, 2, run="20240101000000000000"),
+             "none": latest_checkpoint(root, 4, 2)}
+    got = {k: (None if v is None else os.path.relpath(str(v), root)) for k, v in found.items()}
+    assert got == ref["discovery"]
