@@ -343,33 +343,23 @@ __global__ void __launch_bounds__(THREADS, 1) ag_gemm_kernel(const __grid_consta
 
 using namespace b2;
 
-extern "C" {
-
-// y[M,N] = x[M,K] * W[N,K]^T with W row-sharded over ``n`` ranks.  ``seg_rows``: rows of each of the ``num_seg``
-// stacked segments of W (their sum is N; each a multiple of n).  ``w_peers``/``sig``: MAX_RANKS device addresses
-// (each rank's copy of W, each rank's signal pad).  ``block_flags``: int32 [ceil(N/256)] in local memory, zeroed
-// once at allocation; ``flag_epoch`` counts the launches that used it (1 for the first).  Every launch with the
-// same counters must use the same grid, which is the SM count.  Returns -20 when the device cannot co-schedule
-// one CTA per SM (the caller then gathers and multiplies separately).
-int b2_ag_gemm_nt(const void* x, const unsigned long long* w_peers, void* y, int M, int N, int K, long long ldx,
-                  long long ldy, const int* seg_rows, int num_seg, int n, int rank, const unsigned long long* sig,
-                  int sig_slot, int seq, int* block_flags, int flag_epoch, int* status, cudaStream_t stream) {
-  if (N % 32 || K % 8 || n < 1 || n > MAX_RANKS || rank < 0 || rank >= n || num_seg < 1 || num_seg > ag::MAX_SEG ||
+// Host side of the schedule: row ownership from the segment sizes, then the order in which column blocks are
+// computed and copied — blocks whose rows are all mine first, then the others starting after my last own block, so
+// that the ranks do not all read the same peer rows at the same time.  Returns non-zero for an invalid layout.
+static int plan_blocks(ag::Params& p, const int* seg_rows, int num_seg, int n, int rank, int N) {
+  if (n < 1 || n > MAX_RANKS || rank < 0 || rank >= n || num_seg < 1 || num_seg > ag::MAX_SEG || N < 1 ||
       (N + ag::BN - 1) / ag::BN > ag::MAX_BLOCKS)
-    return -10;
-  ag::Params p{};
-  p.M = M; p.N = N; p.K = K; p.n = n; p.rank = rank; p.num_seg = num_seg;
+    return -1;
+  p.N = N; p.n = n; p.rank = rank; p.num_seg = num_seg; p.n_local = 0;
   int row = 0;
   for (int s = 0; s < num_seg; ++s) {
-    if (seg_rows[s] <= 0 || seg_rows[s] % n) return -10;
+    if (seg_rows[s] <= 0 || seg_rows[s] % n) return -1;
     p.seg_begin[s] = row;
     p.seg_shard[s] = seg_rows[s] / n;
     row += seg_rows[s];
   }
-  if (row != N) return -10;
+  if (row != N) return -1;
   p.seg_begin[num_seg] = N;
-  // column blocks whose rows are all mine first, then the others starting after my last own block, so that the
-  // ranks do not all read the same peer rows at the same time
   const int n_tiles = (N + ag::BN - 1) / ag::BN;
   int others[ag::MAX_BLOCKS], n_others = 0, last_local = -1;
   for (int b = 0; b < n_tiles; ++b) {
@@ -387,6 +377,39 @@ int b2_ag_gemm_nt(const void* x, const unsigned long long* w_peers, void* y, int
   int start = 0;
   while (start < n_others && others[start] < last_local) ++start;
   for (int i = 0; i < n_others; ++i) p.order[p.n_local + i] = static_cast<unsigned char>(others[(start + i) % n_others]);
+  return 0;
+}
+
+extern "C" {
+
+// The schedule of ``b2_ag_gemm_nt`` for one rank, computed on the host without touching a device (for tests and
+// tools): ``order_out`` [ceil(N/256)] column blocks in launch order, ``n_local_out`` how many of them need no peer
+// rows, ``owner_out`` (optional) [N] the rank that owns each row.  Returns non-zero for an invalid layout.
+int b2_ag_gemm_plan(const int* seg_rows, int num_seg, int n, int rank, int N, int* order_out, int* n_local_out,
+                    int* owner_out) {
+  ag::Params p{};
+  if (plan_blocks(p, seg_rows, num_seg, n, rank, N)) return -10;
+  const int n_tiles = (N + ag::BN - 1) / ag::BN;
+  for (int i = 0; i < n_tiles; ++i) order_out[i] = p.order[i];
+  *n_local_out = p.n_local;
+  if (owner_out)
+    for (int r = 0; r < N; ++r) owner_out[r] = ag::owner_of_row(p, r);
+  return 0;
+}
+
+// y[M,N] = x[M,K] * W[N,K]^T with W row-sharded over ``n`` ranks.  ``seg_rows``: rows of each of the ``num_seg``
+// stacked segments of W (their sum is N; each a multiple of n).  ``w_peers``/``sig``: MAX_RANKS device addresses
+// (each rank's copy of W, each rank's signal pad).  ``block_flags``: int32 [ceil(N/256)] in local memory, zeroed
+// once at allocation; ``flag_epoch`` counts the launches that used it (1 for the first).  Every launch with the
+// same counters must use the same grid, which is the SM count.  Returns -20 when the device cannot co-schedule
+// one CTA per SM (the caller then gathers and multiplies separately).
+int b2_ag_gemm_nt(const void* x, const unsigned long long* w_peers, void* y, int M, int N, int K, long long ldx,
+                  long long ldy, const int* seg_rows, int num_seg, int n, int rank, const unsigned long long* sig,
+                  int sig_slot, int seq, int* block_flags, int flag_epoch, int* status, cudaStream_t stream) {
+  if (N % 32 || K % 8) return -10;
+  ag::Params p{};
+  p.M = M; p.K = K;
+  if (plan_blocks(p, seg_rows, num_seg, n, rank, N)) return -10;
   for (int i = 0; i < MAX_RANKS; ++i) {
     p.w.ptr[i] = i < n ? reinterpret_cast<void*>(w_peers[i]) : nullptr;
     p.sig.ptr[i] = i < n ? reinterpret_cast<void*>(sig[i]) : nullptr;

@@ -359,6 +359,24 @@ def ag_gemm_grid() -> int:
     return int(require().b2_ag_gemm_grid())
 
 
+def ag_gemm_plan(segments, world: int, rank: int):
+    """Host-only: the schedule ``ag_gemm_nt`` uses for ``rank``.  Returns ``(order, n_local, owner)``: the column
+    blocks (256 rows of ``W`` each) in launch order, how many of them (the leading ones) need no peer rows, and the
+    owning rank of every row.  Needs no GPU."""
+    segments = [int(v) for v in segments]
+    total = sum(segments)
+    blocks = (total + 255) // 256
+    seg = (ctypes.c_int * len(segments))(*segments)
+    order = (ctypes.c_int * max(blocks, 1))()
+    owner = (ctypes.c_int * max(total, 1))()
+    n_local = ctypes.c_int(0)
+    rc = require().b2_ag_gemm_plan(seg, _I(len(segments)), _I(world), _I(rank), _I(total), order,
+                                   ctypes.byref(n_local), owner)
+    if rc != 0:
+        raise ValueError(f"invalid row layout for the all-gather GEMM (code {rc})")
+    return list(order[:blocks]), int(n_local.value), list(owner[:total])
+
+
 def ag_gemm_nt(x, w_ptrs, n_rows: int, segments, world: int, rank: int, sig_ptrs, sig_slot: int, seq: int,
                block_flags, flag_epoch: int):
     """``x [M,K] @ W [n_rows,K]ᵀ`` where ``W`` is row-sharded over ``world`` ranks: ``w_ptrs`` holds every rank's

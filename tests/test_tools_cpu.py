@@ -208,3 +208,42 @@ def test_status_watchdog_reports_to_the_loop_and_exits_when_the_loop_is_stuck():
     with pytest.raises(RuntimeError):
         dog.raise_if_failed()
     dog.stop()
+
+
+def test_allgather_gemm_schedule_on_the_host():
+    """The native host code that orders the column blocks of the all-gather + GEMM kernel: every block exactly once,
+    the blocks whose weight rows all belong to this rank first, peers' blocks rotated so that ranks start on
+    different peers; row ownership follows the per-segment sharding (a fused q/k/v weight has three segments)."""
+    from b200moe.ops import native
+    try:
+        native.require()
+    except RuntimeError as error:
+        pytest.skip(str(error))
+    cases = [([6144], 2), ([4096, 1024, 1024], 2), ([4096, 1024, 1024], 4), ([1984], 2), ([32000], 8),
+             ([1024, 512, 512, 384], 4), ([256], 2), ([512], 1)]
+    for segments, world in cases:
+        total = sum(segments)
+        blocks = (total + 255) // 256
+        want_owner = []
+        for rows in segments:
+            want_owner += [r // (rows // world) for r in range(rows)]
+        firsts = []
+        for rank in range(world):
+            order, n_local, owner = native.ag_gemm_plan(segments, world, rank)
+            assert owner == want_owner
+            assert sorted(order) == list(range(blocks))
+            local = [b for b in range(blocks) if all(o == rank for o in want_owner[b * 256:(b + 1) * 256])]
+            assert order[:n_local] == local
+            rest = order[n_local:]
+            if rest:
+                # the peers' blocks keep their cyclic order, starting after this rank's last own block
+                base = [b for b in range(blocks) if b not in local]
+                shift = base.index(rest[0])
+                assert rest == base[shift:] + base[:shift]
+                assert not local or rest[0] > local[-1] or all(b < local[-1] for b in base)
+                firsts.append(rest[0])
+        if world > 1 and blocks >= 2 * world and len(segments) == 1:
+            assert len(set(firsts)) == world          # every rank starts copying from a different block
+    for bad in (([100], 3), ([0], 2), ([256 * 200], 2)):
+        with pytest.raises(ValueError):
+            native.ag_gemm_plan(bad[0], bad[1], 0)
