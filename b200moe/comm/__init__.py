@@ -106,14 +106,25 @@ class GroupComm:
 
 
 class Comm:
-    def __init__(self, mesh, device):
+    def __init__(self, mesh, device, multicast: bool = False, wait_seconds: float | None = None):
+        """``multicast``: let the symmetric-memory rendezvous bind buffers to an NVSwitch multicast address (only
+        the NVLS all-reduce uses it).  Off by default: a process that dies while bound raises NVLink faults on the
+        other ranks' GPUs, and nothing else here needs the binding.  ``wait_seconds``: budget of every cross-GPU
+        wait inside the kernels (``native.set_wait_seconds``)."""
+        import os
         native.require()
+        self.multicast = bool(multicast)
+        if not self.multicast:
+            # read by the symmetric-memory allocator at its first rendezvous in this process
+            os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
+        seconds = os.environ.get("B200MOE_WAIT_SECONDS") or wait_seconds
+        if seconds is not None:
+            native.set_wait_seconds(float(seconds))
         self.mesh = mesh
         self.device = device
         self.status = native.status_word(device)
         self.fsdp = GroupComm(mesh.group("fsdp"), device) if mesh.fsdp > 1 else None
         self.ddp = GroupComm(mesh.group("ddp"), device) if mesh.ddp > 1 else None
-        import os
         self.capacity_mode = os.environ.get("B200MOE_EP_CAPACITY", "exact")
         self.capacity_bucket = int(os.environ.get("B200MOE_EP_BUCKET", "4096"))
         self._symm = {}
@@ -121,6 +132,37 @@ class Comm:
         self._ar_stage = {}
         self._ag_state = {}
         self._entries = {}
+
+    # -- lifetime ------------------------------------------------------------------------
+    def buffers(self):
+        """Every symmetric buffer this object owns."""
+        found = list(self._symm.values()) + list(self._ar_stage.values())
+        for g in (self.fsdp, self.ddp):
+            if g is not None:
+                found.append(g.sig)
+        for ctx in self._ep.values():
+            found.extend(ctx.buffers())
+        return found
+
+    def any_multicast(self) -> bool:
+        """True while any symmetric buffer of this process is bound to a multicast address."""
+        return any(getattr(b, "mc_ptr", 0) for b in self.buffers())
+
+    def release(self) -> None:
+        """Let go of every symmetric buffer (call between steps, before the process leaves on an error path, so
+        that peers never see a mapping disappear under a kernel).  The object is unusable afterwards."""
+        try:
+            torch.cuda.synchronize(self.device)
+        except Exception:
+            pass
+        for b in self.buffers():
+            b.mc_ptr = 0
+            b.handle = None
+            b.tensor = None
+        self._symm.clear()
+        self._ar_stage.clear()
+        self._ep.clear()
+        self.fsdp = self.ddp = None
 
     # -- allocation ----------------------------------------------------------------------
     def alloc_flat(self, numel: int, dtype):
@@ -371,6 +413,21 @@ class EPContext:
         hint[0].copy_(meta, non_blocking=True)
         hint[1].record()
 
+    def buffers(self):
+        out = [self.counts_all, self.fwd_ret, self.bwd_ret, self.ret_scalar]
+        for land in (self.fwd_land, self.bwd_land):
+            out += [b for b in (land.rows, land.tag, land.src, land.scalar) if b is not None]
+        return out
+
+    def worst_load(self) -> float:
+        """Rows this rank received in the last call of its busiest layer, relative to a balanced split (from the
+        asynchronous read-backs of the plan kernels; 0 before the first one)."""
+        worst = 0
+        for hint in self._hints.values():
+            if hint[1].query():
+                worst = max(worst, int(hint[0][3]))
+        return worst / self.slots
+
     def dispatch(self, x, idx, key=None) -> Route:
         g, dev = self.g, x.device
         i32 = dict(dtype=torch.int32, device=dev)
@@ -453,5 +510,5 @@ class EPContext:
         return dx, dweights
 
 
-def make_comm(mesh, device) -> Comm:
-    return Comm(mesh, device)
+def make_comm(mesh, device, multicast: bool = False, wait_seconds: float | None = None) -> Comm:
+    return Comm(mesh, device, multicast=multicast, wait_seconds=wait_seconds)

@@ -7,7 +7,7 @@ distributed_parallel_training_pipelined.py:104-131).  Keys this framework adds
 are optional and default to the reference's behaviour:
 
 ``model.rope_theta``            RoPE base, default 10000 (reference layers.py:383)
-``train.activation_recompute``  ``none`` | ``swiglu`` | ``block``
+``train.activation_recompute``  ``none`` | ``swiglu`` | ``block`` | ``auto`` (keep gate/up while HBM has room)
 ``train.router_aux_loss_coef``  passed to the pipeline step (reference validates
                                 it in startup.py:57 but never forwards it)
 ``train.expert_state_dtype``    ``float32`` | ``bfloat16`` AdamW m/v of experts
@@ -114,8 +114,8 @@ def validate_config(config: dict, *, check_data: bool = False, check_cuda: bool 
     sched = train["learning_rate_scheduler"]
     if not 0 <= sched["t_w"] < sched["t_c"]:
         raise ValueError("Scheduler requires 0 <= t_w < t_c")
-    if train.get("activation_recompute", "none") not in ("none", "swiglu", "block"):
-        raise ValueError("train.activation_recompute must be none, swiglu or block")
+    if train.get("activation_recompute", "none") not in ("none", "swiglu", "block", "auto"):
+        raise ValueError("train.activation_recompute must be none, swiglu, block or auto")
     for key in ("expert_state_dtype", "expert_grad_dtype"):
         if train.get(key, "float32") not in ("float32", "bfloat16"):
             raise ValueError(f"train.{key} must be float32 or bfloat16")

@@ -154,9 +154,9 @@ __global__ void __launch_bounds__(THREADS, 1) ag_gemm_kernel(const __grid_consta
           const int* flag = p.block_flags + t.n_tile;
           bool ok = ld_acquire_gpu(flag) - flag_target >= 0;
           if (!ok) {
-            const long long start = clock64();
+            const Deadline deadline;
             while (!(ok = ld_acquire_gpu(flag) - flag_target >= 0)) {
-              if (clock64() - start > COMM_WAIT_CYCLES) break;
+              if (deadline.expired()) break;
               __nanosleep(200);
             }
           }
@@ -201,9 +201,14 @@ __global__ void __launch_bounds__(THREADS, 1) ag_gemm_kernel(const __grid_consta
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool failed = false;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          // the producer may be waiting for a peer copy (bounded by COMM_WAIT_CYCLES), so allow several budgets
+          // the producer may be waiting for a peer copy (bounded by the cross-GPU wait budget): keep waiting in
+          // mbarrier-budget slices until that budget, plus a slice, is over
           bool got = false;
-          for (int tries = 0; tries < 6 && !got && !*abort_flag; ++tries) got = mbar_wait(&full_bar[stage], phase);
+          const Deadline deadline;
+          while (!got && !*abort_flag) {
+            got = mbar_wait(&full_bar[stage], phase);
+            if (!got && deadline.expired()) break;
+          }
           if (!got) {
             failed = true;
             break;
@@ -244,7 +249,11 @@ __global__ void __launch_bounds__(THREADS, 1) ag_gemm_kernel(const __grid_consta
       bool local;
       const Tile t = decode(p, tile, m_tiles, n_tiles, &local);
       bool got = false;
-      for (int tries = 0; tries < 8 && !got && !*abort_flag; ++tries) got = mbar_wait(&tmem_full[acc], acc_phase);
+      const Deadline deadline;
+      while (!got && !*abort_flag) {
+        got = mbar_wait(&tmem_full[acc], acc_phase);
+        if (!got && deadline.expired()) break;
+      }
       if (!got) {
         if (!*abort_flag) atomicExch(p.status, 305);
         *abort_flag = 1;
@@ -287,7 +296,7 @@ __global__ void __launch_bounds__(THREADS, 1) ag_gemm_kernel(const __grid_consta
       }
       const int* my_sig = static_cast<const int*>(p.sig.ptr[p.rank]);
       for (int src = 0; src < p.n; ++src) {
-        if (src != p.rank && !wait_one(my_sig, p.sig_slot, src, p.seq)) {
+        if (src != p.rank && !wait_one(my_sig, p.sig_slot, src, p.seq, p.status)) {
           atomicExch(p.status, 306);
           *copy_ok = 0;
         }
@@ -449,3 +458,5 @@ int b2_ag_gemm_grid() {
 }
 
 }  // extern "C"
+
+B2_DEFINE_WAIT_SETTER(b2_ag_gemm_file_set_wait_ns)

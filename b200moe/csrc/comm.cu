@@ -25,12 +25,18 @@
 
 namespace b2 {
 
-// Block-wide: threads 0..n-1 each wait for one source, then everyone proceeds.
-__device__ __forceinline__ void block_wait_all(const int* my_sig, int slot, int n, int seq, int* status, int code) {
+// Block-wide: threads 0..n-1 each wait for one source, then everyone proceeds.  Returns (to every thread of the
+// block) whether all sources arrived; on failure ``code`` is in the status word and the caller skips whatever
+// depended on the peers.
+__device__ __forceinline__ bool block_wait_all(const int* my_sig, int slot, int n, int seq, int* status, int code) {
+  int ok = 1;
   if (threadIdx.x < n) {
-    if (!wait_one(my_sig, slot, threadIdx.x, seq)) atomicExch(status, code);
+    if (!wait_one(my_sig, slot, threadIdx.x, seq, status)) {
+      atomicCAS(status, 0, code);
+      ok = 0;
+    }
   }
-  __syncthreads();
+  return __syncthreads_and(ok) != 0;
 }
 
 struct alignas(16) vec16 {
@@ -106,7 +112,21 @@ __global__ void __launch_bounds__(PLAN_THREADS) ep_plan_kernel(const EpPlanArgs 
   __syncthreads();
   if (tid == 0) signal_all(a.sig, a.sig_slot, a.rank, a.ep, a.seq);
   const int* my_sig = static_cast<const int*>(a.sig.ptr[a.rank]);
-  block_wait_all(my_sig, a.sig_slot, a.ep, a.seq, a.status, 101);
+  if (!block_wait_all(my_sig, a.sig_slot, a.ep, a.seq, a.status, 101)) {
+    // a peer's counts never came: plan nothing (no tiles, no rows, every slot unsent) instead of using stale counts
+    if (tid == 0) {
+      a.meta[0] = 0; a.meta[1] = 0; a.meta[2] = 1; a.meta[3] = 0;
+    }
+    if (tid < e_local) {
+      a.offs[tid] = 0;
+      a.seg_live_end[tid] = 0;
+    }
+    for (int s = s0; s < s1; ++s) {
+      a.slot_row[s] = -1;
+      a.slot_dest[s] = -1;
+    }
+    return;
+  }
   if (tid < a.ep * E) {
     const int src = tid / E, e = tid - src * E;
     all_counts[src][e] = ld_acquire_sys(static_cast<const int*>(a.counts_all.ptr[a.rank]) + src * MAX_EXPERTS + e);
@@ -226,7 +246,7 @@ struct EpConsumeArgs {
 };
 
 __global__ void __launch_bounds__(256) ep_consume_kernel(const EpConsumeArgs a) {
-  block_wait_all(a.my_sig, a.sig_slot, a.n, a.seq, a.status, 103);
+  if (!block_wait_all(a.my_sig, a.sig_slot, a.n, a.seq, a.status, 103)) return;   // rows of a peer are missing
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int live_rows = min(a.meta[1], a.capacity);
   for (int r = blockIdx.x * 8 + warp; r < live_rows; r += gridDim.x * 8) {
@@ -276,7 +296,7 @@ __global__ void __launch_bounds__(256) ep_consume_kernel(const EpConsumeArgs a) 
 
 // One block: wait for every peer's flag in ``sig_slot`` (placed before a kernel that reads landed data).
 __global__ void ep_wait_kernel(const int* my_sig, int sig_slot, int n, int seq, int* status) {
-  block_wait_all(my_sig, sig_slot, n, seq, status, 104);
+  block_wait_all(my_sig, sig_slot, n, seq, status, 104);   // on failure the status word tells the host
 }
 
 // ------------------------------------------------------------------ replica all-reduce
@@ -291,32 +311,38 @@ struct ArArgs {
   int* status;
 };
 
-// Grid barrier across GPUs: block 0 announces arrival; every block waits for all ranks.
-__device__ __forceinline__ void gpu_barrier_enter(const ArArgs& a, int slot) {
+// Grid barrier across GPUs: block 0 announces arrival; every block waits for all ranks.  Returns false (to the
+// whole block) when a rank did not arrive in time: the caller must then touch neither its own state nor a peer's.
+__device__ __forceinline__ bool gpu_barrier_enter(const ArArgs& a, int slot) {
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     __threadfence_system();
     signal_all(a.sig, slot, a.rank, a.n, a.seq);
   }
-  block_wait_all(static_cast<const int*>(a.sig.ptr[a.rank]), slot, a.n, a.seq, a.status, 105);
+  return block_wait_all(static_cast<const int*>(a.sig.ptr[a.rank]), slot, a.n, a.seq, a.status, 105);
 }
-// Leave: the last block to finish tells the peers and waits until every peer has finished too.
-__device__ __forceinline__ void gpu_barrier_leave(const ArArgs& a, int slot) {
+// Leave: the last block to finish tells the peers and waits until every peer has finished too.  With ``entered``
+// false (the enter barrier failed) only the block counter is restored: the peers are not told that this rank is
+// done, because it has not done its part, and they run into their own budget.
+__device__ __forceinline__ void gpu_barrier_leave(const ArArgs& a, int slot, bool entered = true) {
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
     const unsigned int old = atomicInc(a.counter, gridDim.x - 1);
-    if (old == gridDim.x - 1) {
+    if (old == gridDim.x - 1 && entered) {
       signal_all(a.sig, slot, a.rank, a.n, a.seq);
       const int* my_sig = static_cast<const int*>(a.sig.ptr[a.rank]);
       for (int src = 0; src < a.n; ++src)
-        if (!wait_one(my_sig, slot, src, a.seq)) atomicExch(a.status, 106);
+        if (!wait_one(my_sig, slot, src, a.seq, a.status)) atomicCAS(a.status, 0, 106);
     }
   }
 }
 
 // One-shot: every rank reads all copies and writes the sum to a private output.
 __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const ArArgs a, float* out) {
-  gpu_barrier_enter(a, a.sig_slot);
+  if (!gpu_barrier_enter(a, a.sig_slot)) {
+    gpu_barrier_leave(a, a.sig_slot + 1, false);
+    return;
+  }
   const long long vecs = a.count / 4;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < vecs;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -333,7 +359,10 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const ArArgs a, 
 
 // Two-shot, in place: rank r reduces chunk r from all copies and stores the result into every copy.
 __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(const ArArgs a) {
-  gpu_barrier_enter(a, a.sig_slot);
+  if (!gpu_barrier_enter(a, a.sig_slot)) {
+    gpu_barrier_leave(a, a.sig_slot + 1, false);
+    return;
+  }
   const long long vecs = a.count / 4;
   const long long chunk = (vecs + a.n - 1) / a.n;
   const long long lo = chunk * a.rank, hi = min(vecs, lo + chunk);
@@ -352,7 +381,10 @@ __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(const ArArgs a) 
 
 // NVLS, in place: the switch sums the copies (multimem.ld_reduce) and broadcasts the result (multimem.st).
 __global__ void __launch_bounds__(512) allreduce_nvls_kernel(const ArArgs a) {
-  gpu_barrier_enter(a, a.sig_slot);
+  if (!gpu_barrier_enter(a, a.sig_slot)) {
+    gpu_barrier_leave(a, a.sig_slot + 1, false);
+    return;
+  }
   const long long vecs = a.count / 4;
   const long long chunk = (vecs + a.n - 1) / a.n;
   const long long lo = chunk * a.rank, hi = min(vecs, lo + chunk);
@@ -398,16 +430,85 @@ struct FsdpArgs {
   int* status;
 };
 
+// One AdamW step on a value and its moments (the reference's rule, implementation/optimizer.py:29-39).
+__device__ __forceinline__ float adamw_one(const FsdpArgs& a, float p, float g, float& m, float& v) {
+  p *= 1.f - a.lr * a.wd;
+  m = a.beta1 * m + (1.f - a.beta1) * g;
+  v = a.beta2 * v + (1.f - a.beta2) * g * g;
+  return p - a.a_t * m / (sqrtf(v) + a.eps);
+}
+
+// Gradients cross NVLink as 16-byte fp32 vectors (peer loads), new weights as 16-byte vectors of eight bf16
+// (peer stores); entries whose offsets or sizes are not multiples of eight elements take the scalar loop.
 __global__ void __launch_bounds__(512) fsdp_step_kernel(const FsdpArgs a) {
   ArArgs bar{};
   bar.sig = a.sig; bar.rank = a.rank; bar.n = a.n; bar.seq = a.seq; bar.counter = a.counter; bar.status = a.status;
-  gpu_barrier_enter(bar, a.sig_slot);   // every rank has finished accumulating its gradients
+  // every rank has finished accumulating its gradients; if one never says so, this rank neither reduces nor
+  // updates (master weights and moments stay as they were) and does not report completion to the others
+  if (!gpu_barrier_enter(bar, a.sig_slot)) {
+    gpu_barrier_leave(bar, a.sig_slot + 1, false);
+    return;
+  }
   const float inv = 1.f / a.n;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
   for (int e = 0; e < a.num_entries; ++e) {
     const FsdpEntry ent = a.entries[e];
     const long long full_base = ent.full_off + ent.shard_numel * a.rank;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < ent.shard_numel;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const bool everyone = !(ent.local_only && !a.push_all);
+    if (((full_base | ent.shard_off | ent.shard_numel) & 7) == 0) {
+      for (long long i = tid * 8; i < ent.shard_numel; i += nthreads * 8) {
+        const long long si = ent.shard_off + i;
+        float g[8];
+        if (a.do_reduce) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] = 0.f;
+          for (int p = 0; p < a.n; ++p) {
+            const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(a.full_g.ptr[p]) + full_base + i);
+            const float4 lo = src[0], hi = src[1];
+            g[0] += lo.x; g[1] += lo.y; g[2] += lo.z; g[3] += lo.w;
+            g[4] += hi.x; g[5] += hi.y; g[6] += hi.z; g[7] += hi.w;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] *= inv;
+          float4* sg = reinterpret_cast<float4*>(a.shard_grad + si);
+          sg[0] = make_float4(g[0], g[1], g[2], g[3]);
+          sg[1] = make_float4(g[4], g[5], g[6], g[7]);
+        } else {
+          const float4* sg = reinterpret_cast<const float4*>(a.shard_grad + si);
+          const float4 lo = sg[0], hi = sg[1];
+          g[0] = lo.x; g[1] = lo.y; g[2] = lo.z; g[3] = lo.w; g[4] = hi.x; g[5] = hi.y; g[6] = hi.z; g[7] = hi.w;
+        }
+        if (a.do_update) {
+          float4* pm = reinterpret_cast<float4*>(a.master + si);
+          float4* mm = reinterpret_cast<float4*>(a.m + si);
+          float4* vm = reinterpret_cast<float4*>(a.v + si);
+          float pv[8], mv[8], vv[8];
+          *reinterpret_cast<float4*>(pv) = pm[0]; *reinterpret_cast<float4*>(pv + 4) = pm[1];
+          *reinterpret_cast<float4*>(mv) = mm[0]; *reinterpret_cast<float4*>(mv + 4) = mm[1];
+          *reinterpret_cast<float4*>(vv) = vm[0]; *reinterpret_cast<float4*>(vv + 4) = vm[1];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) pv[j] = adamw_one(a, pv[j], g[j], mv[j], vv[j]);
+          pm[0] = *reinterpret_cast<float4*>(pv); pm[1] = *reinterpret_cast<float4*>(pv + 4);
+          mm[0] = *reinterpret_cast<float4*>(mv); mm[1] = *reinterpret_cast<float4*>(mv + 4);
+          vm[0] = *reinterpret_cast<float4*>(vv); vm[1] = *reinterpret_cast<float4*>(vv + 4);
+          vec16 w;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(pv[2 * j], pv[2 * j + 1]);
+            w.v[j] = *reinterpret_cast<const uint32_t*>(&b);
+          }
+          if (everyone) {
+            for (int p = 0; p < a.n; ++p)
+              *reinterpret_cast<vec16*>(static_cast<__nv_bfloat16*>(a.full_w.ptr[p]) + full_base + i) = w;
+          } else {
+            *reinterpret_cast<vec16*>(static_cast<__nv_bfloat16*>(a.full_w.ptr[a.rank]) + full_base + i) = w;
+          }
+        }
+      }
+      continue;
+    }
+    for (long long i = tid; i < ent.shard_numel; i += nthreads) {
       const long long si = ent.shard_off + i;
       float g;
       if (a.do_reduce) {
@@ -419,18 +520,16 @@ __global__ void __launch_bounds__(512) fsdp_step_kernel(const FsdpArgs a) {
         g = a.shard_grad[si];
       }
       if (a.do_update) {
-        float pv = a.master[si] * (1.f - a.lr * a.wd);
-        const float mv = a.beta1 * a.m[si] + (1.f - a.beta1) * g;
-        const float vv = a.beta2 * a.v[si] + (1.f - a.beta2) * g * g;
-        pv -= a.a_t * mv / (sqrtf(vv) + a.eps);
+        float mv = a.m[si], vv = a.v[si];
+        const float pv = adamw_one(a, a.master[si], g, mv, vv);
         a.master[si] = pv;
         a.m[si] = mv;
         a.v[si] = vv;
         const __nv_bfloat16 wb = __float2bfloat16_rn(pv);
-        if (ent.local_only && !a.push_all) {
-          static_cast<__nv_bfloat16*>(a.full_w.ptr[a.rank])[full_base + i] = wb;
-        } else {
+        if (everyone) {
           for (int p = 0; p < a.n; ++p) static_cast<__nv_bfloat16*>(a.full_w.ptr[p])[full_base + i] = wb;
+        } else {
+          static_cast<__nv_bfloat16*>(a.full_w.ptr[a.rank])[full_base + i] = wb;
         }
       }
     }
@@ -442,21 +541,54 @@ __global__ void __launch_bounds__(512) fsdp_step_kernel(const FsdpArgs a) {
 __global__ void __launch_bounds__(512) fsdp_allgather_kernel(const FsdpArgs a) {
   ArArgs bar{};
   bar.sig = a.sig; bar.rank = a.rank; bar.n = a.n; bar.seq = a.seq; bar.counter = a.counter; bar.status = a.status;
-  gpu_barrier_enter(bar, a.sig_slot);
+  if (!gpu_barrier_enter(bar, a.sig_slot)) {
+    gpu_barrier_leave(bar, a.sig_slot + 1, false);
+    return;
+  }
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
   for (int e = 0; e < a.num_entries; ++e) {
     const FsdpEntry ent = a.entries[e];
     const long long full_base = ent.full_off + ent.shard_numel * a.rank;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < ent.shard_numel;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const bool everyone = !(ent.local_only && !a.push_all);
+    if (((full_base | ent.shard_off | ent.shard_numel) & 7) == 0) {
+      for (long long i = tid * 8; i < ent.shard_numel; i += nthreads * 8) {
+        const float4* pm = reinterpret_cast<const float4*>(a.master + ent.shard_off + i);
+        const float4 lo = pm[0], hi = pm[1];
+        const __nv_bfloat162 b0 = __floats2bfloat162_rn(lo.x, lo.y), b1 = __floats2bfloat162_rn(lo.z, lo.w);
+        const __nv_bfloat162 b2v = __floats2bfloat162_rn(hi.x, hi.y), b3 = __floats2bfloat162_rn(hi.z, hi.w);
+        vec16 w;
+        w.v[0] = *reinterpret_cast<const uint32_t*>(&b0); w.v[1] = *reinterpret_cast<const uint32_t*>(&b1);
+        w.v[2] = *reinterpret_cast<const uint32_t*>(&b2v); w.v[3] = *reinterpret_cast<const uint32_t*>(&b3);
+        if (everyone) {
+          for (int p = 0; p < a.n; ++p)
+            *reinterpret_cast<vec16*>(static_cast<__nv_bfloat16*>(a.full_w.ptr[p]) + full_base + i) = w;
+        } else {
+          *reinterpret_cast<vec16*>(static_cast<__nv_bfloat16*>(a.full_w.ptr[a.rank]) + full_base + i) = w;
+        }
+      }
+      continue;
+    }
+    for (long long i = tid; i < ent.shard_numel; i += nthreads) {
       const __nv_bfloat16 wb = __float2bfloat16_rn(a.master[ent.shard_off + i]);
-      if (ent.local_only && !a.push_all) {
-        static_cast<__nv_bfloat16*>(a.full_w.ptr[a.rank])[full_base + i] = wb;
-      } else {
+      if (everyone) {
         for (int p = 0; p < a.n; ++p) static_cast<__nv_bfloat16*>(a.full_w.ptr[p])[full_base + i] = wb;
+      } else {
+        static_cast<__nv_bfloat16*>(a.full_w.ptr[a.rank])[full_base + i] = wb;
       }
     }
   }
   gpu_barrier_leave(bar, a.sig_slot + 1);
+}
+
+static int device_sms() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return sms;
 }
 
 static inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : -1; }
@@ -466,6 +598,19 @@ static inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : -1
 using namespace b2;
 
 extern "C" {
+
+int b2_ag_gemm_file_set_wait_ns(long long ns);
+int b2_comm_file_set_wait_ns(long long ns);
+int b2_moe_ep_file_set_wait_ns(long long ns);
+
+// Budget, in nanoseconds of the device-wide clock, of every cross-GPU wait in this library's kernels on the
+// current device (default 10 s).  Returns non-zero if a file's copy of the setting could not be written.
+int b2_comm_set_wait_ns(long long ns) {
+  int rc = b2_comm_file_set_wait_ns(ns);
+  if (!rc) rc = b2_ag_gemm_file_set_wait_ns(ns);
+  if (!rc) rc = b2_moe_ep_file_set_wait_ns(ns);
+  return rc;
+}
 
 int b2_comm_max_ranks() { return MAX_RANKS; }
 int b2_comm_max_experts() { return MAX_EXPERTS; }
@@ -510,7 +655,7 @@ int b2_ep_push(const void* src, const int* row_of, const int* dest_of, const int
   a.dest_capacity = dest_capacity; a.rank = rank; a.n = n; a.seq = seq; a.sig_slot = sig_slot;
   a.land = table(land); a.land_tag = table(land_tag); a.land_src = table(land_src);
   a.land_scalar = table(land_scalar); a.sig = table(sig); a.counter = counter;
-  ep_push_kernel<<<148 * 8, 256, 0, s>>>(a);
+  ep_push_kernel<<<device_sms() * 8, 256, 0, s>>>(a);
   return launched();
 }
 
@@ -525,7 +670,7 @@ int b2_ep_consume(const void* land, const int* land_tag, const int* land_src, co
   a.y_perm = static_cast<const __nv_bfloat16*>(y_perm); a.ret_scalar = table(ret_scalar);
   a.out = static_cast<__nv_bfloat16*>(out); a.row_tag = row_tag; a.row_src = row_src; a.my_sig = my_sig; a.D = D;
   a.capacity = capacity; a.n = n; a.seq = seq; a.sig_slot = sig_slot; a.status = status;
-  ep_consume_kernel<<<148 * 4, 256, 0, s>>>(a);
+  ep_consume_kernel<<<device_sms() * 4, 256, 0, s>>>(a);
   return launched();
 }
 
@@ -544,7 +689,7 @@ int b2_comm_allreduce(const unsigned long long* buf, const unsigned long long* s
   a.sig_slot = sig_slot; a.count = count; a.scale = scale; a.counter = counter; a.status = status;
   const long long vecs = count / 4;
   int blocks = static_cast<int>((vecs + 511) / 512);
-  blocks = blocks < 1 ? 1 : (blocks > 148 * 2 ? 148 * 2 : blocks);
+  blocks = blocks < 1 ? 1 : (blocks > device_sms() * 2 ? device_sms() * 2 : blocks);
   if (kind == 0) allreduce_oneshot_kernel<<<blocks, 512, 0, s>>>(a, out);
   else if (kind == 1) allreduce_twoshot_kernel<<<blocks, 512, 0, s>>>(a);
   else if (kind == 2 && mc) allreduce_nvls_kernel<<<blocks, 512, 0, s>>>(a);
@@ -566,11 +711,12 @@ int b2_fsdp_step(const unsigned long long* full_g, const unsigned long long* ful
   a.do_reduce = mode == 0 || mode == 1;
   a.do_update = mode == 1 || mode == 2;
   a.push_all = push_all;
-  if (mode == 3) fsdp_allgather_kernel<<<148 * 2, 512, 0, s>>>(a);
-  else fsdp_step_kernel<<<148 * 2, 512, 0, s>>>(a);
+  if (mode == 3) fsdp_allgather_kernel<<<device_sms() * 2, 512, 0, s>>>(a);
+  else fsdp_step_kernel<<<device_sms() * 2, 512, 0, s>>>(a);
   return launched();
 }
 
 }  // extern "C"
 
 B2_DEFINE_DEBUG_READER(b2_comm_debug_read)
+B2_DEFINE_WAIT_SETTER(b2_comm_file_set_wait_ns)

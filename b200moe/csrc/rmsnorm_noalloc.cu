@@ -151,6 +151,12 @@ extern "C" int b2_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float
   if (!dy || !x || !w || !rstd || !dx || !dw) return -1;
   if (rows < 1 || D < 8 || D % 8) return -2;
   if (D > B2_NOALLOC_MAX_D) return -3;
+  // the kernels move eight bf16 per 16-byte access: a pointer off that grid would fault on the device
+  const uintptr_t wide = reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) |
+                         reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(residual);
+  const uintptr_t narrow = reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(rstd) |
+                           reinterpret_cast<uintptr_t>(dw);
+  if ((wide & 15) || (narrow & 3)) return -8;
   float* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc) return rc;
@@ -158,8 +164,10 @@ extern "C" int b2_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float
   bwd_rows_kernel<<<parts, THREADS, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), w, rstd,
       static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(dx), scratch, rows, D);
+  // cudaPeekAtLastError: report this launch without consuming an error some earlier, unrelated call left behind
+  if (cudaPeekAtLastError() != cudaSuccess) return -7;
   sum_parts_kernel<<<(D + 255) / 256, 256, 0, stream>>>(scratch, dw, parts, D);
-  return cudaGetLastError() == cudaSuccess ? 0 : -7;
+  return cudaPeekAtLastError() == cudaSuccess ? 0 : -7;
 }
 
 extern "C" const char* b2_rmsnorm_bwd_noalloc_strerror(int code) {
@@ -171,7 +179,8 @@ extern "C" const char* b2_rmsnorm_bwd_noalloc_strerror(int code) {
     case -4: return "cudaGetDevice failed";
     case -5: return "device ordinal beyond the 64 this library tracks";
     case -6: return "cudaGetSymbolAddress failed for the built-in scratch";
-    case -7: return "kernel launch failed";
+    case -7: return "kernel launch failed (or an earlier CUDA error is still pending on this thread)";
+    case -8: return "dy, x, dx and residual must be 16-byte aligned, w, rstd and dw 4-byte aligned";
     default: return "unknown code";
   }
 }

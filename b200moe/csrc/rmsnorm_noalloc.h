@@ -23,6 +23,11 @@
 //     the last call left in it.  Nothing in it has to start at zero: each call
 //     overwrites every element it later reads.  Two calls that overlap on the
 //     GPU (different streams, no ordering between them) race on it; order them.
+//   * dy, x, dx and (when given) residual are dense row-major [rows, D] bf16 (row pitch exactly D elements) and
+//     start on a 16-byte boundary: the kernels move eight bf16 per access.  w, rstd and dw are 4-byte aligned.
+//     A pointer off that grid is refused with code -8 before any launch; it never reaches the device.
+//   * dx may be the same buffer as residual (each element is read before it is written by the same thread).
+//     dx must not alias dy or x.
 //   * It calls no cudaMalloc, cudaFree or other allocating routine.
 #pragma once
 #include <cuda_runtime.h>

@@ -248,6 +248,7 @@ class MoELayerMulti(nn.Module):
         self.experts = GroupedPositionWiseFFLayer(num_expert_per_node, d_model, d_ff, device=device, dtype=dtype)
         self.router = LinearLayer(d_model, self.world_size * num_expert_per_node, device=device)
         self.recompute = False
+        self.budget = None  # parallel.memory.ActivationBudget of the stage (set by the trainer), or None
         self.comm = None  # peer-memory communication layer, set by the FSDP wrapper (fused backend)
 
     def forward(self, x, return_aux_loss=False):
@@ -260,7 +261,7 @@ class MoELayerMulti(nn.Module):
             ep_ctx = self.comm.ep_context(flat.shape[0], flat.shape[1], self.world_size * self.num_expert_per_node)
         out = ops.moe_ffn(flat, weights, idx, self.experts.w1, self.experts.w2, self.experts.w3,
                           group=self.dp_group if self.world_size > 1 else None,
-                          recompute=self.recompute, ep_ctx=ep_ctx, key=id(self))
+                          recompute=self.recompute, ep_ctx=ep_ctx, key=id(self), budget=self.budget)
         out = out.view(shape).to(in_dtype)
         if return_aux_loss:
             from ..ops.moe import aux_loss_from

@@ -37,7 +37,7 @@ def _wgrad(dy, x, param, offs, num_experts):
 
 class _MoEFused(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weights, idx, w1, w2, w3, recompute, ep_ctx, key):
+    def forward(ctx, x, weights, idx, w1, w2, w3, recompute, ep_ctx, key, budget):
         tokens, dim = x.shape
         experts = w1.shape[0]
         x = x.contiguous()
@@ -52,6 +52,14 @@ class _MoEFused(torch.autograd.Function):
             cap, offs, tile_expert, meta, x_perm = route.cap, route.offs, route.tile_expert, route.meta, route.x_perm
             slot_row = row_slot = None
         tiles = meta[0:1]
+        # what this call keeps for its backward pass: the permuted input and the expert outputs always, the
+        # gate/up pre-activations while the stage's activation budget has room for them
+        ledger = None
+        if budget is not None and any(ctx.needs_input_grad):
+            ledger = (cap * dim * 4, cap * w1.shape[1] * 4)
+            kept = budget.enter(*ledger)
+            recompute = recompute or not kept
+            ledger += (not recompute,)
         h, gate, up = native.gemm_swiglu(x_perm, w1, w3, tile_expert, tiles, save_gate_up=not recompute, align256=True)
         y_perm = native.gemm_nt(h, w2, tile_expert=tile_expert, num_m_tiles=tiles, num_experts=experts, align256=True)
         if ep_ctx is None:
@@ -60,6 +68,7 @@ class _MoEFused(torch.autograd.Function):
             out = ep_ctx.combine(route, y_perm, weights, tokens)
         ctx.params = (w1, w2, w3)
         ctx.meta_py = (tokens, dim, experts, cap, recompute, ep_ctx, route)
+        ctx.budget, ctx.ledger = budget, ledger
         saved = [x_perm, y_perm, weights, offs, tile_expert, meta]
         if ep_ctx is None:
             saved += [slot_row, row_slot]
@@ -103,10 +112,13 @@ class _MoEFused(torch.autograd.Function):
             dx = native.moe_combine(dx_perm, slot_row, None, tokens)
         else:
             dx, dweights = ep_ctx.dispatch_backward(route, dx_perm, tokens)
-        return dx, dweights, None, dw1, dw2, dw3, None, None, None
+        if ctx.ledger is not None:
+            ctx.budget.leave(*ctx.ledger)
+        return dx, dweights, None, dw1, dw2, dw3, None, None, None, None
 
 
-def moe_ffn_fused(x, weights, idx, w1, w2, w3, ep_ctx=None, recompute: bool = False, key=None):
+def moe_ffn_fused(x, weights, idx, w1, w2, w3, ep_ctx=None, recompute: bool = False, key=None, budget=None):
     """``key`` names the calling layer; the expert-parallel context keeps one
-    capacity hint per key."""
-    return _MoEFused.apply(x, weights, idx, w1, w2, w3, recompute, ep_ctx, key if key is not None else id(w1))
+    capacity hint per key.  ``budget`` (``parallel.memory.ActivationBudget``): when given, the call keeps its
+    gate/up pre-activations only while the budget has room and rebuilds them in the backward pass otherwise."""
+    return _MoEFused.apply(x, weights, idx, w1, w2, w3, recompute, ep_ctx, key if key is not None else id(w1), budget)

@@ -108,6 +108,19 @@ def debug_records(clear: bool = False) -> dict:
     return found
 
 
+def set_wait_seconds(seconds: float) -> None:
+    """Budget of every cross-GPU wait inside this library's kernels on the current device (default 10 s).  A wait
+    that runs out makes its kernel skip the dependent work, set the status word and return."""
+    rc = require().b2_comm_set_wait_ns(ctypes.c_longlong(int(float(seconds) * 1e9)))
+    if rc != 0:
+        raise RuntimeError(f"b2_comm_set_wait_ns failed with code {rc}")
+
+
+def clear_status(device=None) -> None:
+    """Reset the status word after a reported failure has been handled (tests; a trainer restarts instead)."""
+    status_word(device).zero_()
+
+
 def check_status() -> int:
     """Synchronising read of the status word; raises if a kernel gave up (or, in the checked build, if a kernel
     recorded an out-of-range index)."""

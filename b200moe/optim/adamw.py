@@ -71,6 +71,16 @@ class AdamW(torch.optim.Optimizer):
                 state["v"] = torch.zeros_like(p, dtype=dtype)
         return state["m"], state["v"]
 
+    def materialize_state(self) -> int:
+        """Allocate the moments of every parameter now instead of at the first ``step`` (they are zeros either
+        way), so that whoever plans the remaining device memory sees them.  Returns the bytes they take."""
+        total = 0
+        for group in self.param_groups:
+            for p in group["params"]:
+                m, v = self._moments(p)
+                total += m.numel() * m.element_size() + v.numel() * v.element_size()
+        return total
+
     @staticmethod
     def _grad_of(p):
         main = getattr(p, "main_grad", None)

@@ -313,6 +313,9 @@ class FSDPWrapperPipelined(nn.Module):
     # -- gradients -----------------------------------------------------------------------
     @torch.no_grad()
     def clear_grad_accumulators(self):
+        budget = getattr(self, "activation_budget", None)
+        if budget is not None:
+            budget.reset()      # start of a step: no activation of the previous one is alive
         self.flat.full_g.zero_()
         for p in self.sharded_params + self.replicated_params:
             p.grad = None

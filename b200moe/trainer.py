@@ -59,7 +59,12 @@ def build_model(config: dict, mesh, device, fsdp_group, ddp_group, compute_dtype
         d_ff=model_cfg["d_ff"], theta=model_cfg.get("rope_theta", 10000), dp_group=fsdp_group,
         moe_compute_dtype=moe_dtype)
     model.to(device)
-    recompute = train_cfg.get("activation_recompute", "none")
+    # ``train.activation_recompute``: ``none`` keeps every activation (the reference's behaviour), ``swiglu``
+    # rebuilds the experts' gate/up pre-activations in the backward pass, ``block`` re-runs whole blocks, ``auto``
+    # (the default on a GPU) keeps gate/up while the stage's activation budget has room (parallel/memory.py).
+    recompute = train_cfg.get("activation_recompute") or ("auto" if device.type == "cuda" else "none")
+    if recompute not in ("none", "swiglu", "block", "auto"):
+        raise ValueError("train.activation_recompute must be none, swiglu, block or auto")
     model.block_recompute = recompute == "block"
     # ``train.recompute_layers``: how many blocks (from the front of the stage) rebuild their gate/up
     # activations in the backward pass; an int, or one int per pipeline stage (earlier stages keep more
@@ -82,6 +87,22 @@ def build_model(config: dict, mesh, device, fsdp_group, ddp_group, compute_dtype
     opt_cfg = train_cfg["optimizer"]
     optimizer = AdamW(wrapped.parameters(), lr=train_cfg["learning_rate"],
                       betas=(opt_cfg["beta1"], opt_cfg["beta2"]), weight_decay=opt_cfg["lambda"])
+    wrapped.activation_budget = None
+    if recompute == "auto" and device.type == "cuda":
+        from .parallel.memory import stage_activation_budget
+        optimizer.materialize_state()
+        fsdp, ddp = parallel_sizes(train_cfg)
+        local_batch = train_cfg["batch_size"] // (fsdp * ddp)
+        tokens = local_batch // train_cfg["microbatch_num"] * model_cfg["context_len"]
+        budget = stage_activation_budget(
+            tokens_per_microbatch=tokens, d_model=model_cfg["d_model"], d_ff=model_cfg["d_ff"],
+            num_heads=model_cfg["num_head"], experts_total=model_cfg["num_expert_per_node"] * fsdp, ep=fsdp,
+            blocks=len(model.layers), pp=mesh.pp, stage=mesh.stage, microbatches=train_cfg["microbatch_num"],
+            vocab=data_cfg["vocab_size"], device=device,
+            margin_bytes=int(float(train_cfg.get("activation_margin_gib", 6.0)) * 2 ** 30))
+        for layer in model.layers:
+            layer.ffn.budget = budget
+        wrapped.activation_budget = budget
     return wrapped, optimizer
 
 
@@ -115,9 +136,14 @@ def train(local_rank: int, cluster_rank: int, world_size: int, config: dict):
     resume_dir = ckpt.select_checkpoint(config, rank, info_src)
 
     comm = None
-    if device.type == "cuda" and (config.get("comm") or {}).get("backend", "fused") == "fused":
+    comm_cfg = config.get("comm") or {}
+    recovery = config.get("recovery", {}) or {}
+    if device.type == "cuda" and comm_cfg.get("backend", "fused") == "fused":
         from .comm import make_comm
-        comm = make_comm(mesh, device)
+        # comm.multicast (default off): bind the symmetric buffers to an NVSwitch multicast address, which the NVLS
+        # all-reduce needs.  A process must not die while bound, so self-kill fault injection is refused with it.
+        comm = make_comm(mesh, device, multicast=bool(comm_cfg.get("multicast", False)),
+                         wait_seconds=float(recovery.get("device_wait_seconds", 20.0)))
     model, optimizer = build_model(config, mesh, device, fsdp_group, ddp_group, compute_dtype, comm)
 
     run_id = datetime.now().strftime("%Y%m%d%H%M%S%f")
@@ -156,8 +182,9 @@ def train(local_rank: int, cluster_rank: int, world_size: int, config: dict):
     print_every, save_every = train_cfg["print_loss_interval"], train_cfg["save_interval"]
     ctx_len, d_model, vocab = model_cfg["context_len"], model_cfg["d_model"], data_cfg["vocab_size"]
     aux_coef = train_cfg.get("router_aux_loss_coef", 0.0) if train_cfg.get("use_router_aux_loss", False) else 0.0
-    chaos = ChaosEnginnerTrigger(config.get("chaos_engineering")) if (config.get("chaos_engineering") or {}).get(
-        "wired", True) else ChaosEnginnerTrigger(None)
+    chaos = ChaosEnginnerTrigger(
+        config.get("chaos_engineering") if (config.get("chaos_engineering") or {}).get("wired", True) else None,
+        multicast_bound=(comm.any_multicast if comm is not None else None))
     sink = MetricsSink(general.get("metrics_path")) if rank == info_src else None
     flops_tok = flops_per_token(d_model, model_cfg["d_ff"], model_cfg["num_head"],
                                 model_cfg["num_expert_per_node"] * fsdp_size, vocab,
@@ -168,83 +195,101 @@ def train(local_rank: int, cluster_rank: int, world_size: int, config: dict):
         from .ops import native as _native
         if _native.has("gemm"):
             from .utils.watchdog import StatusWatchdog, device_status_reader
-            recovery = config.get("recovery", {}) or {}
             watchdog = StatusWatchdog(device_status_reader(device),
                                       interval_s=float(recovery.get("status_poll_seconds", 1.0)),
-                                      grace_s=float(recovery.get("status_grace_seconds", 30.0))).start()
+                                      grace_s=float(recovery.get("status_grace_seconds", 30.0)),
+                                      before_exit=(comm.release if comm is not None else None)).start()
             _native.set_nvtx(bool(profiling))
     pp_ranks = dist.get_process_group_ranks(pp_group)
     loss_acc, span_s, span_dev_ms, span_tokens = 0.0, 0.0, 0.0, 0
     pending: list = []
 
-    while iteration < target:
-        if watchdog is not None:
-            watchdog.raise_if_failed()
-        with nvtx_range(f"train_iteration_{iteration}|rank={rank}|pp={stage}|dp={dp_idx}"):
-            x = y = None
-            with nvtx_range("batch_preparation"):
-                if rank in (pp_ranks[0], pp_ranks[-1]):
-                    x, y = get_batch(dataset, local_batch, ctx_len, device, rng=data_rng, vocab_size=vocab,
-                                     validate=data_cfg.get("validate_batches", False), mock_data=mock)
-            with nvtx_range("learning_rate_update"):
-                lr = lr_at(iteration)
-                for group in optimizer.param_groups:
-                    group["lr"] = lr
-            if profiling:
-                with nvtx_range("pre_step_synchronization"):
+    def device_healthy() -> bool:
+        """No kernel of this rank gave up a bounded wait (synchronising read of the status word)."""
+        if watchdog is None:
+            return True
+        from .ops import native
+        return watchdog.code == 0 and int(native.status_word(device).item()) == 0
+
+    try:
+        while iteration < target:
+            if watchdog is not None:
+                watchdog.raise_if_failed()
+            with nvtx_range(f"train_iteration_{iteration}|rank={rank}|pp={stage}|dp={dp_idx}"):
+                x = y = None
+                with nvtx_range("batch_preparation"):
+                    if rank in (pp_ranks[0], pp_ranks[-1]):
+                        x, y = get_batch(dataset, local_batch, ctx_len, device, rng=data_rng, vocab_size=vocab,
+                                         validate=data_cfg.get("validate_batches", False), mock_data=mock)
+                with nvtx_range("learning_rate_update"):
+                    lr = lr_at(iteration)
+                    for group in optimizer.param_groups:
+                        group["lr"] = lr
+                if profiling:
+                    with nvtx_range("pre_step_synchronization"):
+                        if device.type == "cuda":
+                            torch.cuda.synchronize()
+                        dist.barrier()
+                t0 = time.perf_counter()
+                timer.start()
+                with nvtx_range("pipeline_step|forward_backward_p2p_dp_sync_optimizer"):
+                    loss = pipelined_train_overlap(
+                        model, optimizer, x, y, [local_batch, ctx_len, d_model], microbatch_num, stage,
+                        cross_entropy, dtype=compute_dtype, device=device, pp_group=pp_group, dp_group=data_group,
+                        router_aux_loss_coef=aux_coef)
+                reporting = (iteration + 1) % print_every == 0
+                if profiling or reporting:
+                    with nvtx_range("post_step_synchronization"):
+                        span_dev_ms += timer.stop_ms()
                     if device.type == "cuda":
-                        torch.cuda.synchronize()
-                    dist.barrier()
-            t0 = time.perf_counter()
-            timer.start()
-            with nvtx_range("pipeline_step|forward_backward_p2p_dp_sync_optimizer"):
-                loss = pipelined_train_overlap(
-                    model, optimizer, x, y, [local_batch, ctx_len, d_model], microbatch_num, stage,
-                    cross_entropy, dtype=compute_dtype, device=device, pp_group=pp_group, dp_group=data_group,
-                    router_aux_loss_coef=aux_coef)
-            reporting = (iteration + 1) % print_every == 0
-            if profiling or reporting:
-                with nvtx_range("post_step_synchronization"):
-                    span_dev_ms += timer.stop_ms()
-                if device.type == "cuda":
-                    from .ops import native
-                    if native.has("gemm"):
-                        native.check_status()
-            span_s += time.perf_counter() - t0
-            loss_acc = loss_acc + loss
-            span_tokens += batch_size * ctx_len
-            iteration += 1
-            if reporting:
-                if rank == info_src:
-                    print(f"Rank {rank} finishes iteration {iteration}", flush=True)
-                    rate = span_tokens / span_s
-                    print(f"Iterations {iteration - print_every + 1}-{iteration}: processed {span_tokens:,} "
-                          f"tokens in {span_s:.6f} seconds ({rate:,.2f} tokens/s)", flush=True)
-                    if sink is not None:
-                        sink.write(iteration=iteration, tokens=span_tokens, host_seconds=span_s,
-                                   device_ms_last_step=span_dev_ms, tokens_per_s=rate,
-                                   mfu=mfu(rate, flops_tok, world_size))
-                if rank == pp_ranks[-1]:
-                    print(f"Rank {rank} Loss from last {print_every} iterations is {loss_acc / print_every}",
-                          flush=True)
-                    loss_acc = 0.0
-                span_s, span_dev_ms, span_tokens = 0.0, 0.0, 0
-            ckpt.verify_pending_checkpoints(pending, iteration, rank, info_src, device)
-            if iteration % save_every == 0:
-                with nvtx_range("checkpoint_io"):
-                    directory = f"{general['checkpoint_folder']}/checkpoint/{run_id}/{iteration}"
-                    try:
-                        os.makedirs(directory, exist_ok=True)
-                        future = ckpt.save_checkpoint_async_dist(
-                            model, optimizer, iteration, os.path.join(directory, ckpt.shard_name(dp_idx, stage)),
-                            data_rng=data_rng)
-                    except Exception as error:
-                        future = Future()
-                        future.set_exception(error)
-                    pending.append((iteration, directory, future))
-            if len(chaos):
-                chaos.trigger()
-    ckpt.verify_pending_checkpoints(pending, iteration, rank, info_src, device, drain=True)
+                        from .ops import native
+                        if native.has("gemm"):
+                            native.check_status()
+                span_s += time.perf_counter() - t0
+                loss_acc = loss_acc + loss
+                span_tokens += batch_size * ctx_len
+                iteration += 1
+                if reporting:
+                    if rank == info_src:
+                        print(f"Rank {rank} finishes iteration {iteration}", flush=True)
+                        rate = span_tokens / span_s
+                        print(f"Iterations {iteration - print_every + 1}-{iteration}: processed {span_tokens:,} "
+                              f"tokens in {span_s:.6f} seconds ({rate:,.2f} tokens/s)", flush=True)
+                        if sink is not None:
+                            sink.write(iteration=iteration, tokens=span_tokens, host_seconds=span_s,
+                                       device_ms_last_step=span_dev_ms, tokens_per_s=rate,
+                                       mfu=mfu(rate, flops_tok, world_size))
+                    if rank == pp_ranks[-1]:
+                        print(f"Rank {rank} Loss from last {print_every} iterations is {loss_acc / print_every}",
+                              flush=True)
+                        loss_acc = 0.0
+                    span_s, span_dev_ms, span_tokens = 0.0, 0.0, 0
+                ckpt.verify_pending_checkpoints(pending, iteration, rank, info_src, device, healthy=device_healthy)
+                if iteration % save_every == 0:
+                    with nvtx_range("checkpoint_io"):
+                        directory = f"{general['checkpoint_folder']}/checkpoint/{run_id}/{iteration}"
+                        try:
+                            if not device_healthy():      # never stage a state that a failed wait may have damaged
+                                raise RuntimeError("a device-side wait ran out before this checkpoint")
+                            os.makedirs(directory, exist_ok=True)
+                            future = ckpt.save_checkpoint_async_dist(
+                                model, optimizer, iteration, os.path.join(directory, ckpt.shard_name(dp_idx, stage)),
+                                data_rng=data_rng)
+                        except Exception as error:
+                            future = Future()
+                            future.set_exception(error)
+                        pending.append((iteration, directory, future))
+                if len(chaos):
+                    chaos.trigger()
+    except BaseException:
+        # leaving on an error path: stop the watchdog and let go of the peer-mapped buffers first, with no
+        # kernel of this rank in flight, so that the peers never see a mapping vanish under a running kernel
+        if watchdog is not None:
+            watchdog.stop()
+        if comm is not None:
+            comm.release()
+        raise
+    ckpt.verify_pending_checkpoints(pending, iteration, rank, info_src, device, drain=True, healthy=device_healthy)
     release_leaks()
     if watchdog is not None:
         watchdog.stop()

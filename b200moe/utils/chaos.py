@@ -98,13 +98,19 @@ class ChaosEnginnerTrigger:
     """Build closures for every enabled entry of ``chaos_engineering`` and fire
     them all on ``trigger()``.  (The class name keeps the reference's spelling.)"""
 
-    def __init__(self, chaos_config: dict | None):
+    def __init__(self, chaos_config: dict | None, multicast_bound=None):
+        """``multicast_bound``: optional callable telling whether any buffer of this process is bound to an NVLink
+        multicast object.  A process that dies in that state raises NVLink faults on its peers' GPUs, so
+        ``random_kill`` is refused while it returns true."""
         self._triggers = []
         for name, parameters in (chaos_config or {}).items():
-            if not parameters.get("enabled", False):
+            if not isinstance(parameters, dict) or not parameters.get("enabled", False):
                 continue
             if name not in CHAOS_FUNCTIONS:
                 raise ValueError(f"Unknown chaos function: {name}")
+            if name == "random_kill" and multicast_bound is not None and multicast_bound():
+                raise ValueError("chaos_engineering.random_kill is refused while symmetric buffers are bound to an "
+                                 "NVLink multicast object (comm.multicast: true); switch one of them off")
             kwargs = {k: v for k, v in parameters.items() if k != "enabled"}
             self._triggers.append(function_register(CHAOS_FUNCTIONS[name], kwargs))
 

@@ -92,10 +92,14 @@ def select_checkpoint(config: dict, rank: int, info_src: int, group=None):
 
 
 def verify_pending_checkpoints(pending: list, iteration: int, rank: int, info_src: int, device,
-                               drain: bool = False, min_age: int = 5, group=None) -> None:
+                               drain: bool = False, min_age: int = 5, group=None, healthy=None) -> None:
     """Commit saves that are ``min_age`` iterations old (all of them when
     ``drain``): join the writer, agree by ``all_reduce(MIN)`` and let the info
-    rank publish the ``COMMITTED`` marker by rename."""
+    rank publish the ``COMMITTED`` marker by rename.  ``healthy``: optional
+    callable returning a false value when this rank has seen a device-side
+    failure (a bounded kernel wait that ran out) since the save; such a rank
+    votes against the commit, so a state that may already be damaged is never
+    published."""
     import torch.distributed as dist
     while pending and (drain or iteration - pending[0][0] >= min_age):
         saved_iteration, directory, future = pending.pop(0)
@@ -105,6 +109,16 @@ def verify_pending_checkpoints(pending: list, iteration: int, rank: int, info_sr
         except Exception as error:
             ok = 0
             print(f"Rank {rank} checkpoint at iteration {saved_iteration} failed: {error}", flush=True)
+        if ok and healthy is not None:
+            try:
+                fine = bool(healthy())
+            except Exception as error:
+                fine = False
+                print(f"Rank {rank} device status check failed: {error}", flush=True)
+            if not fine:
+                ok = 0
+                print(f"Rank {rank} votes against the checkpoint at iteration {saved_iteration}: a device-side "
+                      f"wait ran out since it was staged", flush=True)
         flag = torch.tensor(ok, dtype=torch.int32, device=device)
         if dist.is_available() and dist.is_initialized():
             dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)

@@ -46,8 +46,11 @@ def device_status_reader(device=None):
 
 class StatusWatchdog:
     def __init__(self, read_status, interval_s: float = 1.0, grace_s: float = 30.0, on_failure=None,
-                 exit_process=os._exit, log=print):
+                 exit_process=os._exit, log=print, before_exit=None):
+        """``before_exit``: optional callable run (errors ignored) right before the process is ended, e.g. to
+        unbind symmetric buffers from their multicast object so that the exit cannot disturb the peers."""
         self._read = read_status
+        self._before_exit = before_exit
         self.interval_s, self.grace_s = float(interval_s), float(grace_s)
         self._on_failure = on_failure
         self._exit = exit_process
@@ -96,5 +99,10 @@ class StatusWatchdog:
             if not self._stop.is_set():
                 self._log(f"[watchdog] training thread did not react within {self.grace_s:.0f} s; "
                           f"exiting with code {WATCHDOG_EXIT_CODE}", flush=True)
+                if self._before_exit is not None:
+                    try:
+                        self._before_exit()
+                    except Exception as error:
+                        self._log(f"[watchdog] release before exit failed: {error}", flush=True)
                 self._exit(WATCHDOG_EXIT_CODE)
             return

@@ -18,6 +18,18 @@ Model per GPU count (layer count scaled so per-GPU work is constant; d_model
 ``tokens_per_s_raw`` and ``mfu`` (of 2.25 PFLOP/s dense bf16 per GPU) are also
 reported.  ``--impl reference`` times the unmodified reference package from
 ``baseline/_ref`` through its own public API on the same configuration.
+
+Both arms run the loop of the reference's ``train()`` (distributed_parallel_
+training_pipelined.py:210-257): every step draws a fresh batch on the host,
+copies it from pinned memory to the device, sets the learning rate from the
+reference's warm-up/cosine schedule (``configs/run_config.yaml``: 0 at iteration
+0, 2e-6 per iteration), runs the pipelined step and reads the loss back.  One
+timed pass gives both numbers: ``ms_per_step`` from CUDA events around the K
+steps, ``e2e`` from the larger of that and the host clock around the same steps.
+
+``--layout`` selects other named configurations on 8 GPUs: ``ddp2`` (PP1 x FSDP4 x
+EP4 x DDP2, 8 blocks, global batch 32, RoPE base 1e6) and ``pp2`` (PP2 x FSDP4 x
+EP4, 32 blocks, global batch 64 in 16 microbatches).
 """
 from __future__ import annotations
 
@@ -34,6 +46,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 BASELINE_TOKENS_PER_S = 75076.0
 MODEL = {"d_model": 4096, "d_ff": 14336, "num_head": 32, "experts": 8, "vocab": 32000, "seq": 8192}
 LAYOUT = {1: (1, 1, 8, 64), 2: (1, 2, 8, 128), 4: (2, 2, 8, 128), 8: (4, 2, 8, 128)}  # pp, fsdp, blocks/stage, batch
+# other named configurations: pp, fsdp, ddp, blocks/stage, global batch, microbatches, rope base
+NAMED = {"ddp2": (1, 4, 2, 8, 32, 4, 1e6), "pp2": (2, 4, 1, 16, 64, 16, 1e4)}
+SCHEDULE = {"a_max": 0.01, "a_min": 0.0001, "t_w": 5000, "t_c": 20000}     # the reference's run_config.yaml
 
 
 def parse_args():
@@ -49,7 +64,7 @@ def parse_args():
     p.add_argument("--seq", type=int, default=MODEL["seq"])
     p.add_argument("--recompute", default=None, choices=["none", "swiglu", "block"])
     p.add_argument("--backend", default=None, choices=["fused", "nccl"])
-    p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--layout", default=None, choices=sorted(NAMED), help="a named 8-GPU configuration")
     return p.parse_args()
 
 
@@ -102,13 +117,20 @@ class ClockSampler:
 
 
 def run_config(args):
-    if args.gpus not in LAYOUT:
-        raise SystemExit(f"--gpus must be one of {sorted(LAYOUT)}")
-    pp, fsdp, blocks, batch = LAYOUT[args.gpus]
+    if args.layout:
+        pp, fsdp, ddp, blocks, batch, microbatches, theta = NAMED[args.layout]
+        if args.gpus != pp * fsdp * ddp:
+            raise SystemExit(f"--layout {args.layout} needs --gpus {pp * fsdp * ddp}")
+    else:
+        if args.gpus not in LAYOUT:
+            raise SystemExit(f"--gpus must be one of {sorted(LAYOUT)}")
+        pp, fsdp, blocks, batch = LAYOUT[args.gpus]
+        ddp, microbatches, theta = 1, args.microbatches, 1e4
     blocks = args.layers or blocks
     batch = args.batch or batch
-    return {"pp": pp, "fsdp": fsdp, "ddp": 1, "blocks_per_stage": blocks, "batch": batch,
-            "microbatches": args.microbatches, "seq": args.seq, "experts_per_rank": MODEL["experts"] // fsdp}
+    return {"pp": pp, "fsdp": fsdp, "ddp": ddp, "blocks_per_stage": blocks, "batch": batch,
+            "microbatches": microbatches, "seq": args.seq, "experts_per_rank": MODEL["experts"] // fsdp,
+            "rope_theta": theta}
 
 
 def init_dist(args, timeout_s=None):
@@ -129,8 +151,11 @@ def init_dist(args, timeout_s=None):
     return rank, world, local, device
 
 
-def measure(step_device, step_e2e, args, device, rank, launches_fn):
-    """Warm up, then time K device-only steps and K end-to-end steps."""
+def measure(step, args, device, rank, launches_fn):
+    """``warmup`` untimed steps, then ``steps`` timed ones in ONE pass.  ``step(i)`` is a whole iteration of the
+    training loop: host batch -> pinned memory -> device, learning rate, pipelined step, loss read back.  Returns
+    device ms per step (CUDA events, max over ranks), end-to-end ms per step (the larger of the events and the
+    host clock around the same steps, max over ranks), the clock record, launches and the last loss."""
     import torch
     import torch.distributed as dist
 
@@ -139,40 +164,50 @@ def measure(step_device, step_e2e, args, device, rank, launches_fn):
         dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step_device()
+    for i in range(args.warmup):
+        step(i)
     fence()
     sampler = ClockSampler(device.index) if rank == 0 else None
     if sampler:
         sampler.start()
     launches_before = launches_fn()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
     begin.record()
     last = None
-    for _ in range(args.steps):
-        last = step_device()
+    for i in range(args.steps):
+        last = step(args.warmup + i)
     end.record()
     fence()
+    wall = (time.perf_counter() - t0) * 1e3
     launches = launches_fn() - launches_before
     clocks = sampler.stop() if sampler else None
-    ms = torch.tensor([begin.elapsed_time(end)], dtype=torch.float64, device=device)
+    events = begin.elapsed_time(end)
+    ms = torch.tensor([events, max(events, wall)], dtype=torch.float64, device=device)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    device_ms = float(ms.item()) / args.steps
-    e2e_ms = None
-    if step_e2e is not None:
-        step_e2e()
-        fence()
-        begin.record()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            last = step_e2e()
-        end.record()
-        fence()
-        wall = (time.perf_counter() - t0) * 1e3
-        ms = torch.tensor([max(begin.elapsed_time(end), wall)], dtype=torch.float64, device=device)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        e2e_ms = float(ms.item()) / args.steps
+    device_ms, e2e_ms = (float(v) / args.steps for v in ms.tolist())
     return device_ms, e2e_ms, clocks, launches, last
+
+
+def say_failure(impl, args, error, detail=""):
+    """First failing rank of a run: one line that names the exception (stderr for people, a JSON line on stdout
+    for the reference arm, whose contract is an ``unavailable`` line), then leave non-zero without waiting in
+    collective teardown for peers, so that torchrun ends them at once."""
+    rank = int(os.environ.get("RANK", "0"))
+    text = str(error).strip().splitlines()
+    reason = f"{type(error).__name__}: {text[0][:300] if text else ''}"
+    print(f"[bench {impl}, rank {rank}] {reason} {detail}".rstrip(), file=sys.stderr, flush=True)
+    marker = os.path.join("/tmp", f"b200moe_bench_failed_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}")
+    try:
+        os.close(os.open(marker, os.O_CREAT | os.O_EXCL | os.O_WRONLY))
+        first = True
+    except OSError:
+        first = False          # another rank already reported; its line is the root cause
+    if first and impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": f"rank {rank}: {reason}", "n_gpus": args.gpus}),
+              flush=True)
+    # a lone reference process reports and ends normally; under torchrun a non-zero code ends the peers
+    os._exit(0 if impl == "reference" and int(os.environ.get("WORLD_SIZE", "1")) == 1 else 1)
 
 
 def report(args, cfg, device_ms, e2e_ms, clocks, launches, loss, h2d, d2h, impl, extra=None):
@@ -201,7 +236,10 @@ def report(args, cfg, device_ms, e2e_ms, clocks, launches, loss, h2d, d2h, impl,
                             f"8 experts top-2, vocab 32000)",
                    "global_batch": cfg["batch"], "seq_len": cfg["seq"], "microbatches": cfg["microbatches"],
                    "parallelism": f"pp{cfg['pp']}·fsdp{cfg['fsdp']}·ep{cfg['fsdp']}·ddp{cfg['ddp']}",
-                   "blocks_total": blocks_total,
+                   "blocks_total": blocks_total, "layout": args.layout or "scaling",
+                   "rope_theta": cfg["rope_theta"],
+                   "loop": "fresh host batch + H2D from pinned memory, lr from the reference's warm-up schedule, "
+                           "pipelined step, loss read back: every step, warm-up included",
                    "l2": "no flush: every step streams >20 GB of weights and activations (inputs larger than L2)"},
         "clocks": clocks, "gpu_launches": launches,
     }
@@ -219,85 +257,102 @@ def bench_b200moe(args):
     import torch
     import torch.distributed as dist
     sys.path.insert(0, ROOT)
-    rank, world, local, device = init_dist(args)
-    from b200moe.ops import native
-    from b200moe.ops.functional import cross_entropy
-    from b200moe.parallel import pipelined_train_overlap
-    from b200moe.topology import build_groups
-    from b200moe.trainer import build_model
-    from b200moe.utils.data import BatchStager
-    cfg = run_config(args)
-    recompute = args.recompute or ("none" if cfg["pp"] <= 2 else "swiglu")   # 4 microbatches in flight on stage 0
-    single = args.gpus == 1
-    config = {
-        "general": {"device": "gpu", "n_workers": world, "gpu_per_node": world, "info_src": 0},
-        "data": {"vocab_size": MODEL["vocab"], "mock_data": True, "seed": 42},
-        "model": {"num_head": MODEL["num_head"], "d_model": MODEL["d_model"], "d_ff": MODEL["d_ff"],
-                  "context_len": cfg["seq"], "num_layers": cfg["blocks_per_stage"],
-                  "num_expert_per_node": cfg["experts_per_rank"], "rope_theta": 10000},
-        "comm": {"backend": args.backend or "fused"},
-        "train": {"fsdp_parallel_num": cfg["fsdp"], "data_parallel_num": 1, "pipeline_parallel_stages": cfg["pp"],
-                  "microbatch_num": cfg["microbatches"], "batch_size": cfg["batch"], "learning_rate": 1e-4,
-                  "optimizer": {"beta1": 0.9, "beta2": 0.999, "lambda": 0.01},
-                  "activation_recompute": recompute,
-                  # 1F1B keeps pp - stage microbatches alive: only the early stages have to drop activations
-                  "recompute_layers": [4, 2, 0, 0] if cfg["pp"] == 4 and args.recompute is None else None,
-                  # one GPU holds all 8 experts of 8 blocks (11.3 G parameters): moments and gradient
-                  # accumulators use the reference's bf16 there; fp32 everywhere else
-                  "expert_state_dtype": "bfloat16" if single else "float32",
-                  "expert_grad_dtype": "bfloat16" if single else "float32"},
-    }
-    mesh = build_groups(config["train"], rank, world, world)
-    comm = None
-    if config["comm"]["backend"] == "fused" and native.has("comm"):
-        from b200moe.comm import make_comm
-        comm = make_comm(mesh, device)
-    torch.manual_seed(1234 + mesh.stage)
-    model, optimizer = build_model(config, mesh, device, mesh.group("fsdp"), mesh.group("ddp"), torch.bfloat16, comm)
-    local_batch = cfg["batch"] // (cfg["fsdp"] * cfg["ddp"])
-    stager = BatchStager(local_batch, cfg["seq"], device)
-    rng = np.random.default_rng(42 + mesh.dp_idx)
-    edge = mesh.stage in (0, mesh.pp - 1)
-    fixed = stager.next(None, rng, MODEL["vocab"], mock_data=True) if edge else (None, None)
-    fixed = tuple(t.clone() if t is not None else None for t in fixed)
-    spec = [local_batch, cfg["seq"], MODEL["d_model"]]
+    state = {}
+    try:
+        rank, world, local, device = init_dist(args)
+        from b200moe.ops import native
+        from b200moe.ops.functional import cross_entropy
+        from b200moe.parallel import pipelined_train_overlap
+        from b200moe.topology import build_groups
+        from b200moe.trainer import build_model
+        from b200moe.utils.data import BatchStager
+        from b200moe.utils.schedule import learning_rate_schedule_wrapper
+        cfg = run_config(args)
+        single = args.gpus == 1
+        config = {
+            "general": {"device": "gpu", "n_workers": world, "gpu_per_node": world, "info_src": 0},
+            "data": {"vocab_size": MODEL["vocab"], "mock_data": True, "seed": 42},
+            "model": {"num_head": MODEL["num_head"], "d_model": MODEL["d_model"], "d_ff": MODEL["d_ff"],
+                      "context_len": cfg["seq"], "num_layers": cfg["blocks_per_stage"],
+                      "num_expert_per_node": cfg["experts_per_rank"], "rope_theta": cfg["rope_theta"]},
+            "comm": {"backend": args.backend or "fused"},
+            "train": {"fsdp_parallel_num": cfg["fsdp"], "data_parallel_num": cfg["ddp"],
+                      "pipeline_parallel_stages": cfg["pp"], "microbatch_num": cfg["microbatches"],
+                      "batch_size": cfg["batch"], "learning_rate": 1e-4,
+                      "optimizer": {"beta1": 0.9, "beta2": 0.999, "lambda": 0.01},
+                      # the trainer decides per MoE call, from the HBM it has left, whether the gate/up
+                      # pre-activations are kept or rebuilt in the backward pass
+                      "activation_recompute": args.recompute or "auto",
+                      # one GPU holds all 8 experts of 8 blocks (11.3 G parameters): moments and gradient
+                      # accumulators use the reference's bf16 there; fp32 everywhere else
+                      "expert_state_dtype": "bfloat16" if single else "float32",
+                      "expert_grad_dtype": "bfloat16" if single else "float32"},
+        }
+        mesh = build_groups(config["train"], rank, world, world)
+        comm = None
+        if config["comm"]["backend"] == "fused" and native.has("comm"):
+            from b200moe.comm import make_comm
+            comm = make_comm(mesh, device)
+        state["comm"] = comm
+        torch.manual_seed(1234 + mesh.stage)
+        model, optimizer = build_model(config, mesh, device, mesh.group("fsdp"), mesh.group("ddp"), torch.bfloat16,
+                                       comm)
+        width = cfg["fsdp"] * cfg["ddp"]
+        local_batch = cfg["batch"] // width
+        stager = BatchStager(local_batch, cfg["seq"], device)
+        rng = np.random.default_rng(42 + mesh.dp_idx)
+        edge = mesh.stage in (0, mesh.pp - 1)
+        spec = [local_batch, cfg["seq"], MODEL["d_model"]]
+        lr_at = learning_rate_schedule_wrapper(**SCHEDULE)
 
-    def run(x, y):
-        return pipelined_train_overlap(model, optimizer, x, y, spec, cfg["microbatches"], mesh.stage, cross_entropy,
-                                       dtype=torch.bfloat16, device=device, pp_group=mesh.group("pp"),
-                                       dp_group=mesh.group("data"))
+        def step(iteration):
+            x, y = stager.next(None, rng, MODEL["vocab"], mock_data=True) if edge else (None, None)   # H2D
+            for group in optimizer.param_groups:
+                group["lr"] = lr_at(iteration)
+            loss = pipelined_train_overlap(model, optimizer, x, y, spec, cfg["microbatches"], mesh.stage,
+                                           cross_entropy, dtype=torch.bfloat16, device=device,
+                                           pp_group=mesh.group("pp"), dp_group=mesh.group("data"))
+            return float(loss) if torch.is_tensor(loss) else loss      # device -> host read of the step's loss
 
-    def step_device():
-        return run(*fixed)
+        device_ms, e2e_ms, clocks, launches, last = measure(step, args, device, rank, native.launch_count)
+        native.check_status()      # a device-side wait that ran out is an error
+        loss = torch.tensor([float(last) if last is not None else 0.0], device=device)
+        dist.all_reduce(loss, op=dist.ReduceOp.MAX)
+        peak = torch.tensor([torch.cuda.max_memory_allocated() / 2 ** 30], device=device)
+        dist.all_reduce(peak, op=dist.ReduceOp.MAX)
+        load = torch.tensor([_worst_expert_load(comm)], device=device)
+        dist.all_reduce(load, op=dist.ReduceOp.MAX)
+        budget = getattr(model, "activation_budget", None)
+        kept = torch.tensor(list((budget.granted, budget.refused) if budget else (0, 0)), device=device,
+                            dtype=torch.float64)
+        dist.all_reduce(kept, op=dist.ReduceOp.SUM)
+        if rank == 0:
+            report(args, cfg, device_ms, e2e_ms, clocks, launches, float(loss), stager.h2d_bytes if edge else 0, 4,
+                   "b200moe", {"peak_mem_gib": float(peak),
+                               "activation_recompute": config["train"]["activation_recompute"],
+                               "moe_calls_kept_gate_up": int(kept[0]), "moe_calls_rebuilt_gate_up": int(kept[1]),
+                               "ep_max_rows_over_balanced": round(float(load), 3),
+                               "comm_backend": "fused" if comm is not None else "nccl",
+                               "native_ops": native.available_ops()})
+        dist.destroy_process_group()
+    except Exception as error:
+        import torch
+        detail = ""
+        try:
+            detail = (f"| peak_mem_gib {torch.cuda.max_memory_allocated() / 2 ** 30:.1f} "
+                      f"| ep_max_rows_over_balanced {_worst_expert_load(state.get('comm')):.3f}")
+        except Exception:
+            pass
+        say_failure("b200moe", args, error, detail)
 
-    def step_e2e():
-        x, y = stager.next(None, rng, MODEL["vocab"], mock_data=True) if edge else (None, None)
-        loss = run(x, y)
-        return float(loss) if torch.is_tensor(loss) else loss      # device -> host read of the step's loss
 
-    device_ms, e2e_ms, clocks, launches, last = measure(
-        step_device, None if args.no_e2e else step_e2e, args, device, rank, native.launch_count)
-    native.check_status()      # a device-side wait that ran out or an expert-capacity overflow is an error
-    loss = torch.tensor([float(last) if last is not None else 0.0], device=device)
-    dist.all_reduce(loss, op=dist.ReduceOp.MAX)
-    peak = torch.tensor([torch.cuda.max_memory_allocated() / 2 ** 30], device=device)
-    dist.all_reduce(peak, op=dist.ReduceOp.MAX)
-    # expert load of the last microbatch: rows the busiest rank of any layer had to process, relative to a
-    # perfectly balanced split (random-init routers collapse with depth, which slows the deeper stages)
-    worst_rows = 0
+def _worst_expert_load(comm) -> float:
+    """Rows the busiest rank of any layer received in its last call, relative to a perfectly balanced split."""
+    worst = 0.0
     if comm is not None:
         for ctx in comm._ep.values():
-            for hint in ctx._hints.values():
-                worst_rows = max(worst_rows, int(hint[0][3]) / ctx.slots)
-    load = torch.tensor([float(worst_rows)], device=device)
-    dist.all_reduce(load, op=dist.ReduceOp.MAX)
-    if rank == 0:
-        report(args, cfg, device_ms, e2e_ms, clocks, launches, float(loss), stager.h2d_bytes if edge else 0, 4,
-               "b200moe", {"peak_mem_gib": float(peak), "activation_recompute": recompute,
-                           "ep_max_rows_over_balanced": round(float(load), 3),
-                           "comm_backend": "fused" if comm is not None else "nccl",
-                           "native_ops": native.available_ops()})
-    dist.destroy_process_group()
+            worst = max(worst, ctx.worst_load())
+    return worst
 
 
 # ------------------------------------------------------------------------------ reference arm
@@ -315,20 +370,21 @@ def bench_reference(args):
         rank, world, local, device = init_dist(args, timeout_s=240)   # a rank that dies ends the others quickly
         from implementation.distributed.ddp_modules import FSDPWrapperPipelined
         from implementation.layers import TransformerLMPipelined
-        from implementation.nnfunctions import cross_entropy
+        from implementation.nnfunctions import cross_entropy, learning_rate_schedule_wrapper
         from implementation.optimizer import AdamW
         from implementation.startup import parallel_rank_groups
         from implementation.train_utils import compile_model, get_batch
         from pipeline import pipelined_train_overlap
         cfg = run_config(args)
-        train = {"fsdp_parallel_num": cfg["fsdp"], "data_parallel_num": 1, "pipeline_parallel_stages": cfg["pp"]}
+        train = {"fsdp_parallel_num": cfg["fsdp"], "data_parallel_num": cfg["ddp"],
+                 "pipeline_parallel_stages": cfg["pp"]}
         groups = {}
         for name, lists in parallel_rank_groups(train, world, world).items():
             for ranks in lists:
                 g = dist.new_group(ranks=ranks)
                 if rank in ranks:
                     groups[name] = g
-        width = cfg["fsdp"]
+        width = cfg["fsdp"] * cfg["ddp"]
         stage, dp_idx = rank // width, rank % width
         torch.backends.cuda.matmul.allow_tf32 = True
         torch.backends.cudnn.allow_tf32 = True
@@ -336,35 +392,31 @@ def bench_reference(args):
         model = TransformerLMPipelined(MODEL["vocab"], cfg["seq"], MODEL["d_model"], cfg["blocks_per_stage"],
                                        MODEL["num_head"], stage, cfg["pp"],
                                        num_expert_per_node=cfg["experts_per_rank"], d_ff=MODEL["d_ff"],
-                                       dp_group=groups["fsdp"], moe_compute_dtype=torch.bfloat16)
+                                       theta=cfg["rope_theta"], dp_group=groups["fsdp"],
+                                       moe_compute_dtype=torch.bfloat16)
         model.to(device)
-        model = FSDPWrapperPipelined(model, FSDP_communication_group=groups["fsdp"], DDP_communication_group=None,
+        model = FSDPWrapperPipelined(model, FSDP_communication_group=groups["fsdp"],
+                                     DDP_communication_group=groups["ddp"] if cfg["ddp"] > 1 else None,
                                      compute_dtype=torch.float16, moe_compute_dtype=torch.bfloat16)
         optimizer = AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.999), weight_decay=0.01)
         model = compile_model(model)
         local_batch = cfg["batch"] // width
         rng = np.random.default_rng(42 + dp_idx)
         edge = stage in (0, cfg["pp"] - 1)
-        fixed = get_batch(None, local_batch, cfg["seq"], device, rng=rng, vocab_size=MODEL["vocab"],
-                          mock_data=True) if edge else (None, None)
         spec = [local_batch, cfg["seq"], MODEL["d_model"]]
+        lr_at = learning_rate_schedule_wrapper(**SCHEDULE)
 
-        def run(x, y):
-            return pipelined_train_overlap(model, optimizer, x, y, spec, cfg["microbatches"], stage, cross_entropy,
-                                           dtype=torch.float16, device=device, pp_group=groups["pp"],
-                                           dp_group=groups["data"])
-
-        def step_device():
-            return run(*fixed)
-
-        def step_e2e():
+        def step(iteration):         # the body of the reference's own training loop
             x, y = get_batch(None, local_batch, cfg["seq"], device, rng=rng, vocab_size=MODEL["vocab"],
                              mock_data=True) if edge else (None, None)
-            loss = run(x, y)
+            for group in optimizer.param_groups:
+                group["lr"] = lr_at(iteration)
+            loss = pipelined_train_overlap(model, optimizer, x, y, spec, cfg["microbatches"], stage, cross_entropy,
+                                           dtype=torch.float16, device=device, pp_group=groups["pp"],
+                                           dp_group=groups["data"])
             return float(loss) if torch.is_tensor(loss) else loss
 
-        device_ms, e2e_ms, clocks, _, last = measure(step_device, None if args.no_e2e else step_e2e, args, device,
-                                                     rank, lambda: 0)
+        device_ms, e2e_ms, clocks, _, last = measure(step, args, device, rank, lambda: 0)
         loss = torch.tensor([float(last) if last is not None else 0.0], device=device)
         dist.all_reduce(loss, op=dist.ReduceOp.MAX)
         peak = torch.tensor([torch.cuda.max_memory_allocated() / 2 ** 30], device=device)
@@ -373,13 +425,8 @@ def bench_reference(args):
             report(args, cfg, device_ms, e2e_ms, clocks, 0, float(loss), 2 * local_batch * cfg["seq"] * 8 if edge else 0,
                    4, "reference", {"peak_mem_gib": float(peak)})
         dist.destroy_process_group()
-    except Exception as error:  # report instead of failing the driver's run
-        reason = f"{type(error).__name__}: {str(error).splitlines()[0][:300] if str(error) else ''}"
-        rank = int(os.environ.get("RANK", "0"))
-        print(f"[reference arm, rank {rank}] {reason}", file=sys.stderr, flush=True)
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": reason, "n_gpus": args.gpus}), flush=True)
-        os._exit(0)      # do not wait in collective teardown for ranks that are gone
+    except Exception as error:
+        say_failure("reference", args, error)
 
 
 if __name__ == "__main__":

@@ -17,7 +17,7 @@ import bench  # noqa: E402
 
 def _args(**over):
     base = dict(gpus=1, steps=2, warmup=3, impl="b200moe", layers=None, microbatches=32, batch=None, seq=8192,
-                recompute=None, backend=None, no_e2e=False)
+                recompute=None, backend=None, layout=None)
     base.update(over)
     return argparse.Namespace(**base)
 
@@ -26,13 +26,52 @@ def test_layout_scales_layers_with_gpus_and_names_the_published_configuration():
     seen = {n: bench.run_config(_args(gpus=n)) for n in (1, 2, 4, 8)}
     assert [seen[n]["pp"] * seen[n]["blocks_per_stage"] for n in (1, 2, 4, 8)] == [8, 8, 16, 32]
     assert seen[8] == {"pp": 4, "fsdp": 2, "ddp": 1, "blocks_per_stage": 8, "batch": 128, "microbatches": 32,
-                       "seq": 8192, "experts_per_rank": 4}
+                       "seq": 8192, "experts_per_rank": 4, "rope_theta": 1e4}
     for n, cfg in seen.items():
         assert cfg["pp"] * cfg["fsdp"] * cfg["ddp"] == n
         # weak scaling: sequences per data-parallel rank and blocks per GPU stay fixed
         assert cfg["batch"] // (cfg["fsdp"] * cfg["ddp"]) == 64 and cfg["blocks_per_stage"] == 8
     with pytest.raises(SystemExit):
         bench.run_config(_args(gpus=3))
+
+
+def test_named_layouts_cover_the_replica_and_the_wide_expert_configurations():
+    ddp2 = bench.run_config(_args(gpus=8, layout="ddp2"))
+    assert (ddp2["pp"], ddp2["fsdp"], ddp2["ddp"], ddp2["blocks_per_stage"], ddp2["batch"]) == (1, 4, 2, 8, 32)
+    assert ddp2["experts_per_rank"] == 2 and ddp2["rope_theta"] == 1e6
+    assert ddp2["batch"] % (ddp2["fsdp"] * ddp2["ddp"] * ddp2["microbatches"]) == 0
+    pp2 = bench.run_config(_args(gpus=8, layout="pp2"))
+    assert (pp2["pp"], pp2["fsdp"], pp2["ddp"], pp2["blocks_per_stage"], pp2["batch"], pp2["microbatches"]) == \
+        (2, 4, 1, 16, 64, 16)
+    with pytest.raises(SystemExit):
+        bench.run_config(_args(gpus=4, layout="pp2"))
+
+
+def test_a_failing_rank_names_its_exception_once_and_leaves_non_zero(monkeypatch, capsys):
+    codes = []
+    monkeypatch.setattr(bench.os, "_exit", lambda code: codes.append(code))
+    monkeypatch.setenv("MASTER_PORT", "1")
+    monkeypatch.setenv("RANK", "3")
+    monkeypatch.setenv("WORLD_SIZE", "8")
+    marker = os.path.join("/tmp", f"b200moe_bench_failed_1_{os.getppid()}")
+    if os.path.exists(marker):
+        os.unlink(marker)
+    try:
+        bench.say_failure("reference", _args(gpus=8, impl="reference"), RuntimeError("out of memory\nmore"))
+        bench.say_failure("reference", _args(gpus=8, impl="reference"), RuntimeError("NCCL: peer gone"))
+    finally:
+        if os.path.exists(marker):
+            os.unlink(marker)
+    captured = capsys.readouterr()
+    lines = [json.loads(l) for l in captured.out.strip().splitlines()]
+    assert len(lines) == 1 and lines[0]["unavailable"] == "rank 3: RuntimeError: out of memory"
+    assert "RuntimeError: out of memory" in captured.err and "peer gone" in captured.err
+    assert codes == [1, 1]
+    # a lone reference process ends normally after its line
+    monkeypatch.setenv("WORLD_SIZE", "1")
+    bench.say_failure("reference", _args(impl="reference"), ValueError("x"))
+    os.unlink(marker)
+    assert codes[-1] == 0
 
 
 def test_json_line_has_the_contract_keys_and_consistent_numbers():
@@ -52,6 +91,7 @@ def test_json_line_has_the_contract_keys_and_consistent_numbers():
     assert line["n_gpus"] == 8 and line["higher_is_better"] is True and line["scaling"] == "weak"
     assert line["dtype"] == "bf16" and "synthetic" in line["data"]
     assert line["config"]["parallelism"] == "pp4·fsdp2·ep2·ddp1" and line["config"]["global_batch"] == 128
+    assert "H2D" in line["config"]["loop"] and line["config"]["layout"] == "scaling"
     assert line["e2e"]["value"] == pytest.approx(tokens / 14.1) and line["e2e"]["h2d_bytes_per_step"] == 8388608
     assert line["e2e"]["d2h_bytes_per_step"] == 4 and line["gpu_launches"] == 12345
     assert line["mfu"] == pytest.approx(line["tokens_per_s_raw"] * 84.007714816e9 / (8 * 2.25e15), rel=1e-6)

@@ -1,0 +1,107 @@
+"""A cross-GPU wait that runs out, on one GPU and without any fault: the peer's flag is simply never written.  The
+kernel must return within its budget, leave its status code in the status word (which ``check_status`` turns into an
+exception) and must not have touched the state that depended on the missing peer."""
+import ctypes
+import time
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+MAX_RANKS = 8
+
+
+@pytest.fixture
+def native():
+    from b200moe.ops import native as nat
+    nat.require()
+    nat.clear_status()
+    nat.set_wait_seconds(0.002)
+    yield nat
+    nat.clear_status()
+    nat.set_wait_seconds(10.0)
+
+
+def _table(*tensors):
+    ptrs = [t.data_ptr() for t in tensors] + [0] * (MAX_RANKS - len(tensors))
+    return (ctypes.c_ulonglong * MAX_RANKS)(*ptrs)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def test_wait_kernel_gives_up_and_reports_its_code(native):
+    pad = torch.zeros(32 * MAX_RANKS, dtype=torch.int32, device="cuda")       # nobody ever signals
+    status = native.status_word()
+    t0 = time.perf_counter()
+    native._call("b2_ep_wait", ctypes.c_void_p(pad.data_ptr()), ctypes.c_int(2), ctypes.c_int(2), ctypes.c_int(1),
+                 ctypes.c_void_p(status.data_ptr()), _stream())
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0
+    assert int(status.item()) == 104
+    with pytest.raises(RuntimeError, match="104"):
+        native.check_status()
+    native.clear_status()
+    assert native.check_status() == 0
+
+
+def test_end_of_step_kernel_leaves_master_and_moments_alone_when_a_rank_never_arrives(native):
+    n = 4096
+    full_g = torch.randn(2 * n, device="cuda")
+    full_w = torch.zeros(2 * n, dtype=torch.bfloat16, device="cuda")
+    pad = torch.zeros(32 * MAX_RANKS, dtype=torch.int32, device="cuda")
+    entries = torch.tensor([[0, 0, n, 0]], dtype=torch.int64, device="cuda")
+    master, m, v = torch.randn(n, device="cuda"), torch.rand(n, device="cuda"), torch.rand(n, device="cuda")
+    shard_grad = torch.zeros(n, device="cuda")
+    before = [t.clone() for t in (master, m, v, shard_grad, full_w)]
+    counter = torch.zeros(8, dtype=torch.int32, device="cuda")
+    status = native.status_word()
+    # rank 0 of an emulated pair whose other member never launches: its flag [slot][1] stays 0
+    native._call("b2_fsdp_step", _table(full_g, full_g), _table(full_w, full_w), _table(pad, pad),
+                 ctypes.c_void_p(entries.data_ptr()), ctypes.c_int(1), ctypes.c_int(0), ctypes.c_int(2),
+                 ctypes.c_int(1), ctypes.c_int(8), ctypes.c_void_p(master.data_ptr()), ctypes.c_void_p(m.data_ptr()),
+                 ctypes.c_void_p(v.data_ptr()), ctypes.c_void_p(shard_grad.data_ptr()), ctypes.c_float(1e-3),
+                 ctypes.c_float(0.9), ctypes.c_float(0.999), ctypes.c_float(1e-8), ctypes.c_float(0.01),
+                 ctypes.c_float(1e-3), ctypes.c_int(1), ctypes.c_int(0), ctypes.c_void_p(counter.data_ptr()),
+                 ctypes.c_void_p(status.data_ptr()), _stream())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 105
+    for now, then in zip((master, m, v, shard_grad, full_w), before):
+        assert torch.equal(now, then)
+    assert int(counter[0].item()) == 0          # the block counter is back at zero for the next launch
+    # the "leave" flag was not raised: the other rank must not take this one for finished
+    assert int(pad.view(32, MAX_RANKS)[9, 0].item()) == 0
+    native.clear_status()
+
+
+def test_vectorised_end_of_step_kernel_matches_the_adamw_rule_on_emulated_single_rank(native):
+    native.set_wait_seconds(5.0)
+    n = 8 * 1000
+    full_g = torch.randn(n, device="cuda")
+    full_w = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    pad = torch.zeros(32 * MAX_RANKS, dtype=torch.int32, device="cuda")
+    entries = torch.tensor([[0, 0, n - 64, 0], [n - 64, n - 64, 64, 0]], dtype=torch.int64, device="cuda")
+    master, m, v = torch.randn(n, device="cuda"), torch.rand(n, device="cuda") * 0.1, torch.rand(n, device="cuda")
+    shard_grad = torch.zeros(n, device="cuda")
+    p0, m0, v0 = master.clone(), m.clone(), v.clone()
+    counter = torch.zeros(8, dtype=torch.int32, device="cuda")
+    lr, b1, b2, eps, wd, a_t = 1e-2, 0.9, 0.999, 1e-8, 0.01, 3e-3
+    native._call("b2_fsdp_step", _table(full_g), _table(full_w), _table(pad), ctypes.c_void_p(entries.data_ptr()),
+                 ctypes.c_int(2), ctypes.c_int(0), ctypes.c_int(1), ctypes.c_int(1), ctypes.c_int(8),
+                 ctypes.c_void_p(master.data_ptr()), ctypes.c_void_p(m.data_ptr()), ctypes.c_void_p(v.data_ptr()),
+                 ctypes.c_void_p(shard_grad.data_ptr()), ctypes.c_float(lr), ctypes.c_float(b1), ctypes.c_float(b2),
+                 ctypes.c_float(eps), ctypes.c_float(wd), ctypes.c_float(a_t), ctypes.c_int(1), ctypes.c_int(0),
+                 ctypes.c_void_p(counter.data_ptr()), ctypes.c_void_p(native.status_word().data_ptr()), _stream())
+    torch.cuda.synchronize()
+    assert native.check_status() == 0
+    g = full_g
+    want_m = b1 * m0 + (1 - b1) * g
+    want_v = b2 * v0 + (1 - b2) * g * g
+    want_p = p0 * (1 - lr * wd) - a_t * want_m / (want_v.sqrt() + eps)
+    torch.testing.assert_close(shard_grad, g)
+    torch.testing.assert_close(m, want_m, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(v, want_v, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(master, want_p, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(full_w.float(), want_p.bfloat16().float())
