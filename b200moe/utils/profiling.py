@@ -7,6 +7,7 @@ stream and reduces the result as the maximum over ranks.
 """
 from __future__ import annotations
 
+import math
 import statistics
 from contextlib import nullcontext
 
@@ -20,94 +21,120 @@ def nvtx_range(name: str):
 
 
 def cuda_device(device="cuda:0") -> torch.device:
-    device = torch.device(device)
-    if device.type != "cuda":
-        raise ValueError("Profiling requires an NVIDIA CUDA device, not CPU.")
-    if torch.version.cuda is None or not torch.cuda.is_available():
-        raise RuntimeError("An NVIDIA GPU and CUDA-enabled PyTorch are required.")
-    if device.index is None:
-        device = torch.device("cuda", torch.cuda.current_device())
-    if device.index >= torch.cuda.device_count():
-        raise ValueError(f"CUDA device index {device.index} is not available.")
-    return device
+    """Resolve a device string to an existing CUDA device (with its index filled in) or say why not."""
+    wanted = torch.device(device)
+    problems = []
+    if wanted.type != "cuda":
+        problems.append(ValueError("Profiling requires an NVIDIA CUDA device, not CPU."))
+    elif not (torch.version.cuda and torch.cuda.is_available()):
+        problems.append(RuntimeError("An NVIDIA GPU and CUDA-enabled PyTorch are required."))
+    if problems:
+        raise problems[0]
+    index = torch.cuda.current_device() if wanted.index is None else wanted.index
+    if not 0 <= index < torch.cuda.device_count():
+        raise ValueError(f"CUDA device index {index} is not available.")
+    return torch.device("cuda", index)
+
+
+class _LatencySeries:
+    """Per-call device times of one closure, taken with a CUDA event pair around each call."""
+
+    def __init__(self):
+        self.ms: list[float] = []
+        self._pair = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+
+    def settle(self):
+        """Record the pair once so that the events' own set-up never lands in a sample."""
+        first, second = self._pair
+        first.record()
+        second.record()
+        second.synchronize()
+
+    def run(self, fn):
+        first, second = self._pair
+        first.record()
+        out = fn()
+        second.record()
+        second.synchronize()
+        self.ms.append(first.elapsed_time(second))
+        return out
+
+    def stats(self) -> dict:
+        ms = self.ms
+        return {"mean": statistics.fmean(ms), "median": statistics.median(ms), "stddev": statistics.pstdev(ms),
+                "min": min(ms), "max": max(ms), "total": math.fsum(ms)}
+
+
+def _require_count(name: str, value, least: int, message: str) -> None:
+    if type(value) is not int or value < least:
+        raise ValueError(message)
 
 
 def profile_callable(step, *, device="cuda:0", warmup: int = 10, iterations: int = 100) -> dict:
+    """Latency statistics (ms per call, CUDA events) and allocator peaks (MiB) of ``step()`` after ``warmup``
+    untimed calls; the result has the keys of the reference tool (run_experiment.py:38-98)."""
     if not callable(step):
         raise TypeError("step must be callable")
-    if type(warmup) is not int or warmup < 0:
-        raise ValueError("warmup must be nonnegative integer")
-    if type(iterations) is not int or iterations < 1:
-        raise ValueError("iterations must be a positive integer")
-    device = cuda_device(device)
-    mib = float(1 << 20)
-    with torch.cuda.device(device):
+    _require_count("warmup", warmup, 0, "warmup must be nonnegative integer")
+    _require_count("iterations", iterations, 1, "iterations must be a positive integer")
+    target = cuda_device(device)
+    to_mib = 1.0 / (1 << 20)
+    with torch.cuda.device(target):
         for _ in range(warmup):
             step()
-        torch.cuda.synchronize(device)
-        begin, end = (torch.cuda.Event(enable_timing=True) for _ in range(2))
-        begin.record(); end.record(); end.synchronize()
-        base_alloc = torch.cuda.memory_allocated(device)
-        base_reserved = torch.cuda.memory_reserved(device)
-        torch.cuda.reset_peak_memory_stats(device)
-        samples = []
+        torch.cuda.synchronize(target)
+        series = _LatencySeries()
+        series.settle()
+        floor = {"allocated": torch.cuda.memory_allocated(target), "reserved": torch.cuda.memory_reserved(target)}
+        torch.cuda.reset_peak_memory_stats(target)
         for _ in range(iterations):
-            begin.record()
-            result = step()
-            end.record()
-            end.synchronize()
-            samples.append(begin.elapsed_time(end))
-            del result
-        torch.cuda.synchronize(device)
-        peak = torch.cuda.max_memory_allocated(device)
-        return {
-            "device": str(device),
-            "gpu": torch.cuda.get_device_name(device),
-            "iterations": iterations,
-            "warmup_iterations": warmup,
-            "time_ms": {"mean": statistics.mean(samples), "median": statistics.median(samples),
-                        "stddev": statistics.pstdev(samples), "min": min(samples),
-                        "max": max(samples), "total": sum(samples)},
-            "memory_mib": {"baseline_allocated": base_alloc / mib, "peak_allocated": peak / mib,
-                           "peak_above_baseline": (peak - base_alloc) / mib,
-                           "baseline_reserved": base_reserved / mib,
-                           "peak_reserved": torch.cuda.max_memory_reserved(device) / mib},
-        }
+            series.run(step)         # the closure's result is dropped here, before the next call allocates
+        torch.cuda.synchronize(target)
+        top = {"allocated": torch.cuda.max_memory_allocated(target),
+               "reserved": torch.cuda.max_memory_reserved(target)}
+    memory = {"baseline_allocated": floor["allocated"] * to_mib, "peak_allocated": top["allocated"] * to_mib,
+              "peak_above_baseline": (top["allocated"] - floor["allocated"]) * to_mib,
+              "baseline_reserved": floor["reserved"] * to_mib, "peak_reserved": top["reserved"] * to_mib}
+    return {"device": str(target), "gpu": torch.cuda.get_device_name(target), "iterations": iterations,
+            "warmup_iterations": warmup, "time_ms": series.stats(), "memory_mib": memory}
+
+
+class _ModuleStep:
+    """Callable that runs a module forward (and backward when training) and leaves no gradient behind; there is
+    no optimizer step (the contract of the reference's ``make_module_step``, run_experiment.py:127-166)."""
+
+    def __init__(self, module, inputs, training: bool, loss_fn):
+        self.module, self.inputs, self.training, self.loss_fn = module, inputs, training, loss_fn
+        module.train(training)
+        self.leaf_inputs = [t for t in inputs if isinstance(t, torch.Tensor) and t.is_leaf]
+        for t in self.leaf_inputs:
+            if t.is_floating_point():
+                t.requires_grad_(training)
+        self.drop_gradients()
+
+    def drop_gradients(self):
+        self.module.zero_grad(set_to_none=True)
+        for t in self.leaf_inputs:
+            t.grad = None
+
+    def __call__(self):
+        if not self.training:
+            with torch.no_grad():
+                return self.module(*self.inputs)
+        try:
+            with torch.enable_grad():
+                out = self.module(*self.inputs)
+                value = out.float().mean() if self.loss_fn is None else self.loss_fn(out)
+                value.backward()
+            return value.detach()
+        finally:
+            self.drop_gradients()
 
 
 def make_module_step(module, inputs, mode: str, loss_fn=None):
-    """A closure that runs forward (+ backward in ``training`` mode) and clears
-    gradients afterwards; no optimizer step (reference run_experiment.py:127-166)."""
     if mode not in ("training", "evaluation"):
         raise ValueError("mode must be training or evaluation")
-    training = mode == "training"
-    module.train(training)
-    leaves = [t for t in inputs if isinstance(t, torch.Tensor) and t.is_leaf]
-    for tensor in leaves:
-        if tensor.is_floating_point():
-            tensor.requires_grad_(training)
-
-    def clear():
-        module.zero_grad(set_to_none=True)
-        for tensor in leaves:
-            tensor.grad = None
-
-    clear()
-
-    def step():
-        if not training:
-            with torch.no_grad():
-                return module(*inputs)
-        with torch.enable_grad():
-            try:
-                output = module(*inputs)
-                loss = loss_fn(output) if loss_fn is not None else output.float().mean()
-                loss.backward()
-                return loss.detach()
-            finally:
-                clear()
-
-    return step
+    return _ModuleStep(module, inputs, mode == "training", loss_fn)
 
 
 class DeviceStepTimer:

@@ -20,27 +20,34 @@ ITERATIONS = 100
 DEFAULT_CONFIG_PATH = Path(__file__).resolve().parent / "configs" / "run_config.yaml"
 
 
+def _is_shape_list(value) -> bool:
+    def is_shape(shape):
+        return isinstance(shape, list) and len(shape) > 0 and all(type(d) is int and d > 0 for d in shape)
+    return isinstance(value, list) and len(value) > 0 and all(is_shape(shape) for shape in value)
+
+
+# one rule per key of the ``experiment`` section: (key, predicate, message)
+_EXPERIMENT_RULES = (
+    ("warmup", lambda v: type(v) is int and v >= 0, "experiment.warmup must be an integer >= 0"),
+    ("iterations", lambda v: type(v) is int and v >= 1, "experiment.iterations must be an integer >= 1"),
+    ("dtype", lambda v: v in ("float32", "float16", "bfloat16"),
+     "experiment.dtype must be float32, float16, or bfloat16"),
+    ("device", lambda v: isinstance(v, str), "experiment.device must be a CUDA device string"),
+    ("mode", lambda v: v in ("training", "evaluation"), "experiment.mode must be training or evaluation"),
+    ("input_shapes", _is_shape_list, "experiment.input_shapes must be a list of positive integer shapes"),
+)
+
+
 def load_experiment_config(path):
-    with Path(path).open(encoding="utf-8") as source:
-        config = yaml.safe_load(source)
-    if not isinstance(config, dict) or not isinstance(config.get("experiment"), dict):
+    """Read the YAML file and check its ``experiment`` section rule by rule (the keys and verdicts of the
+    reference tool, run_experiment.py:101-124)."""
+    config = yaml.safe_load(Path(path).read_text(encoding="utf-8"))
+    section = config.get("experiment") if isinstance(config, dict) else None
+    if not isinstance(section, dict):
         raise ValueError("Configuration must contain an experiment section")
-    experiment = config["experiment"]
-    for key, minimum in (("warmup", 0), ("iterations", 1)):
-        value = experiment.get(key)
-        if type(value) is not int or value < minimum:
-            raise ValueError(f"experiment.{key} must be an integer >= {minimum}")
-    if experiment.get("dtype") not in ("float32", "float16", "bfloat16"):
-        raise ValueError("experiment.dtype must be float32, float16, or bfloat16")
-    if not isinstance(experiment.get("device"), str):
-        raise ValueError("experiment.device must be a CUDA device string")
-    if experiment.get("mode") not in ("training", "evaluation"):
-        raise ValueError("experiment.mode must be training or evaluation")
-    shapes = experiment.get("input_shapes")
-    good = isinstance(shapes, list) and shapes and all(
-        isinstance(shape, list) and shape and all(type(d) is int and d > 0 for d in shape) for shape in shapes)
-    if not good:
-        raise ValueError("experiment.input_shapes must be a list of positive integer shapes")
+    for key, accepts, message in _EXPERIMENT_RULES:
+        if not accepts(section.get(key)):
+            raise ValueError(message)
     return config
 
 
@@ -55,23 +62,24 @@ def module_wrapper(config, device, dtype):
     return make_module_step(module, inputs, config["experiment"]["mode"])
 
 
-def main(argv=None):
-    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("--config-path", type=Path, default=DEFAULT_CONFIG_PATH)
-    args = parser.parse_args(argv)
-    config = load_experiment_config(args.config_path)
-    experiment = config["experiment"]
-    device = cuda_device(experiment["device"])
-    dtype = getattr(torch, experiment["dtype"])
+def run(config_path) -> dict:
+    """Profile the module of ``module_wrapper`` as the ``experiment`` section of ``config_path`` says."""
+    config = load_experiment_config(config_path)
+    section = config["experiment"]
+    device = cuda_device(section["device"])
     with torch.cuda.device(device):
-        step = module_wrapper(config, device, dtype)
-        result = profile_callable(step, device=device, warmup=experiment["warmup"],
-                                  iterations=experiment["iterations"])
-    result["mode"] = experiment["mode"]
-    result["config_path"] = str(Path(args.config_path).resolve())
-    result["experiment"] = experiment
-    print(json.dumps(result, indent=2))
-    return result
+        step = module_wrapper(config, device, getattr(torch, section["dtype"]))
+        report = profile_callable(step, device=device, warmup=section["warmup"], iterations=section["iterations"])
+    report.update(mode=section["mode"], config_path=str(Path(config_path).resolve()), experiment=section)
+    return report
+
+
+def main(argv=None):
+    cli = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    cli.add_argument("--config-path", type=Path, default=DEFAULT_CONFIG_PATH)
+    report = run(cli.parse_args(argv).config_path)
+    print(json.dumps(report, indent=2))
+    return report
 
 
 if __name__ == "__main__":
