@@ -125,6 +125,10 @@ class Comm:
         self.status = native.status_word(device)
         self.fsdp = GroupComm(mesh.group("fsdp"), device) if mesh.fsdp > 1 else None
         self.ddp = GroupComm(mesh.group("ddp"), device) if mesh.ddp > 1 else None
+        # expert exchange: "pull" = fused with the expert GEMMs (comm/ep.py); "push" = the separate push/consume kernels
+        self.ep_mode = os.environ.get("B200MOE_EP_MODE", "pull")
+        skew = os.environ.get("B200MOE_EP_MAX_SKEW")
+        self.ep_max_skew = float(skew) if skew else None
         self.capacity_mode = os.environ.get("B200MOE_EP_CAPACITY", "exact")
         self.capacity_bucket = int(os.environ.get("B200MOE_EP_BUCKET", "4096"))
         self._symm = {}
@@ -308,11 +312,18 @@ class Comm:
 
     # -- expert parallel --------------------------------------------------------------------
     def ep_context(self, tokens: int, dim: int, experts_total: int, capacity_factor: float = 1.25,
-                   capacity_mode: str | None = None):
+                   capacity_mode: str | None = None, ffn: int | None = None):
         key = (tokens, dim, experts_total)
         ctx = self._ep.get(key)
         if ctx is None:
-            ctx = EPContext(self, tokens, dim, experts_total, capacity_factor, capacity_mode or self.capacity_mode)
+            if self.ep_mode == "pull" and ffn is not None:
+                from .ep import EPPull
+                # a wide group's worst case (every slot of every rank on one rank) is far from anything a trained
+                # router does: beyond four ranks the accepted skew is bounded unless configured otherwise
+                skew = self.ep_max_skew if self.ep_max_skew else (None if self.fsdp.world <= 4 else 4.0)
+                ctx = EPPull(self.fsdp, self.status, self.device, tokens, dim, ffn, experts_total, max_skew=skew)
+            else:
+                ctx = EPContext(self, tokens, dim, experts_total, capacity_factor, capacity_mode or self.capacity_mode)
             self._ep[key] = ctx
         return ctx
 

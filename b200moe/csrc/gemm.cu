@@ -17,6 +17,7 @@
 // of tile i overlaps the main loop of tile i+1.  Shared memory holds a 4-stage
 // ring of {A 128x64, B 256x64} bf16 tiles in the 128-byte-swizzled layout that
 // both TMA and the MMA descriptors understand.
+#include "peer.cuh"
 #include "ptx.cuh"
 #include "tensormap.cuh"
 
@@ -52,6 +53,8 @@ enum Epilogue : int {
   EPI_ACC_BF16 = 2,     // D[M,N] bf16 += acc
   EPI_SWIGLU = 3,       // H[M,N/2] = silu(acc[:, :128]) * acc[:, 128:]; optional gate/up stores
   EPI_STORE_F32 = 4,    // D[M,N] fp32 = acc
+  EPI_PUSH = 5,         // expert-parallel return: row r, scaled by push_w[r], is stored as bf16 into row push_tag[r]
+                        // of rank push_src[r]'s buffer through its peer pointer; the last CTA raises a flag
 };
 
 enum Schedule : int {
@@ -78,6 +81,14 @@ struct GemmParams {
   long long d_expert_stride;   // elements between experts in d (SCHED_WGRAD)
   float beta;                  // 1 accumulate, 0 overwrite (EPI_ACC_*)
   int* status;                 // device word; non-zero = a wait ran out
+  // EPI_PUSH only
+  Peers push_dst;              // every rank's return buffer [slots, ldd] bf16
+  const int* push_tag;         // [M] destination row (slot id) of each row, -1 for padding rows
+  const int* push_src;         // [M] destination rank
+  const float* push_w;         // [M] scale (routing weight), or null for 1
+  Peers push_sig;              // signal pads
+  int push_slot, push_seq, push_rank, push_n;
+  unsigned int* push_ticket;   // self-resetting CTA counter
 };
 
 struct TileCoord {
@@ -380,7 +391,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const long long col = col_base + c;
           if (!row_ok || col >= p.N) continue;   // N is a multiple of 32 (checked on the host)
           const long long off = expert_off + row * p.ldd + col;
-          if (EPI == EPI_STORE_BF16) {
+          if (EPI == EPI_PUSH) {
+            const int tag = p.push_tag[row];
+            const int dest = p.push_src[row];
+            if (tag < 0 || dest < 0 || dest >= p.push_n) continue;       // padding row: nobody waits for it
+            const float w = p.push_w ? p.push_w[row] : 1.f;
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.push_dst.ptr[dest]) +
+                                                  static_cast<long long>(tag) * p.ldd + col);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              dst[i] = make_uint4(pack_bf16(w * __uint_as_float(v[8 * i]), w * __uint_as_float(v[8 * i + 1])),
+                                  pack_bf16(w * __uint_as_float(v[8 * i + 2]), w * __uint_as_float(v[8 * i + 3])),
+                                  pack_bf16(w * __uint_as_float(v[8 * i + 4]), w * __uint_as_float(v[8 * i + 5])),
+                                  pack_bf16(w * __uint_as_float(v[8 * i + 6]), w * __uint_as_float(v[8 * i + 7])));
+          } else if (EPI == EPI_STORE_BF16) {
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.d) + off);
 #pragma unroll
             for (int i = 0; i < 4; ++i)
@@ -446,6 +470,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     }
   }
 
+  if (EPI == EPI_PUSH) __threadfence_system();   // my rows are in the peers' memory before the flag below
   tc_fence_before();
   __syncthreads();
   if (PAIR) cluster_sync_all();   // the peer's shared memory, barriers and tensor memory are idle as well
@@ -453,6 +478,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     tc_fence_after();
     if (PAIR) tmem_dealloc_pair(tmem_base, 512);
     else tmem_dealloc(tmem_base, 512);
+  }
+  if (EPI == EPI_PUSH && threadIdx.x == 0) {
+    // the last CTA to get here tells every rank that this rank's rows have been delivered
+    const unsigned int old = atomicInc(p.push_ticket, gridDim.x - 1);
+    if (old == gridDim.x - 1) {
+      __threadfence_system();
+      signal_all(p.push_sig, p.push_slot, p.push_rank, p.push_n, p.push_seq);
+    }
   }
 }
 
@@ -638,6 +671,59 @@ int b2_gemm_nn(const void* a, const void* w, const void* w2, void* d, int M, int
   p.tile_expert = tile_expert; p.num_m_tiles = num_m_tiles; p.d = d; p.ldd = ldd; p.status = status;
   p.group_align256 = group_align256;
   return launch<0, 1, EPI_STORE_BF16, SCHED_FLAT>(p, sm_count(), stream);
+}
+
+static void fill_push(GemmParams& p, const unsigned long long* dst, const int* tag, const int* src, const float* w,
+                      const unsigned long long* sig, int slot, int seq, int rank, int n, unsigned int* ticket) {
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    p.push_dst.ptr[i] = i < n ? reinterpret_cast<void*>(dst[i]) : nullptr;
+    p.push_sig.ptr[i] = i < n ? reinterpret_cast<void*>(sig[i]) : nullptr;
+  }
+  p.push_tag = tag; p.push_src = src; p.push_w = w; p.push_slot = slot; p.push_seq = seq; p.push_rank = rank;
+  p.push_n = n; p.push_ticket = ticket;
+}
+
+// Expert-parallel return fused into the epilogue.  The product a[M,K] * w[e][N,K]^T (NT) is not stored locally: row r
+// is scaled by push_w[r] (null: 1) and written as bf16 into row push_tag[r] of rank push_src[r]'s buffer
+// (``push_dst``: MAX_RANKS device addresses, row pitch N); rows with a negative tag are skipped.  When all CTAs are
+// done the kernel writes ``seq`` into slot ``sig_slot`` of every rank's signal pad.  ``ticket``: a zero-initialised
+// device word that the kernel leaves at zero.
+int b2_gemm_nt_push(const void* a, const void* w, int M, int N, int K, long long lda, int num_experts,
+                    const int* tile_expert, const int* num_m_tiles, int group_align256,
+                    const unsigned long long* push_dst, const int* push_tag, const int* push_src, const float* push_w,
+                    const unsigned long long* sig, int sig_slot, int seq, int rank, int n, unsigned int* ticket,
+                    int* status, cudaStream_t stream) {
+  if (N % 32 || K % 8 || n < 1 || n > MAX_RANKS) return -10;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.num_experts = num_experts; p.b_expert_rows = N; p.k_split = 0;
+  p.tile_expert = tile_expert; p.num_m_tiles = num_m_tiles; p.d = nullptr; p.ldd = N; p.status = status;
+  p.group_align256 = group_align256;
+  fill_push(p, push_dst, push_tag, push_src, push_w, sig, sig_slot, seq, rank, n, ticket);
+  const int sms = sm_count();
+  const TileKind kind = choose_tile<SCHED_FLAT>(p, sms, pair_available<0, 0, EPI_PUSH, SCHED_FLAT>(sms));
+  if (make_map(&p.map_a, a, K, M, lda, BM)) return -11;
+  if (make_map(&p.map_b, w, K, static_cast<long long>(num_experts) * N, K, kind == TILE_PAIR ? BN / 2 : BN))
+    return -12;
+  return launch<0, 0, EPI_PUSH, SCHED_FLAT>(p, kind, sms, stream);
+}
+
+// The same for a[M,K] * w[e][K,N] with the reduction continued over w2 (dx = dgate W1 + dup W3).
+int b2_gemm_nn_push(const void* a, const void* w, const void* w2, int M, int N, int K, int k_split, long long lda,
+                    int num_experts, const int* tile_expert, const int* num_m_tiles, int group_align256,
+                    const unsigned long long* push_dst, const int* push_tag, const int* push_src, const float* push_w,
+                    const unsigned long long* sig, int sig_slot, int seq, int rank, int n, unsigned int* ticket,
+                    int* status, cudaStream_t stream) {
+  if (N % 32 || K % 64 || (w2 && k_split % 64) || n < 1 || n > MAX_RANKS) return -10;
+  GemmParams p{};
+  const int rows = w2 ? k_split : K;
+  if (make_map(&p.map_a, a, K, M, lda, BM)) return -11;
+  if (make_map(&p.map_b, w, N, static_cast<long long>(num_experts) * rows, N, 64)) return -12;
+  if (w2 && make_map(&p.map_b2, w2, N, static_cast<long long>(num_experts) * (K - k_split), N, 64)) return -12;
+  p.M = M; p.N = N; p.K = K; p.num_experts = num_experts; p.b_expert_rows = rows; p.k_split = w2 ? k_split : 0;
+  p.tile_expert = tile_expert; p.num_m_tiles = num_m_tiles; p.d = nullptr; p.ldd = N; p.status = status;
+  p.group_align256 = group_align256;
+  fill_push(p, push_dst, push_tag, push_src, push_w, sig, sig_slot, seq, rank, n, ticket);
+  return launch<0, 1, EPI_PUSH, SCHED_FLAT>(p, sm_count(), stream);
 }
 
 // dw[e][M,N] (+)= a[rows_e, M]^T * b[rows_e, N]   (both MN-major; rows_e from cumulative offsets, or all R rows

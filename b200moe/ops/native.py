@@ -73,6 +73,12 @@ def launch_count() -> int:
     return _launches
 
 
+def count_launch(n: int = 1) -> None:
+    """For callers that launch through ``require()`` directly."""
+    global _launches
+    _launches += n
+
+
 def _p(t):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
@@ -98,7 +104,7 @@ def debug_records(clear: bool = False) -> dict:
     found = {}
     if lib is None:
         return found
-    for name in ("moe", "comm"):
+    for name in ("moe", "comm", "moe_ep"):
         reader = getattr(lib, f"b2_{name}_debug_read", None) if _DEBUG else None
         if reader is None:
             continue
@@ -507,3 +513,39 @@ def swiglu_bwd(dh, gate, up, live_rows=None, want_h: bool = True):
     h = torch.empty(rows, F, dtype=torch.bfloat16, device=dh.device) if want_h else None
     _call("b2_swiglu_bwd", _p(_bf16(dh)), _p(gate), _p(up), _p(dgu), _p(h), _p(live_rows), _I(rows), _I(F), _stream())
     return dgu, h
+
+
+# ------------------------------------------------------------------------------ expert-parallel return in the epilogue
+def gemm_nt_push(a, w, tile_expert, num_m_tiles, num_experts, dst_table, row_tag, row_src, row_w, sig_table,
+                 sig_slot: int, seq: int, rank: int, n: int, ticket):
+    """Rows of ``a [M,K] @ w[e] [N,K]ᵀ``, scaled by ``row_w`` (or 1), stored as bf16 into row ``row_tag[r]`` of rank
+    ``row_src[r]``'s buffer (``dst_table``: ctypes array of ``MAX_RANKS`` addresses, row pitch ``N``); afterwards
+    flag ``seq`` is raised in slot ``sig_slot`` of every rank's signal pad."""
+    M, K = a.shape
+    N = w.shape[-2]
+    assert a.stride(-1) == 1 and w.is_contiguous()
+    _call("b2_gemm_nt_push", _p(_bf16(a)), _p(_bf16(w)), _I(M), _I(N), _I(K), _L(a.stride(0)), _I(num_experts),
+          _p(tile_expert), _p(num_m_tiles), _I(1), dst_table, _p(row_tag), _p(row_src), _p(row_w), sig_table,
+          _I(sig_slot), _I(seq), _I(rank), _I(n), _p(ticket), _p(status_word(a.device)), _stream())
+
+
+def gemm_nn_push(a, w, w2, tile_expert, num_m_tiles, num_experts, dst_table, row_tag, row_src, row_w, sig_table,
+                 sig_slot: int, seq: int, rank: int, n: int, ticket):
+    """The same for ``a [M,K] @ [w[e]; w2[e]]`` (``w``, ``w2``: ``[E, K/2, N]``, the reduction runs over their rows)."""
+    M, K = a.shape
+    N = w.shape[-1]
+    k_split = w.shape[-2] if w2 is not None else 0
+    assert a.stride(-1) == 1 and w.is_contiguous()
+    _call("b2_gemm_nn_push", _p(_bf16(a)), _p(_bf16(w)), _p(w2), _I(M), _I(N), _I(K), _I(k_split), _L(a.stride(0)),
+          _I(num_experts), _p(tile_expert), _p(num_m_tiles), _I(1), dst_table, _p(row_tag), _p(row_src), _p(row_w),
+          sig_table, _I(sig_slot), _I(seq), _I(rank), _I(n), _p(ticket), _p(status_word(a.device)), _stream())
+
+
+def ep_swiglu_bwd(dh, gate_lo, up_lo, gate_hi, up_hi, split_row: int, dgu, meta, row_tag, row_src, row_w,
+                  dw_table, n: int):
+    """SwiGLU backward on expert-major rows with the routing weight folded in (see ``ep_swiglu_bwd_kernel``):
+    ``dh`` is overwritten with ``w·h``, ``dgu`` receives ``w·[dgate | dup]``, the routing-weight gradient of every
+    row goes to its source rank's ``dw_table`` entry."""
+    rows, F = dh.shape
+    _call("b2_ep_swiglu_bwd", _p(_bf16(dh)), _p(gate_lo), _p(up_lo), _p(gate_hi), _p(up_hi), _I(split_row), _p(dgu),
+          _p(meta), _p(row_tag), _p(row_src), _p(row_w), dw_table, _I(rows), _I(F), _I(n), _stream())

@@ -70,8 +70,25 @@ def _allreduce(rank, world, port, out_dir):
     native.check_status()
 
 
+def _moe_pull_once(epc, x, logits, params, dout, keep_rows=None, recompute=False):
+    """One forward/backward of the pull-based block; returns out and the gradients."""
+    import torch
+    from b200moe import ops
+    from b200moe.ops.moe_fused import moe_ffn_pull
+    xs, lg = x.clone().requires_grad_(True), logits.clone().requires_grad_(True)
+    ps = [p.clone().requires_grad_(True) for p in params]
+    if keep_rows is not None:
+        epc.expected_rows = lambda key: keep_rows       # force a partial keep of the gate/up rows
+    out, _, _ = moe_ffn_pull(xs, lambda staged: ops.router_top2(lg), *ps, epc, recompute=recompute)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    return [out.detach(), xs.grad, lg.grad] + [p.grad for p in ps]
+
+
 def _moe_ep(rank, world, port, out_dir):
-    """Peer-memory dispatch/return against the NCCL all-to-all path, forward and backward."""
+    """Expert-parallel block against the NCCL all-to-all path, forward and backward: the exchange fused with the
+    expert GEMMs with the gate/up rows all kept, partly kept and all rebuilt, under an unbalanced router and under one
+    that sends every row of every rank to rank 0."""
     import torch
     from b200moe import ops
     from b200moe.comm import make_comm
@@ -81,36 +98,44 @@ def _moe_ep(rank, world, port, out_dir):
     device = _setup(rank, world, port)
     mesh = build_groups({"fsdp_parallel_num": world, "data_parallel_num": 1, "pipeline_parallel_stages": 1},
                         rank, world, world)
-    comm = make_comm(mesh, device)
+    comm = make_comm(mesh, device, wait_seconds=3.0)
     group = mesh.group("fsdp")
     T, D, Fd, E_total = 1024, 256, 512, 8
     e_local = E_total // world
     torch.manual_seed(5 + rank)
     x = (torch.randn(T, D, device=device)).bfloat16()
-    logits = torch.randn(T, E_total, device=device)
-    if rank == 0:
-        logits[:, 0] += 2.0                      # unbalanced routing
     w1, w3, w2 = ((torch.randn(e_local, Fd, D, device=device) * 0.06).bfloat16(),
                   (torch.randn(e_local, Fd, D, device=device) * 0.06).bfloat16(),
                   (torch.randn(e_local, D, Fd, device=device) * 0.06).bfloat16())
     dout = torch.randn(T, D, device=device).bfloat16()
-    results = []
-    for fused in (True, False, True):
+    epc = comm.ep_context(T, D, E_total, ffn=Fd)
+    assert hasattr(epc, "acquire")
+    for case in ("unbalanced", "all_to_rank0"):
+        logits = torch.randn(T, E_total, device=device)
+        if case == "unbalanced":
+            if rank == 0:
+                logits[:, 0] += 2.0
+        else:
+            logits[:, :e_local] += 30.0              # every token of every rank picks two experts of rank 0
         xs, lg = x.clone().requires_grad_(True), logits.clone().requires_grad_(True)
         params = [p.clone().requires_grad_(True) for p in (w1, w2, w3)]
         weights, idx = ops.router_top2(lg)
-        ctx = comm.ep_context(T, D, E_total, capacity_factor=2.0) if fused else None
-        ops.set_native(fused)
+        ops.set_native(False)
         try:
-            out = moe_ffn(xs, weights, idx, *params, group=group, ep_ctx=ctx)
+            out = moe_ffn(xs, weights, idx, *params, group=group)          # NCCL all-to-all, PyTorch statements
             out.backward(dout)
         finally:
             ops.set_native(True)
-        results.append([out.detach(), xs.grad, lg.grad] + [p.grad for p in params])
-    for got, want, again in zip(*results):
-        assert _rel(got, want) < 2e-2, _rel(got, want)
-        assert _rel(again, want) < 2e-2
-    native.check_status()
+        want = [out.detach(), xs.grad, lg.grad] + [p.grad for p in params]
+        for keep_rows, recompute in ((None, False), (256, False), (None, True), (None, False)):
+            got = _moe_pull_once(epc, x, logits, (w1, w2, w3), dout, keep_rows, recompute)
+            for name, a, b in zip(("out", "dx", "dlogits", "dw1", "dw2", "dw3"), got, want):
+                assert _rel(a, b) < 2e-2, (case, keep_rows, recompute, name, _rel(a, b))
+            native.check_status()
+            epc.__dict__.pop("expected_rows", None)
+        assert len(epc.free) == len(epc.pool) >= 1                           # every pool slot came back
+        if case == "all_to_rank0" and rank == 0:
+            assert epc.worst_load() >= float(world)                          # every slot of every rank landed here
 
 
 def _train_parity(rank, world, port, out_dir, pp):

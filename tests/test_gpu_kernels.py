@@ -289,6 +289,48 @@ def test_moe_block_matches_torch_path(native, recompute):
     native.check_status()
 
 
+@pytest.mark.parametrize("keep_rows,recompute", [(None, False), (512, False), (None, True)])
+def test_moe_block_with_fused_exchange_on_a_single_rank_group(native, keep_rows, recompute):
+    """The gather+GEMM kernels, the return in the GEMM epilogue and the combine kernel with every pointer local
+    (expert group of one rank), against the PyTorch statements of the block."""
+    from b200moe import ops
+    from b200moe.comm.ep import EPPull
+    from b200moe.ops.moe import moe_ffn
+    from b200moe.ops.moe_fused import moe_ffn_pull
+    torch.manual_seed(3)
+    T, D, Fd, E = 1000 if keep_rows is None else 1024, 256, 512, 4
+    T = 1024
+    x = _rand(T, D)
+    logits = torch.randn(T, E, device="cuda")
+    logits[:, 1] += 1.0
+    w1, w3, w2 = _rand(E, Fd, D, scale=0.06), _rand(E, Fd, D, scale=0.06), _rand(E, D, Fd, scale=0.06)
+    dout = _rand(T, D)
+    epc = EPPull(None, native.status_word(), torch.device("cuda", torch.cuda.current_device()), T, D, Fd, E)
+    if keep_rows is not None:
+        epc.expected_rows = lambda key: keep_rows
+    results = []
+    for fused in (True, False, True):
+        xs = x.clone().requires_grad_(True)
+        lg = logits.clone().requires_grad_(True)
+        params = [p.clone().requires_grad_(True) for p in (w1, w2, w3)]
+        if fused:
+            out, _, _ = moe_ffn_pull(xs, lambda staged: ops.router_top2(lg), *params, epc, recompute=recompute)
+        else:
+            ops.set_native(False)
+            try:
+                weights, idx = ops.router_top2(lg)
+                out = moe_ffn(xs, weights, idx, *params)
+            finally:
+                ops.set_native(True)
+        out.backward(dout)
+        results.append([out.detach(), xs.grad, lg.grad] + [p.grad for p in params])
+    for got, want, again in zip(*results):
+        assert _rel(got, want) < 2e-2
+        assert _rel(again, want) < 2e-2
+    assert len(epc.free) == len(epc.pool) == 1
+    native.check_status()
+
+
 def test_tiny_model_native_vs_torch_path(native):
     from b200moe import ops
     from b200moe.models import TransformerLMPipelined
