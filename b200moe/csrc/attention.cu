@@ -45,8 +45,29 @@ struct AttnParams {
   __nv_bfloat16* dk;      // [B,S,Hkv,128]
   __nv_bfloat16* dv;      // [B,S,Hkv,128]
   long long dq_pitch, dk_pitch, dv_pitch;   // elements per token of the gradient outputs
+  const float* rope_cos;  // backward, optional: [S, 64] tables of the rotation that was applied to q and k before the
+  const float* rope_sin;  // forward pass; dq and dk are then stored rotated back (gradients of the unrotated q, k)
   int* status;
 };
+
+// Transposed rotary embedding on 32 consecutive columns (16 adjacent pairs) of one head, in registers:
+// (d0, d1) -> (d0 c + d1 s, d1 c - d0 s).  ``first_pair`` = (column of a[0] within the head) / 2.
+__device__ __forceinline__ void unrotate32(uint32_t (&a)[32], const float* cos_t, const float* sin_t, size_t pos,
+                                           int first_pair) {
+  const float4* c4 = reinterpret_cast<const float4*>(cos_t + pos * 64 + first_pair);
+  const float4* s4 = reinterpret_cast<const float4*>(sin_t + pos * 64 + first_pair);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float4 cc = c4[q], ss = s4[q];
+    const float cv[4] = {cc.x, cc.y, cc.z, cc.w}, sv[4] = {ss.x, ss.y, ss.z, ss.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float d0 = __uint_as_float(a[8 * q + 2 * j]), d1 = __uint_as_float(a[8 * q + 2 * j + 1]);
+      a[8 * q + 2 * j] = __float_as_uint(d0 * cv[j] + d1 * sv[j]);
+      a[8 * q + 2 * j + 1] = __float_as_uint(d1 * cv[j] - d0 * sv[j]);
+    }
+  }
+}
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -527,6 +548,7 @@ __global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_bwd_dkv_kernel(const
         tmem_ld_32x32(t_dv + lane_base + c * 32, a);
         tmem_ld_32x32(t_dk + lane_base + c * 32, k2);
         tmem_ld_wait();
+        if (p.rope_cos) unrotate32(k2, p.rope_cos, p.rope_sin, token % static_cast<size_t>(p.S), c * 16);
         uint4* d4 = reinterpret_cast<uint4*>(dvp + c * 32);
         uint4* k4 = reinterpret_cast<uint4*>(dkp + c * 32);
 #pragma unroll
@@ -727,6 +749,7 @@ __global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_bwd_dq_kernel(const 
         uint32_t a[32];
         tmem_ld_32x32(t_dq + lane_base + c * 32, a);
         tmem_ld_wait();
+        if (p.rope_cos) unrotate32(a, p.rope_cos, p.rope_sin, token % static_cast<size_t>(p.S), c * 16);
         uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
@@ -814,12 +837,29 @@ int b2_attention_fwd(const void* q, const void* k, const void* v, long long q_pi
   return b2_attention_fwd_ex(q, k, v, q_pitch, k_pitch, v_pitch, out, lse, B, S, Hq, Hkv, scale, 1, status, stream);
 }
 
+int b2_attention_bwd_rope(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                          const float* lse, long long q_pitch, long long k_pitch, long long v_pitch, float* delta,
+                          void* dq, void* dk, void* dv, long long dq_pitch, long long dk_pitch, long long dv_pitch,
+                          int B, int S, int Hq, int Hkv, float scale, int causal, const float* rope_cos,
+                          const float* rope_sin, int* status, cudaStream_t stream);
+
 // dout, out: [B,S,Hq,128] contiguous; delta: fp32 [B,Hq,S] scratch; dq [B,S,Hq,128], dk, dv [B,S,Hkv,128] with
 // token pitches dq_pitch, dk_pitch, dv_pitch (they may be views into one fused gradient buffer).
 int b2_attention_bwd_ex(const void* dout, const void* q, const void* k, const void* v, const void* out,
                         const float* lse, long long q_pitch, long long k_pitch, long long v_pitch, float* delta,
                         void* dq, void* dk, void* dv, long long dq_pitch, long long dk_pitch, long long dv_pitch,
                         int B, int S, int Hq, int Hkv, float scale, int causal, int* status, cudaStream_t stream) {
+  return b2_attention_bwd_rope(dout, q, k, v, out, lse, q_pitch, k_pitch, v_pitch, delta, dq, dk, dv, dq_pitch,
+                               dk_pitch, dv_pitch, B, S, Hq, Hkv, scale, causal, nullptr, nullptr, status, stream);
+}
+
+// The same with optional rotary tables (fp32 [S, 64]): q and k are the ROTATED tensors the forward pass saw, and dq,
+// dk are stored rotated back, i.e. as gradients of the unrotated projections.
+int b2_attention_bwd_rope(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                          const float* lse, long long q_pitch, long long k_pitch, long long v_pitch, float* delta,
+                          void* dq, void* dk, void* dv, long long dq_pitch, long long dk_pitch, long long dv_pitch,
+                          int B, int S, int Hq, int Hkv, float scale, int causal, const float* rope_cos,
+                          const float* rope_sin, int* status, cudaStream_t stream) {
   if (S % 128 || Hq % Hkv) return -10;
   AttnParams p{};
   const long long tokens = static_cast<long long>(B) * S;
@@ -831,6 +871,7 @@ int b2_attention_bwd_ex(const void* dout, const void* q, const void* k, const vo
   p.lse = const_cast<float*>(lse); p.delta = delta; p.dq = static_cast<__nv_bfloat16*>(dq);
   p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv); p.status = status;
   p.dq_pitch = dq_pitch; p.dk_pitch = dk_pitch; p.dv_pitch = dv_pitch;
+  p.rope_cos = rope_cos; p.rope_sin = rope_sin;
   static bool set = false;
   if (!set) {
     if (cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess ||

@@ -445,6 +445,69 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(__nv_bfloat16
   }
 }
 
+// The same with the whole row held in registers (V <= CE_THREADS * 8 * CE_REG_CHUNKS): one read and one write of
+// the logits instead of three reads and one write.  ``loss_scale`` weighs the row's loss in ``loss`` (1/T for a
+// mean over T tokens), ``grad_scale`` multiplies the gradient written back (1/T times whatever the caller
+// back-propagates into the loss).
+constexpr int CE_REG_CHUNKS = 8;
+__global__ void __launch_bounds__(CE_THREADS) cross_entropy_reg_kernel(__nv_bfloat16* __restrict__ logits,
+                                                                      const long long* __restrict__ targets,
+                                                                      float* __restrict__ loss, int T, int V,
+                                                                      float loss_scale, float grad_scale) {
+  __shared__ float scratch[CE_THREADS / 32];
+  float local_loss = 0.f;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    __nv_bfloat16* row = logits + static_cast<size_t>(t) * V;
+    bf16x8 raw[CE_REG_CHUNKS];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < CE_REG_CHUNKS; ++k) {
+      const int c = (k * CE_THREADS + threadIdx.x) * 8;
+      if (c < V) {
+        raw[k] = *reinterpret_cast<const bf16x8*>(row + c);
+        float v[8];
+        unpack8(raw[k], v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx = fmaxf(mx, v[i]);
+      }
+    }
+    mx = block_max<CE_THREADS>(mx, scratch);
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < CE_REG_CHUNKS; ++k) {
+      const int c = (k * CE_THREADS + threadIdx.x) * 8;
+      if (c < V) {
+        float v[8];
+        unpack8(raw[k], v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum += __expf(v[i] - mx);
+      }
+    }
+    sum = block_sum<CE_THREADS>(sum, scratch);
+    const float inv = 1.f / sum;
+    const int target = static_cast<int>(targets[t]);
+#pragma unroll
+    for (int k = 0; k < CE_REG_CHUNKS; ++k) {
+      const int c = (k * CE_THREADS + threadIdx.x) * 8;
+      if (c < V) {
+        float v[8];
+        unpack8(raw[k], v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (c + i == target) local_loss += (logf(sum) + mx - v[i]) * loss_scale;
+          v[i] = __expf(v[i] - mx) * inv;
+          if (c + i == target) v[i] -= 1.f;
+          v[i] *= grad_scale;
+        }
+        *reinterpret_cast<bf16x8*>(row + c) = pack8(v);
+      }
+    }
+  }
+  // one atomic per CTA: the thread that met a target holds that row's loss
+  local_loss = block_sum<CE_THREADS>(local_loss, scratch);
+  if (threadIdx.x == 0 && local_loss != 0.f) atomicAdd(loss, local_loss);
+}
+
 __global__ void scale_bf16_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ factor, size_t n8) {
   const float f = *factor;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n8;
@@ -598,10 +661,21 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
   }
 }
 
-static inline int grid_for(size_t work, int threads, int cap = 148 * 16) {
+// SM count of the current device (grids are sized as a multiple of it).
+static inline int sm_count_ew() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return sms;
+}
+static inline int grid_for(size_t work, int threads, int per_sm = 16) {
   size_t blocks = (work + threads - 1) / threads;
   if (blocks < 1) blocks = 1;
-  return static_cast<int>(blocks > static_cast<size_t>(cap) ? cap : blocks);
+  const size_t cap = static_cast<size_t>(sm_count_ew()) * per_sm;
+  return static_cast<int>(blocks > cap ? cap : blocks);
 }
 static inline int ok() { return cudaGetLastError() == cudaSuccess ? 0 : -1; }
 
@@ -615,7 +689,7 @@ extern "C" {
 int b2_rmsnorm_fwd(const void* x, const void* delta, const float* w, void* sum_out, void* y, float* rstd, int rows,
                    int D, float eps, cudaStream_t s) {
   if (D % 8 || D > NORM_THREADS * 8 * NORM_MAX_CHUNKS) return -10;
-  const int grid = min(rows, 148 * 8);
+  const int grid = min(rows, sm_count_ew() * 8);
 #define B2_NORM_FWD(CH)                                                                                         \
   rmsnorm_fwd_kernel<CH><<<grid, NORM_THREADS, 0, s>>>((const bf16*)x, (const bf16*)delta, w, (bf16*)sum_out, \
                                                        (bf16*)y, rstd, rows, D, eps)
@@ -627,7 +701,7 @@ int b2_rmsnorm_fwd(const void* x, const void* delta, const float* w, void* sum_o
 }
 
 // dw_partial: fp32 [parts, D] scratch with parts = b2_rmsnorm_bwd_parts(rows); dw: fp32 [D] (overwritten).
-int b2_rmsnorm_bwd_parts(int rows) { return min(rows, 148 * 6); }
+int b2_rmsnorm_bwd_parts(int rows) { return min(rows, sm_count_ew() * 6); }
 int b2_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* residual, void* dx,
                    float* dw_partial, float* dw, int rows, int D, cudaStream_t s) {
   if (D % 8 || D > NORM_THREADS * 8 * NORM_MAX_CHUNKS) return -10;
@@ -653,7 +727,7 @@ int b2_skinny_nt(const void* x, const void* w, float* out, int T, int N, int K, 
     cudaFuncSetAttribute(skinny_nn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     set = true;
   }
-  skinny_nt_kernel<<<min((T + 7) / 8, 148 * 2), 256, smem, s>>>((const bf16*)x, (const bf16*)w, out, T, N, K);
+  skinny_nt_kernel<<<min((T + 7) / 8, sm_count_ew() * 2), 256, smem, s>>>((const bf16*)x, (const bf16*)w, out, T, N, K);
   return ok();
 }
 int b2_skinny_nn(const float* dy, const void* w, void* dx, int T, int N, int K, cudaStream_t s) {
@@ -665,12 +739,12 @@ int b2_skinny_nn(const float* dy, const void* w, void* dx, int T, int N, int K, 
     cudaFuncSetAttribute(skinny_nn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     set = true;
   }
-  skinny_nn_kernel<<<min((T + 7) / 8, 148 * 2), 256, smem, s>>>(dy, (const bf16*)w, (bf16*)dx, T, N, K);
+  skinny_nn_kernel<<<min((T + 7) / 8, sm_count_ew() * 2), 256, smem, s>>>(dy, (const bf16*)w, (bf16*)dx, T, N, K);
   return ok();
 }
 int b2_skinny_tn(const float* dy, const void* x, float* dw, int T, int N, int K, cudaStream_t s) {
   if (N > SKINNY_MAX_N || K % 8) return -10;
-  const int ctas = min(148 * 2, (T + 31) / 32);
+  const int ctas = min(sm_count_ew() * 2, (T + 31) / 32);
   const int per = (T + ctas - 1) / ctas;
   skinny_tn_kernel<<<ctas, 256, 0, s>>>(dy, (const bf16*)x, dw, T, N, K, per);
   return ok();
@@ -699,7 +773,20 @@ int b2_swiglu_bwd(const void* dh, const void* gate, const void* up, void* dgu, v
 // loss must be zeroed by the caller; scale is usually 1/T (mean over tokens).
 int b2_cross_entropy(void* logits, const long long* targets, float* loss, int T, int V, float scale, cudaStream_t s) {
   if (V % 8) return -10;
-  cross_entropy_kernel<<<min(T, 148 * 4), CE_THREADS, 0, s>>>((bf16*)logits, targets, loss, T, V, scale);
+  cross_entropy_kernel<<<min(T, sm_count_ew() * 4), CE_THREADS, 0, s>>>((bf16*)logits, targets, loss, T, V, scale);
+  return ok();
+}
+// Loss and gradient scaled separately; rows up to 32768 entries stay in registers (one read, one write).
+int b2_cross_entropy2(void* logits, const long long* targets, float* loss, int T, int V, float loss_scale,
+                      float grad_scale, cudaStream_t s) {
+  if (V % 8) return -10;
+  if (V > CE_THREADS * 8 * CE_REG_CHUNKS && loss_scale != grad_scale) return -11;   // the streaming kernel has one scale
+  if (V <= CE_THREADS * 8 * CE_REG_CHUNKS) {
+    cross_entropy_reg_kernel<<<min(T, sm_count_ew() * 4), CE_THREADS, 0, s>>>((bf16*)logits, targets, loss, T, V,
+                                                                              loss_scale, grad_scale);
+    return ok();
+  }
+  cross_entropy_kernel<<<min(T, sm_count_ew() * 4), CE_THREADS, 0, s>>>((bf16*)logits, targets, loss, T, V, loss_scale);
   return ok();
 }
 int b2_scale_bf16(void* x, const float* factor, long long n, cudaStream_t s) {
@@ -711,7 +798,7 @@ int b2_scale_bf16(void* x, const float* factor, long long n, cudaStream_t s) {
 // dtype codes: 0 fp32, 1 bf16.  p_bf16 may be null.
 int b2_adamw(void* p, const void* g, void* m, void* v, void* p_bf16, long long n, int p_dt, int g_dt, int s_dt,
              float lr, float beta1, float beta2, float eps, float wd, float a_t, float grad_scale, cudaStream_t s) {
-  const int grid = grid_for((n + 7) / 8, 256, 148 * 16);
+  const int grid = grid_for((n + 7) / 8, 256, 16);
 #define B2_ADAMW(P, G, S)                                                                                      \
   adamw_kernel<P, G, S><<<grid, 256, 0, s>>>((P*)p, (const G*)g, (S*)m, (S*)v, (bf16*)p_bf16, n, lr, beta1, beta2, \
                                              eps, wd, a_t, grad_scale)
@@ -731,7 +818,7 @@ int b2_adamw(void* p, const void* g, void* m, void* v, void* p_bf16, long long n
   return ok();
 }
 int b2_cast_f32_bf16(const float* src, void* dst, long long n, cudaStream_t s) {
-  cast_f32_bf16_kernel<<<grid_for(n, 256, 148 * 32), 256, 0, s>>>(src, (bf16*)dst, n);
+  cast_f32_bf16_kernel<<<grid_for(n, 256, 32), 256, 0, s>>>(src, (bf16*)dst, n);
   return ok();
 }
 

@@ -53,6 +53,8 @@ enum Epilogue : int {
   EPI_ACC_BF16 = 2,     // D[M,N] bf16 += acc
   EPI_SWIGLU = 3,       // H[M,N/2] = silu(acc[:, :128]) * acc[:, 128:]; optional gate/up stores
   EPI_STORE_F32 = 4,    // D[M,N] fp32 = acc
+  EPI_ROPE = 6,         // D[M,N] bf16 = acc with the rotary embedding applied to the leading rope_cols columns
+                        // (adjacent pairs, heads of 128 columns, position = row mod rope_seq): the fused q/k/v projection
   EPI_PUSH = 5,         // expert-parallel return: row r, scaled by push_w[r], is stored as bf16 into row push_tag[r]
                         // of rank push_src[r]'s buffer through its peer pointer; the last CTA raises a flag
 };
@@ -81,6 +83,10 @@ struct GemmParams {
   long long d_expert_stride;   // elements between experts in d (SCHED_WGRAD)
   float beta;                  // 1 accumulate, 0 overwrite (EPI_ACC_*)
   int* status;                 // device word; non-zero = a wait ran out
+  // EPI_ROPE only
+  const float* rope_cos;       // [rope_seq, 64] fp32
+  const float* rope_sin;
+  int rope_cols, rope_seq;
   // EPI_PUSH only
   Peers push_dst;              // every rank's return buffer [slots, ldd] bf16
   const int* push_tag;         // [M] destination row (slot id) of each row, -1 for padding rows
@@ -404,6 +410,31 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
                                   pack_bf16(w * __uint_as_float(v[8 * i + 2]), w * __uint_as_float(v[8 * i + 3])),
                                   pack_bf16(w * __uint_as_float(v[8 * i + 4]), w * __uint_as_float(v[8 * i + 5])),
                                   pack_bf16(w * __uint_as_float(v[8 * i + 6]), w * __uint_as_float(v[8 * i + 7])));
+          } else if (EPI == EPI_ROPE) {
+            if (col < p.rope_cols) {
+              // 32 consecutive columns of one head: pairs (2j, 2j+1), table entries [pos][(col mod 128)/2 + j]
+              const size_t tab = static_cast<size_t>(row % p.rope_seq) * 64 + ((col & 127) >> 1);
+              const float4* c4 = reinterpret_cast<const float4*>(p.rope_cos + tab);
+              const float4* s4 = reinterpret_cast<const float4*>(p.rope_sin + tab);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float4 cc = c4[q], ss = s4[q];
+                const float cv[4] = {cc.x, cc.y, cc.z, cc.w}, sv[4] = {ss.x, ss.y, ss.z, ss.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float x0 = __uint_as_float(v[8 * q + 2 * j]), x1 = __uint_as_float(v[8 * q + 2 * j + 1]);
+                  v[8 * q + 2 * j] = __float_as_uint(x0 * cv[j] - x1 * sv[j]);
+                  v[8 * q + 2 * j + 1] = __float_as_uint(x0 * sv[j] + x1 * cv[j]);
+                }
+              }
+            }
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.d) + off);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              dst[i] = make_uint4(pack_bf16(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
+                                  pack_bf16(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
+                                  pack_bf16(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
+                                  pack_bf16(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])));
           } else if (EPI == EPI_STORE_BF16) {
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.d) + off);
 #pragma unroll
@@ -671,6 +702,24 @@ int b2_gemm_nn(const void* a, const void* w, const void* w2, void* d, int M, int
   p.tile_expert = tile_expert; p.num_m_tiles = num_m_tiles; p.d = d; p.ldd = ldd; p.status = status;
   p.group_align256 = group_align256;
   return launch<0, 1, EPI_STORE_BF16, SCHED_FLAT>(p, sm_count(), stream);
+}
+
+// y[M,N] = a[M,K] * w[N,K]^T with the rotary embedding applied to columns [0, rope_cols) in the epilogue: column c
+// belongs to head c / 128, pairs (2j, 2j+1) inside a head are rotated by the angle of table entry
+// [row mod seq][j] (cos, sin: fp32 [seq, 64]).  rope_cols is a multiple of 128.
+int b2_gemm_nt_rope(const void* a, const void* w, void* d, int M, int N, int K, long long lda, long long ldd,
+                    const float* cos_t, const float* sin_t, int rope_cols, int seq, int* status,
+                    cudaStream_t stream) {
+  if (N % 32 || K % 8 || rope_cols % 128 || rope_cols > N || seq < 1) return -10;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.num_experts = 1; p.b_expert_rows = N; p.k_split = 0;
+  p.d = d; p.ldd = ldd; p.status = status; p.beta = 0.f;
+  p.rope_cos = cos_t; p.rope_sin = sin_t; p.rope_cols = rope_cols; p.rope_seq = seq;
+  const int sms = sm_count();
+  const TileKind kind = choose_tile<SCHED_FLAT>(p, sms, pair_available<0, 0, EPI_ROPE, SCHED_FLAT>(sms));
+  if (make_map(&p.map_a, a, K, M, lda, BM)) return -11;
+  if (make_map(&p.map_b, w, K, N, K, kind == TILE_PAIR ? BN / 2 : BN)) return -12;
+  return launch<0, 0, EPI_ROPE, SCHED_FLAT>(p, kind, sms, stream);
 }
 
 static void fill_push(GemmParams& p, const unsigned long long* dst, const int* tag, const int* src, const float* w,

@@ -185,6 +185,16 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
 using namespace b2;
 typedef __nv_bfloat16 bf16;
 
+static int sm_count_moe() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return sms;
+}
+
 extern "C" {
 
 // idx: int64 [slots] expert of each slot.  Outputs int32: slot_row [slots], row_slot [capacity_rows],
@@ -207,7 +217,7 @@ int b2_moe_plan(const long long* idx, int slots, int E, int* slot_row, int* row_
 int b2_moe_gather(const void* x, const int* row_slot, const int* meta, const float* scale, const void* y_perm,
                   float* dweights, void* x_perm, int D, int capacity_rows, int slots, cudaStream_t s) {
   if (D % 8) return -10;
-  moe_gather_kernel<<<148 * 8, 256, 0, s>>>((const bf16*)x, row_slot, meta, scale, (const bf16*)y_perm, dweights,
+  moe_gather_kernel<<<sm_count_moe() * 8, 256, 0, s>>>((const bf16*)x, row_slot, meta, scale, (const bf16*)y_perm, dweights,
                                             (bf16*)x_perm, D, capacity_rows, slots);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -215,7 +225,7 @@ int b2_moe_gather(const void* x, const int* row_slot, const int* meta, const flo
 int b2_moe_combine(const void* y_perm, const int* slot_row, const float* weights, const void* residual, void* out,
                    int T, int D, int rows, cudaStream_t s) {
   if (D % 8) return -10;
-  moe_combine_kernel<<<min((T + 7) / 8, 148 * 8), 256, 0, s>>>((const bf16*)y_perm, slot_row, weights,
+  moe_combine_kernel<<<min((T + 7) / 8, sm_count_moe() * 8), 256, 0, s>>>((const bf16*)y_perm, slot_row, weights,
                                                                (const bf16*)residual, (bf16*)out, T, D, rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -155,13 +155,20 @@ class MultiHeadLayerLL(nn.Module):
         hq, hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         fused_rope = False
         if self.qkv_weight is not None:
-            qkv = ops.linear(x.reshape(batch * seq, -1), self.qkv_weight)
             from ..ops.attention import attention_backend, fused_qkv_attention
-            if (token_positions is None and mask is None and ops.use_native(qkv, "attention")
+            x2d = x.reshape(batch * seq, -1)
+            if (token_positions is None and mask is None and ops.use_native(x2d, "attention")
                     and attention_backend() == "native" and hd == 128 and seq % 128 == 0):
+                # RoPE rides in the projection GEMM's epilogue (forward) and in the attention backward kernels'
+                # epilogues (its transpose), so q and k are never re-read just to be rotated
                 cos, sin = (self.RoPE.cos, self.RoPE.sin) if self.use_rope else (None, None)
-                out = fused_qkv_attention(qkv, batch, seq, hq, hkv, hd, cos, sin)
+                if self.use_rope:
+                    qkv = ops.linear_rope(x2d, self.qkv_weight, cos, sin, (hq + hkv) * hd, seq)
+                else:
+                    qkv = ops.linear(x2d, self.qkv_weight)
+                out = fused_qkv_attention(qkv, batch, seq, hq, hkv, hd, cos, sin, pre_rotated=self.use_rope)
                 return self.output_proj(out.reshape(batch, seq, hq * hd))
+            qkv = ops.linear(x2d, self.qkv_weight)
             if self.use_rope and token_positions is None and mask is None and ops.use_native(qkv, "rope"):
                 from ..ops.attention import rope_qk_
                 qkv = rope_qk_(qkv, seq, hq + 2 * hkv, hq + hkv, hd, self.RoPE.cos, self.RoPE.sin)

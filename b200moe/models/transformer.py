@@ -95,13 +95,15 @@ class TransformerLMPipelined(nn.Module):
             x = self.lm_head(self.ln_final(x))
         return (x, aux) if return_aux_loss else x
 
-    def loss(self, x, targets, return_aux_loss=False):
+    def loss(self, x, targets, return_aux_loss=False, grad_scale=None):
         """Last stage only: mean next-token loss with the head fused into the
-        loss kernel; the logits are never returned."""
+        loss kernel; the logits are never returned.  ``grad_scale``: the factor
+        the caller will back-propagate into the loss, if it knows it already
+        (lets the head form its gradients chunk by chunk in the forward pass)."""
         out = self.hidden(x, return_aux_loss)
         x, aux = out if return_aux_loss else (out, None)
         weight = self.lm_head.compute_weight if self.lm_head.compute_weight is not None else self.lm_head.weight
-        value = ops.lm_head_cross_entropy(self.ln_final(x), weight, targets)
+        value = ops.lm_head_cross_entropy(self.ln_final(x), weight, targets, grad_scale)
         return (value, aux) if return_aux_loss else value
 
 

@@ -40,12 +40,12 @@ def use_native(t: torch.Tensor, op: str = "") -> bool:
     return native.has(op)
 
 
-from .dense import linear, embedding, rmsnorm, add_rmsnorm  # noqa: E402
+from .dense import linear, linear_rope, embedding, rmsnorm, add_rmsnorm  # noqa: E402
 from .attention import rope_attention  # noqa: E402
 from .loss import lm_head_cross_entropy  # noqa: E402
 from .moe import router_top2, moe_ffn, DispatchPlan  # noqa: E402
 
 __all__ = [
-    "Fn", "set_native", "native_enabled", "use_native", "linear", "embedding", "rmsnorm", "add_rmsnorm",
+    "Fn", "set_native", "native_enabled", "use_native", "linear", "linear_rope", "embedding", "rmsnorm", "add_rmsnorm",
     "rope_attention", "lm_head_cross_entropy", "router_top2", "moe_ffn", "DispatchPlan",
 ]

@@ -65,10 +65,10 @@ class _FusedQKVAttention(torch.autograd.Function):
     so autograd sees a single gradient for the projection output."""
 
     @staticmethod
-    def forward(ctx, qkv, batch, seq, hq, hkv, hd, cos, sin):
+    def forward(ctx, qkv, batch, seq, hq, hkv, hd, cos, sin, pre_rotated):
         native = _native()
         total = hq + 2 * hkv
-        if cos is not None:
+        if cos is not None and not pre_rotated:      # the projection GEMM did not rotate q and k in its epilogue
             native.rope_inplace(qkv, 0, qkv.shape[0], seq, hq + hkv, hd, total * hd, cos, sin, 1.0)
         ctx.mark_dirty(qkv)
         view = qkv.view(batch, seq, total, hd)
@@ -86,16 +86,19 @@ class _FusedQKVAttention(torch.autograd.Function):
         view = qkv.view(batch, seq, total, hd)
         dqkv = torch.empty_like(qkv)
         dview = dqkv.view(batch, seq, total, hd)
+        # the backward kernels rotate dq and dk back as they store them
         native.attention_bwd(dout, view[:, :, :hq], view[:, :, hq:hq + hkv], view[:, :, hq + hkv:], out, lse,
+                             cos=cos, sin=sin,
                              grads=(dview[:, :, :hq], dview[:, :, hq:hq + hkv], dview[:, :, hq + hkv:]))
-        if cos is not None:
-            native.rope_inplace(dqkv, 0, dqkv.shape[0], seq, hq + hkv, hd, total * hd, cos, sin, -1.0)
-        return dqkv, None, None, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None, None, None
 
 
-def fused_qkv_attention(qkv2d, batch, seq, hq, hkv, hd, cos, sin):
-    """Returns the attention output ``[B, S, Hq, hd]`` of a fused projection ``[B*S, (Hq+2Hkv)*hd]``."""
-    _, out = _FusedQKVAttention.apply(qkv2d, batch, seq, hq, hkv, hd, cos, sin)
+def fused_qkv_attention(qkv2d, batch, seq, hq, hkv, hd, cos, sin, pre_rotated: bool = False):
+    """Returns the attention output ``[B, S, Hq, hd]`` of a fused projection ``[B*S, (Hq+2Hkv)*hd]``.
+    ``pre_rotated``: q and k inside ``qkv2d`` already carry the rotation (``ops.linear_rope``)."""
+    if cos is not None:
+        cos, sin = cos[:seq].contiguous(), sin[:seq].contiguous()
+    _, out = _FusedQKVAttention.apply(qkv2d, batch, seq, hq, hkv, hd, cos, sin, pre_rotated)
     return out
 
 

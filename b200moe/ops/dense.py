@@ -28,7 +28,10 @@ def _use_native(t, op):
 
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight):
+    def forward(ctx, x, weight, rope=None):
+        """``rope``: optional ``(cos, sin, rope_cols, seq)``: the rotary embedding is applied to the leading
+        ``rope_cols`` output columns in the GEMM epilogue.  The backward pass then expects the gradient of the
+        UNROTATED output (the attention backward kernels deliver exactly that)."""
         ctx.weight = weight
         ctx.save_for_backward(x)
         x2d = x.reshape(-1, x.shape[-1])
@@ -38,6 +41,12 @@ class _Linear(torch.autograd.Function):
         if gather is not None:
             weight.pending_gather = None
             y = gather(x2d if x2d.is_contiguous() else x2d.contiguous())
+            if rope is not None:
+                cos, sin, cols, seq = rope
+                _native().rope_inplace(y, 0, y.shape[0], seq, cols // 128, 128, y.shape[1], cos, sin, 1.0)
+        elif rope is not None:
+            cos, sin, cols, seq = rope
+            y = _native().gemm_nt_rope(x2d, weight, cos, sin, cols, seq)
         elif _use_native(x, "gemm"):
             y = _native().gemm_nt(x2d, weight)
         else:
@@ -74,12 +83,19 @@ class _Linear(torch.autograd.Function):
                 dw = _native().gemm_tn(dy2d, x2d, out_dtype=weight.dtype)
             else:
                 dw = (dy2d.t() @ x2d).to(weight.dtype)
-        return dx, dw
+        return dx, dw, None
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``y = x @ weightᵀ`` with ``weight`` of shape ``[d_out, d_in]``; no bias."""
     return _Linear.apply(x, weight)
+
+
+def linear_rope(x: torch.Tensor, weight: torch.Tensor, cos, sin, rope_cols: int, seq: int) -> torch.Tensor:
+    """GPU only: ``x @ weightᵀ`` (``x [tokens, d_in]``, tokens laid out as sequences of ``seq``) with the rotary
+    embedding (heads of 128 columns, adjacent pairs) applied to output columns ``[0, rope_cols)`` inside the GEMM.
+    Its backward pass takes the gradient with respect to the unrotated product."""
+    return _Linear.apply(x, weight, (cos[:seq].contiguous(), sin[:seq].contiguous(), rope_cols, seq))
 
 
 class _Embedding(torch.autograd.Function):

@@ -201,7 +201,23 @@ def gemm_nt(x, w, out_dtype=None, tile_expert=None, num_m_tiles=None, num_expert
     return out
 
 
-def gemm_nn(dy, w, w2=None, tile_expert=None, num_m_tiles=None, num_experts: int = 1, align256: bool = False):
+def gemm_nt_rope(x, w, cos, sin, rope_cols: int, seq: int):
+    """``x [M,K] @ w [N,K]ᵀ`` with the rotary embedding applied, in the GEMM epilogue, to output columns
+    ``[0, rope_cols)``: heads of 128 columns, adjacent pairs, position ``row mod seq``; ``cos``/``sin`` fp32
+    ``[>=seq, 64]``."""
+    M, K = x.shape
+    N = w.shape[0]
+    if cos.shape[-1] != 64 or cos.dtype != torch.float32 or not cos.is_contiguous() or cos.shape[0] < seq:
+        raise ValueError("rotary tables must be contiguous fp32 [>= seq, 64] (head_dim 128)")
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    assert x.stride(-1) == 1 and w.is_contiguous()
+    _call("b2_gemm_nt_rope", _p(_bf16(x)), _p(_bf16(w)), _p(out), _I(M), _I(N), _I(K), _L(x.stride(0)), _L(N),
+          _p(cos), _p(sin), _I(rope_cols), _I(seq), _p(status_word(x.device)), _stream())
+    return out
+
+
+def gemm_nn(dy, w, w2=None, tile_expert=None, num_m_tiles=None, num_experts: int = 1, align256: bool = False,
+            out=None):
     """``dy [M,K] @ w[e] [K,N]`` (``w`` rows are the reduction index).  With ``w2``
     the reduction continues over ``w2``'s rows: ``dy = [a | b]``, result ``a w + b w2``."""
     M, K = dy.shape
@@ -210,11 +226,12 @@ def gemm_nn(dy, w, w2=None, tile_expert=None, num_m_tiles=None, num_experts: int
         out = torch.empty(M, N, dtype=torch.bfloat16, device=dy.device)
         _call("b2_skinny_nn", _p(dy.float().contiguous()), _p(_bf16(w)), _p(out), _I(M), _I(K), _I(N), _stream())
         return out
-    out = torch.empty(M, N, dtype=torch.bfloat16, device=dy.device)
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dy.device)
     k_split = w.shape[-2] if w2 is not None else 0
-    assert dy.stride(-1) == 1 and w.is_contiguous()
-    _call("b2_gemm_nn", _p(_bf16(dy)), _p(_bf16(w)), _p(w2), _p(out), _I(M), _I(N), _I(K), _I(k_split),
-          _L(dy.stride(0)), _L(N), _L(N), _I(num_experts), _p(tile_expert), _p(num_m_tiles), _I(int(align256)),
+    assert dy.stride(-1) == 1 and w.is_contiguous() and out.stride(-1) == 1 and out.shape == (M, N)
+    _call("b2_gemm_nn", _p(_bf16(dy)), _p(_bf16(w)), _p(w2), _p(_bf16(out)), _I(M), _I(N), _I(K), _I(k_split),
+          _L(dy.stride(0)), _L(N), _L(out.stride(0)), _I(num_experts), _p(tile_expert), _p(num_m_tiles), _I(int(align256)),
           _p(status_word(dy.device)), _stream())
     return out
 
@@ -319,6 +336,15 @@ def cross_entropy_fwd_bwd_(logits, targets):
     T, V = logits.shape
     loss = torch.zeros((), dtype=torch.float32, device=logits.device)
     _call("b2_cross_entropy", _p(_bf16(logits)), _p(targets.contiguous()), _p(loss), _I(T), _I(V), _F(1.0 / T), _stream())
+    return loss
+
+
+def cross_entropy_scaled_(logits, targets, loss, loss_scale: float, grad_scale: float):
+    """Adds ``loss_scale · Σ_rows CE`` to ``loss`` (fp32 scalar tensor) and overwrites ``logits`` (bf16 [T,V]) with
+    ``grad_scale · (softmax − onehot)``; rows up to 32768 entries are read once and written once."""
+    T, V = logits.shape
+    _call("b2_cross_entropy2", _p(_bf16(logits)), _p(targets.contiguous()), _p(loss), _I(T), _I(V), _F(loss_scale),
+          _F(grad_scale), _stream())
     return loss
 
 
@@ -453,8 +479,10 @@ def attention_fwd(q, k, v, cos=None, sin=None, causal=True):
 
 
 def attention_bwd(dout, q, k, v, out, lse, cos=None, sin=None, grads=None, causal=True):
-    """Gradients of ``attention_fwd`` w.r.t. the (rotated) q, k and v.  ``grads`` may give three preallocated
-    ``[B,S,H,128]`` views (for instance slices of one fused buffer) to write into."""
+    """Gradients of ``attention_fwd``.  ``q`` and ``k`` are the tensors the forward kernel saw (rotated, if a
+    rotation was applied); with ``cos``/``sin`` the kernels store dq and dk rotated back, i.e. as gradients of the
+    unrotated q and k.  ``grads`` may give three preallocated ``[B,S,H,128]`` views (for instance slices of one
+    fused buffer) to write into."""
     B, S, Hq, hd = q.shape
     Hkv = k.shape[2]
     if grads is None:
@@ -464,13 +492,12 @@ def attention_bwd(dout, q, k, v, out, lse, cos=None, sin=None, grads=None, causa
     dq, dk, dv = grads
     delta = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
     dout = _bf16(dout).contiguous()
-    _call("b2_attention_bwd_ex", _p(dout), _p(q), _p(k), _p(v), _p(_bf16(out)), _p(lse), _L(_token_pitch(q)),
+    if cos is not None and (cos.shape[-1] != 64 or not cos.is_contiguous() or cos.shape[0] < S):
+        raise ValueError("rotary tables must be contiguous fp32 [>= S, 64]")
+    _call("b2_attention_bwd_rope", _p(dout), _p(q), _p(k), _p(v), _p(_bf16(out)), _p(lse), _L(_token_pitch(q)),
           _L(_token_pitch(k)), _L(_token_pitch(v)), _p(delta), _p(dq), _p(dk), _p(dv), _L(_token_pitch(dq)),
           _L(_token_pitch(dk)), _L(_token_pitch(dv)), _I(B), _I(S), _I(Hq), _I(Hkv), _F(hd ** -0.5),
-          _I(int(causal)), _p(status_word(q.device)), _stream(), n=3)
-    if cos is not None:
-        rope_inplace(dq, 0, B * S, S, Hq, hd, _token_pitch(dq), cos, sin, -1.0)
-        rope_inplace(dk, 0, B * S, S, Hkv, hd, _token_pitch(dk), cos, sin, -1.0)
+          _I(int(causal)), _p(cos), _p(sin), _p(status_word(q.device)), _stream(), n=3)
     return dq, dk, dv
 
 

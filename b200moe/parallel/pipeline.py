@@ -124,8 +124,10 @@ def pipelined_train_overlap(model, optimizer, x, x_label, x_spec: list[int], spl
             x_in.requires_grad_(True)
         aux = None
         if fused_loss:
-            out = model.loss(x_in, label_chunks[forward_count], return_aux_loss=True) if router_aux_loss_coef \
-                else model.loss(x_in, label_chunks[forward_count])
+            # the loss of a microbatch is back-propagated with the factor 1/split_num (backward_microbatch below)
+            scale = {"grad_scale": 1.0 / split_num} if torch.is_grad_enabled() else {}
+            out = model.loss(x_in, label_chunks[forward_count], return_aux_loss=True, **scale) \
+                if router_aux_loss_coef else model.loss(x_in, label_chunks[forward_count], **scale)
         else:
             out = model(x_in, return_aux_loss=True) if router_aux_loss_coef else model(x_in)
         if router_aux_loss_coef:

@@ -99,7 +99,9 @@ def build_model(config: dict, mesh, device, fsdp_group, ddp_group, compute_dtype
             num_heads=model_cfg["num_head"], experts_total=model_cfg["num_expert_per_node"] * fsdp, ep=fsdp,
             blocks=len(model.layers), pp=mesh.pp, stage=mesh.stage, microbatches=train_cfg["microbatch_num"],
             vocab=data_cfg["vocab_size"], device=device,
-            margin_bytes=int(float(train_cfg.get("activation_margin_gib", 6.0)) * 2 ** 30))
+            margin_bytes=int(float(train_cfg.get("activation_margin_gib", 6.0)) * 2 ** 30),
+            # with the exchange fused into the expert GEMMs a call keeps no routing-dependent tensor but gate/up
+            routed_row_bytes=0 if (comm is not None and fsdp > 1 and comm.ep_mode == "pull") else None)
         for layer in model.layers:
             layer.ffn.budget = budget
         wrapped.activation_budget = budget

@@ -189,6 +189,27 @@ def test_cross_entropy_and_lm_head(native):
     assert _rel(h.grad, hr.grad) < 3e-2 and _rel(w.grad, wr.grad) < 3e-2
 
 
+def test_lm_head_forms_its_gradients_in_the_forward_pass_when_the_loss_factor_is_known(native):
+    """Three token chunks (one ragged); the weight gradient lands in ``main_grad`` with the announced factor."""
+    from b200moe import ops
+    T, D, V = 2 * 4096 + 640, 128, 4096
+    h = _rand(T, D).requires_grad_(True)
+    w = _rand(V, D, scale=0.05)
+    w.main_grad = torch.zeros(V, D, device="cuda")
+    t = torch.randint(0, V, (T,), device="cuda")
+    hr, wr = h.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(hr @ wr.t(), t)
+    (ref * 0.25).backward()
+    for announced in (0.25, None):
+        w.main_grad.zero_()
+        h.grad = None
+        loss = ops.lm_head_cross_entropy(h, w, t, grad_scale=announced)
+        assert abs(float(loss) - float(ref)) < 2e-2
+        (loss * 0.25).backward()
+        assert _rel(h.grad, hr.grad) < 3e-2, announced
+        assert _rel(w.main_grad, wr.grad) < 3e-2, announced
+
+
 def test_embedding_rope_adamw(native):
     from b200moe import ops
     from b200moe.ops import functional as Fn
@@ -434,6 +455,39 @@ def test_fused_qkv_attention_with_rope(native):
     ref.backward(g.float())
     assert _rel(base.grad, ref_in.grad) < 2e-2
     native.check_status()
+
+
+@pytest.mark.parametrize("tile", [0, 3], ids=["tiles_auto", "tiles_cta_pair"])
+def test_projection_with_rope_in_the_gemm_epilogue_then_attention(native, tile):
+    """q/k/v projection whose epilogue rotates q and k, attention on the rotated tensors, and a backward pass whose
+    attention kernels hand back gradients of the unrotated projection: against the fp32 statements end to end."""
+    from b200moe import ops
+    from b200moe.ops import functional as Fn
+    from b200moe.ops.attention import fused_qkv_attention
+    native.set_gemm_tile_mode(tile)
+    try:
+        B, S, Hq, Hkv, hd, D = 2, 256, 8, 2, 128, 512
+        total = Hq + 2 * Hkv
+        cos, sin = Fn.rope_tables(10000.0, hd, 2 * S, device="cuda")       # a table longer than the sequence
+        x = _rand(B * S, D).requires_grad_(True)
+        w = _rand(total * hd, D, scale=0.05).requires_grad_(True)
+        qkv = ops.linear_rope(x, w, cos, sin, (Hq + Hkv) * hd, S)
+        xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+        plain = (xr @ wr.t()).view(B, S, total, hd)
+        rotated = torch.cat([Fn.apply_rope_ref(plain[:, :, :Hq + Hkv].transpose(1, 2), cos[:S], sin[:S]).transpose(1, 2),
+                             plain[:, :, Hq + Hkv:]], dim=2)
+        assert _rel(qkv.view(B, S, total, hd), rotated) < 1e-2
+        out = fused_qkv_attention(qkv, B, S, Hq, Hkv, hd, cos, sin, pre_rotated=True)
+        ref = Fn.attention_ref(plain[:, :, :Hq], plain[:, :, Hq:Hq + Hkv], plain[:, :, Hq + Hkv:], cos[:S], sin[:S],
+                               causal=True)
+        assert _rel(out, ref) < 1.5e-2
+        g = _rand(B, S, Hq, hd)
+        out.backward(g)
+        ref.backward(g.float())
+        assert _rel(x.grad, xr.grad) < 3e-2 and _rel(w.grad, wr.grad) < 3e-2
+        native.check_status()
+    finally:
+        native.set_gemm_tile_mode(0)
 
 
 @pytest.mark.parametrize("M,K,world,segments", [(1000, 512, 2, [1536]), (300, 256, 2, [1984]),
