@@ -125,6 +125,74 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_fwd_kernel(const __nv_bf
 }
 
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) [+ residual]; dw partial per CTA.
+// One CTA per row (grid-stride).  The loads of the CTA's next row are issued before the current row is reduced and
+// stored, so each thread keeps two rows' worth of 16-byte loads in flight across the block-wide reduction.
+template <int CH>
+struct NormRow {
+  bf16x8 dy[CH], x[CH];
+  float r;
+};
+
+template <int CH>
+__device__ __forceinline__ void norm_row_load(NormRow<CH>& row, const __nv_bfloat16* __restrict__ dy,
+                                              const __nv_bfloat16* __restrict__ x, const float* __restrict__ rstd,
+                                              int index, int D) {
+  const size_t base = static_cast<size_t>(index) * D;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int col = (c * NORM_THREADS + threadIdx.x) * 8;
+    if (col < D) {
+      row.dy[c] = *reinterpret_cast<const bf16x8*>(dy + base + col);
+      row.x[c] = *reinterpret_cast<const bf16x8*>(x + base + col);
+    }
+  }
+  row.r = rstd[index];
+}
+
+template <int CH>
+__device__ __forceinline__ void norm_row_finish(const NormRow<CH>& row, float (&dw_acc)[CH][8],
+                                                const float (&wv)[CH][8],
+                                                const __nv_bfloat16* __restrict__ residual,
+                                                __nv_bfloat16* __restrict__ dx, int index, int D, float* scratch) {
+  const size_t base = static_cast<size_t>(index) * D;
+  const float r = row.r;
+  float dot = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int col = (c * NORM_THREADS + threadIdx.x) * 8;
+    if (col < D) {
+      float dyv[8], xv[8];
+      unpack8(row.dy[c], dyv);
+      unpack8(row.x[c], xv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = xv[i] * r;
+        dw_acc[c][i] += dyv[i] * xh;
+        dot += dyv[i] * wv[c][i] * xh;
+      }
+    }
+  }
+  const float mean = block_sum<NORM_THREADS>(dot, scratch) / D;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int col = (c * NORM_THREADS + threadIdx.x) * 8;
+    if (col < D) {
+      float dyv[8], xv[8], o[8];
+      unpack8(row.dy[c], dyv);
+      unpack8(row.x[c], xv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = r * (dyv[i] * wv[c][i] - xv[i] * r * mean);
+      if (residual) {
+        float res[8];
+        unpack8(*reinterpret_cast<const bf16x8*>(residual + base + col), res);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += res[i];
+      }
+      *reinterpret_cast<bf16x8*>(dx + base + col) = pack8(o);
+    }
+  }
+}
+
 template <int CH>
 __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                                                   const __nv_bfloat16* __restrict__ x,
@@ -145,47 +213,18 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_bwd_kernel(const __nv_bf
       wv[c][i] = col < D ? w[col + i] : 0.f;
     }
   }
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const size_t base = static_cast<size_t>(row) * D;
-    const float r = rstd[row];
-    bf16x8 rdy[CH], rx[CH];
-    float dot = 0.f;
-#pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      const int col = (c * NORM_THREADS + threadIdx.x) * 8;
-      if (col < D) {
-        rdy[c] = *reinterpret_cast<const bf16x8*>(dy + base + col);
-        rx[c] = *reinterpret_cast<const bf16x8*>(x + base + col);
-        float dyv[8], xv[8];
-        unpack8(rdy[c], dyv);
-        unpack8(rx[c], xv);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float xh = xv[i] * r;
-          dw_acc[c][i] += dyv[i] * xh;
-          dot += dyv[i] * wv[c][i] * xh;
-        }
-      }
-    }
-    const float mean = block_sum<NORM_THREADS>(dot, scratch) / D;
-#pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      const int col = (c * NORM_THREADS + threadIdx.x) * 8;
-      if (col < D) {
-        float dyv[8], xv[8], o[8];
-        unpack8(rdy[c], dyv);
-        unpack8(rx[c], xv);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = r * (dyv[i] * wv[c][i] - xv[i] * r * mean);
-        if (residual) {
-          float res[8];
-          unpack8(*reinterpret_cast<const bf16x8*>(residual + base + col), res);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] += res[i];
-        }
-        *reinterpret_cast<bf16x8*>(dx + base + col) = pack8(o);
-      }
-    }
+  NormRow<CH> a, b;
+  int row = blockIdx.x;
+  if (row < rows) norm_row_load(a, dy, x, rstd, row, D);
+  while (row < rows) {
+    const int next = row + gridDim.x;
+    if (next < rows) norm_row_load(b, dy, x, rstd, next, D);
+    norm_row_finish(a, dw_acc, wv, residual, dx, row, D, scratch);
+    if (next >= rows) break;
+    const int after = next + gridDim.x;
+    if (after < rows) norm_row_load(a, dy, x, rstd, after, D);
+    norm_row_finish(b, dw_acc, wv, residual, dx, next, D, scratch);
+    row = after;
   }
 #pragma unroll
   for (int c = 0; c < CH; ++c) {
@@ -197,12 +236,32 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_bwd_kernel(const __nv_bf
   }
 }
 
-__global__ void column_sum_kernel(const float* __restrict__ partial, float* __restrict__ out, int parts, int D) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= D) return;
-  float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += partial[static_cast<size_t>(p) * D + col];
-  out[col] = s;
+// out[col] = sum over parts of partial[part][col].  One CTA per 32 columns: lane = column (coalesced 128-byte
+// reads), the eight warps take every eighth part, shared memory adds the eight partial sums.
+__global__ void __launch_bounds__(256) column_sum_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                                        int parts, int D) {
+  __shared__ float acc[8][33];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.x * 32 + lane;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (col < D) {
+    int p = warp;
+    for (; p + 24 < parts; p += 32) {
+      s0 += partial[static_cast<size_t>(p) * D + col];
+      s1 += partial[static_cast<size_t>(p + 8) * D + col];
+      s2 += partial[static_cast<size_t>(p + 16) * D + col];
+      s3 += partial[static_cast<size_t>(p + 24) * D + col];
+    }
+    for (; p < parts; p += 8) s0 += partial[static_cast<size_t>(p) * D + col];
+  }
+  acc[warp][lane] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (warp == 0 && col < D) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += acc[i][lane];
+    out[col] = s;
+  }
 }
 
 // ------------------------------------------------------------------ skinny linear (router: N <= 16 outputs)
@@ -450,7 +509,7 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(__nv_bfloat16
 // mean over T tokens), ``grad_scale`` multiplies the gradient written back (1/T times whatever the caller
 // back-propagates into the loss).
 constexpr int CE_REG_CHUNKS = 8;
-__global__ void __launch_bounds__(CE_THREADS) cross_entropy_reg_kernel(__nv_bfloat16* __restrict__ logits,
+__global__ void __launch_bounds__(CE_THREADS, 2) cross_entropy_reg_kernel(__nv_bfloat16* __restrict__ logits,
                                                                       const long long* __restrict__ targets,
                                                                       float* __restrict__ loss, int T, int V,
                                                                       float loss_scale, float grad_scale) {
@@ -713,7 +772,7 @@ int b2_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* r
   else if (D <= 4096) B2_NORM_BWD(2);
   else B2_NORM_BWD(4);
 #undef B2_NORM_BWD
-  column_sum_kernel<<<(D + 255) / 256, 256, 0, s>>>(dw_partial, dw, parts, D);
+  column_sum_kernel<<<(D + 31) / 32, 256, 0, s>>>(dw_partial, dw, parts, D);
   return ok();
 }
 

@@ -88,7 +88,7 @@ def build_model(config: dict, mesh, device, fsdp_group, ddp_group, compute_dtype
     optimizer = AdamW(wrapped.parameters(), lr=train_cfg["learning_rate"],
                       betas=(opt_cfg["beta1"], opt_cfg["beta2"]), weight_decay=opt_cfg["lambda"])
     wrapped.activation_budget = None
-    if recompute == "auto" and device.type == "cuda":
+    if recompute == "auto" and device.type == "cuda" and "batch_size" in train_cfg and "microbatch_num" in train_cfg:
         from .parallel.memory import stage_activation_budget
         optimizer.materialize_state()
         fsdp, ddp = parallel_sizes(train_cfg)

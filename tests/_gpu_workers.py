@@ -138,8 +138,9 @@ def _moe_ep(rank, world, port, out_dir):
             assert epc.worst_load() >= float(world)                          # every slot of every rank landed here
 
 
-def _train_parity(rank, world, port, out_dir, pp):
-    """A few training steps: fused peer-memory backend against the NCCL backend."""
+def _train_parity(rank, world, port, out_dir, pp, ddp=1, skew=False):
+    """A few training steps: fused peer-memory backend against the NCCL backend.  ``skew``: every token of every
+    rank is routed to the two first experts (both on shard rank 0), the worst case for the expert buffers."""
     import torch
     from b200moe.comm import make_comm
     from b200moe.ops import native
@@ -148,16 +149,25 @@ def _train_parity(rank, world, port, out_dir, pp):
     from b200moe.topology import build_groups
     from b200moe.trainer import build_model
     device = _setup(rank, world, port)
-    fsdp = world // pp
+    fsdp = world // (pp * ddp)
+    if skew:
+        from b200moe import ops
+        plain_top2 = ops.router_top2
+
+        def biased_top2(logits):
+            bias = torch.zeros(logits.shape[-1], device=logits.device, dtype=logits.dtype)
+            bias[:2] = 40.0
+            return plain_top2(logits + bias)
+        ops.router_top2 = biased_top2
     config = {
         "general": {"device": "gpu"}, "data": {"vocab_size": 2048},
         "model": {"num_head": 4, "d_model": 512, "d_ff": 1024, "context_len": 256, "num_layers": 2,
                   "num_expert_per_node": 8 // fsdp},
-        "train": {"fsdp_parallel_num": fsdp, "data_parallel_num": 1, "pipeline_parallel_stages": pp,
+        "train": {"fsdp_parallel_num": fsdp, "data_parallel_num": ddp, "pipeline_parallel_stages": pp,
                   "learning_rate": 1e-3, "optimizer": {"beta1": 0.9, "beta2": 0.999, "lambda": 0.01}},
     }
     mesh = build_groups(config["train"], rank, world, world)
-    comm = make_comm(mesh, device)
+    comm = make_comm(mesh, device, wait_seconds=5.0)
     losses = {}
     weights = {}
     for variant, backend, gather in (("fused", "fused", "step"), ("first_use", "fused", "first_use"),
@@ -237,8 +247,8 @@ def run_moe_ep(rank, world, port, out_dir):
     _guarded(_moe_ep, rank, world, port, out_dir)
 
 
-def run_train_parity(rank, world, port, out_dir, pp):
-    _guarded(_train_parity, rank, world, port, out_dir, pp)
+def run_train_parity(rank, world, port, out_dir, pp, ddp=1, skew=False):
+    _guarded(_train_parity, rank, world, port, out_dir, pp, ddp, skew)
 
 
 def run_allgather_gemm(rank, world, port, out_dir):

@@ -38,6 +38,23 @@ def test_training_steps_fused_vs_nccl_fsdp2(tmp_path, free_port):
     _run(W.run_train_parity, 2, tmp_path, free_port, 1)
 
 
+def test_training_steps_when_every_row_goes_to_one_rank(tmp_path, free_port):
+    """The worst routing there is: every token of both ranks picks the two first experts, which live on rank 0.  The
+    fused exchange must neither overflow nor drop a row, and must agree with the NCCL path."""
+    _need(2)
+    _run(W.run_train_parity, 2, tmp_path, free_port, 1, 1, True)
+
+
 def test_training_steps_fused_vs_nccl_pp2_fsdp2(tmp_path, free_port):
     _need(4)
     _run(W.run_train_parity, 4, tmp_path, free_port, 2)
+
+
+def test_training_steps_fused_vs_nccl_fsdp4_ep4(tmp_path, free_port):
+    _need(4)
+    _run(W.run_train_parity, 4, tmp_path, free_port, 1)
+
+
+def test_training_steps_fused_vs_nccl_fsdp2_with_two_replicas(tmp_path, free_port):
+    _need(4)
+    _run(W.run_train_parity, 4, tmp_path, free_port, 1, 2)
