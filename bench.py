@@ -318,7 +318,10 @@ def bench_b200moe(args):
         native.check_status()      # a device-side wait that ran out is an error
         loss = torch.tensor([float(last) if last is not None else 0.0], device=device)
         dist.all_reduce(loss, op=dist.ReduceOp.MAX)
-        peak = torch.tensor([torch.cuda.max_memory_allocated() / 2 ** 30], device=device)
+        # allocator peak, and what the device itself reports as taken (symmetric buffers and library workspaces
+        # are outside PyTorch's allocator)
+        free, total = torch.cuda.mem_get_info(device)
+        peak = torch.tensor([torch.cuda.max_memory_allocated() / 2 ** 30, (total - free) / 2 ** 30], device=device)
         dist.all_reduce(peak, op=dist.ReduceOp.MAX)
         load = torch.tensor([_worst_expert_load(comm)], device=device)
         dist.all_reduce(load, op=dist.ReduceOp.MAX)
@@ -328,7 +331,7 @@ def bench_b200moe(args):
         dist.all_reduce(kept, op=dist.ReduceOp.SUM)
         if rank == 0:
             report(args, cfg, device_ms, e2e_ms, clocks, launches, float(loss), stager.h2d_bytes if edge else 0, 4,
-                   "b200moe", {"peak_mem_gib": float(peak),
+                   "b200moe", {"peak_mem_gib": float(peak[0]), "device_mem_used_gib": float(peak[1]),
                                "activation_recompute": config["train"]["activation_recompute"],
                                "moe_calls_kept_gate_up": int(kept[0]), "moe_calls_rebuilt_gate_up": int(kept[1]),
                                "ep_max_rows_over_balanced": round(float(load), 3),

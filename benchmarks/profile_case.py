@@ -5,7 +5,10 @@ case needs (operands larger than L2, well under a few GB), runs two warm-up
 launches and three measured ones and prints the CUDA-event time.  Cases:
 gemm_nt, gemm_nn, gemm_tn, gemm_pair (gemm_nt on CTA pairs), ag_gemm (the all-gather + GEMM kernel as rank 0 of
 two emulated ranks: the "peer" is a second buffer on this GPU and its ready signal is written by the host, so no
-launch waits for another), swiglu, moe_down, wgrad, rmsnorm, attention_fwd, attention_bwd, sdpa.
+launch waits for another), swiglu, moe_down, wgrad, rmsnorm, rmsnorm_bwd, cross_entropy, adamw, swiglu_bwd,
+attention_fwd, attention_bwd, sdpa, and the communication kernels with every peer pointer on this GPU: fsdp_step and
+allreduce (rank 0 of two emulated ranks, the peer's flags preset by the host), ep_gateup (gather + gate/up GEMM +
+SwiGLU over a one-rank expert group) and ep_down (down projection with the return in its epilogue).
 """
 import argparse
 import os
@@ -73,6 +76,95 @@ def build(case):
     if case == "rmsnorm":
         x, w = rnd(T, D), torch.ones(D, device="cuda")
         return lambda: native.rmsnorm_fwd(x, w, 1e-5), 0
+    if case == "rmsnorm_bwd":
+        x, dy, w = rnd(2 * T, D), rnd(2 * T, D), torch.ones(D, device="cuda")
+        _, rstd = native.rmsnorm_fwd(x, w, 1e-5)
+        return lambda: native.rmsnorm_bwd(dy, x, w, rstd), 0
+    if case == "cross_entropy":
+        logits = rnd(4096, 32000)
+        targets = torch.randint(0, 32000, (4096,), device="cuda")
+        loss = torch.zeros((), device="cuda")
+        return lambda: native.cross_entropy_scaled_(logits, targets, loss, 1.0 / 4096, 1.0 / 4096), 0
+    if case == "adamw":
+        n = 1 << 27
+        p_, g_, m_, v_ = (torch.zeros(n, device="cuda", dtype=torch.bfloat16) for _ in range(4))
+        return lambda: native.adamw_(p_, g_, m_, v_, 1e-4, 0.9, 0.999, 1e-8, 0.01, 1e-4), 0
+    if case == "swiglu_bwd":
+        dh, gate, up = rnd(R, Fd, scale=0.1), rnd(R, Fd), rnd(R, Fd)
+        return lambda: native.swiglu_bwd(dh, gate, up), 0
+    if case in ("fsdp_step", "allreduce"):
+        import ctypes
+        table = ctypes.c_ulonglong * 8
+        pads = [torch.zeros(32 * 8, dtype=torch.int32, device="cuda") for _ in range(2)]
+        pads[0].fill_(1 << 20)                      # the emulated peer has "arrived" at every barrier to come
+        sig = table(*([s_.data_ptr() for s_ in pads] + [0] * 6))
+        counter = torch.zeros(8, dtype=torch.int32, device="cuda")
+        status = native.status_word()
+        state = {"seq": 0}
+        if case == "allreduce":
+            n = 1 << 26
+            bufs = [torch.randn(n, device="cuda") for _ in range(2)]
+            ptrs = table(*([b.data_ptr() for b in bufs] + [0] * 6))
+
+            def launch():
+                state["seq"] += 1
+                native._call("b2_comm_allreduce", ptrs, sig, ctypes.c_void_p(0), ctypes.c_void_p(0), ctypes.c_int(1),
+                             ctypes.c_int(0), ctypes.c_int(2), ctypes.c_int(state["seq"]), ctypes.c_int(12),
+                             ctypes.c_longlong(n), ctypes.c_float(0.5), ctypes.c_void_p(counter.data_ptr()),
+                             ctypes.c_void_p(status.data_ptr()),
+                             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+            return launch, 0
+        full = 1 << 27                              # parameters of the emulated stage; this rank owns half
+        grads = [torch.randn(full, device="cuda") for _ in range(2)]
+        weights = [torch.zeros(full, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+        master, m_, v_, sg = (torch.zeros(full // 2, device="cuda") for _ in range(4))
+        entries = torch.tensor([[0, 0, full // 2, 0]], dtype=torch.int64, device="cuda")
+        gp = table(*([g_.data_ptr() for g_ in grads] + [0] * 6))
+        wp = table(*([w_.data_ptr() for w_ in weights] + [0] * 6))
+
+        def launch():
+            state["seq"] += 1
+            c = ctypes
+            native._call("b2_fsdp_step", gp, wp, sig, c.c_void_p(entries.data_ptr()), c.c_int(1), c.c_int(0),
+                         c.c_int(2), c.c_int(state["seq"]), c.c_int(8), c.c_void_p(master.data_ptr()),
+                         c.c_void_p(m_.data_ptr()), c.c_void_p(v_.data_ptr()), c.c_void_p(sg.data_ptr()),
+                         c.c_float(1e-4), c.c_float(0.9), c.c_float(0.999), c.c_float(1e-8), c.c_float(0.01),
+                         c.c_float(1e-4), c.c_int(1), c.c_int(0), c.c_void_p(counter.data_ptr()),
+                         c.c_void_p(status.data_ptr()), c.c_void_p(torch.cuda.current_stream().cuda_stream))
+        return launch, 0
+    if case in ("ep_gateup", "ep_down"):
+        from b200moe import ops
+        from b200moe.comm import ep as EP
+        tokens, experts = 4096, 2
+        epc = EP.EPPull(None, native.status_word(), torch.device("cuda", torch.cuda.current_device()), tokens, D, Fd,
+                        experts)
+        x = rnd(tokens, D)
+        w1, w3, w2 = rnd(experts, Fd, D, scale=0.02), rnd(experts, Fd, D, scale=0.02), rnd(experts, D, Fd, scale=0.02)
+        weights, idx = ops.router_top2(torch.randn(tokens, experts, device="cuda"))
+        weights = weights.float().contiguous()
+        slot = epc.acquire()
+        epc.slot_tensor(slot).copy_(x)
+        i32 = dict(dtype=torch.int32, device="cuda")
+        row_src, row_tag = torch.empty(epc.cap, **i32), torch.empty(epc.cap, **i32)
+        row_w = torch.empty(epc.cap, dtype=torch.float32, device="cuda")
+        x_ws, h = epc.ws("x", D), epc.ws("h", Fd)
+        state = {}
+
+        def gateup():
+            offs, seg_end, tile_expert, meta, seq = epc.plan(idx, weights, "profile")
+            state.update(tile_expert=tile_expert, meta=meta)
+            epc.gather_gemm(0, x_ws, w1, w3, 2 * Fd, D, tile_expert, meta, seg_end, 0, epc.pool[slot].table(), 1,
+                            epc.land_src.tensor, epc.land_tag.tensor, epc.land_w.tensor, (row_src, row_tag, row_w),
+                            EP.SIG_META, seq, 1, h, None, None, None, None, 0)
+        if case == "ep_gateup":
+            return gateup, 2 * 2 * tokens * 2 * Fd * D
+        gateup()
+
+        def down():
+            seq = epc.g.next_seq(EP.SIG_RET_F)
+            native.gemm_nt_push(h, w2, state["tile_expert"], state["meta"][0:1], experts, epc.ret_f.table(), row_tag,
+                                row_src, row_w, epc.g.sig.table(), EP.SIG_RET_F, seq, 0, 1, epc.tickets[4:])
+        return down, 2 * 2 * tokens * D * Fd
     B, S, Hq, Hkv, hd = 2, 8192, 32, 8, 128
     q, k, v = rnd(B, S, Hq, hd), rnd(B, S, Hkv, hd), rnd(B, S, Hkv, hd)
     flops = 4 * B * Hq * S * S * hd // 2
