@@ -7,10 +7,10 @@ the same allocation mapped into every rank of a group, optionally bound to an
 NVSwitch multicast address) and drives the kernels of ``csrc/comm.cu`` that read
 and write those buffers through peer pointers:
 
-* ``EPContext``: expert-parallel dispatch / return of token rows, forward and
-  backward, with a device-side count exchange (replaces the reference's
-  ``TensorExchange`` all-to-alls and their ``.cpu()`` split sync,
-  implementation/layers.py:14-52,139-213);
+* ``Comm.ep_context`` → ``comm.ep.EPPull``: the expert-parallel exchange fused
+  with the expert GEMMs (replaces the reference's ``TensorExchange``
+  all-to-alls and their ``.cpu()`` split sync, implementation/layers.py:14-52,
+  139-213);
 * ``Comm.fused_update``: FSDP reduce-scatter + AdamW + weight all-gather in one
   kernel (replaces per-parameter ``reduce_scatter_tensor`` + eager AdamW + the
   per-microbatch all-gathers, implementation/distributed/ddp_modules.py:24-100,
@@ -24,8 +24,6 @@ that all ranks of the group advance in the same order.
 from __future__ import annotations
 
 import ctypes
-from dataclasses import dataclass
-
 import torch
 import torch.distributed as dist
 
@@ -34,8 +32,7 @@ from ..ops import native
 MAX_RANKS = 8
 _U64x8 = ctypes.c_ulonglong * MAX_RANKS
 
-# signal slots
-SIG_EP_COUNTS, SIG_EP_FWD_DATA, SIG_EP_FWD_RET, SIG_EP_BWD_DATA, SIG_EP_BWD_RET = 0, 1, 2, 3, 4
+# signal slots (the expert exchange of comm/ep.py uses 16..20)
 SIG_FSDP = 8      # +1
 SIG_AR = 12       # +1
 SIG_AG_GEMM = 14
@@ -125,12 +122,8 @@ class Comm:
         self.status = native.status_word(device)
         self.fsdp = GroupComm(mesh.group("fsdp"), device) if mesh.fsdp > 1 else None
         self.ddp = GroupComm(mesh.group("ddp"), device) if mesh.ddp > 1 else None
-        # expert exchange: "pull" = fused with the expert GEMMs (comm/ep.py); "push" = the separate push/consume kernels
-        self.ep_mode = os.environ.get("B200MOE_EP_MODE", "pull")
         skew = os.environ.get("B200MOE_EP_MAX_SKEW")
         self.ep_max_skew = float(skew) if skew else None
-        self.capacity_mode = os.environ.get("B200MOE_EP_CAPACITY", "exact")
-        self.capacity_bucket = int(os.environ.get("B200MOE_EP_BUCKET", "4096"))
         self._symm = {}
         self._ep = {}
         self._ar_stage = {}
@@ -311,214 +304,18 @@ class Comm:
         return tensor
 
     # -- expert parallel --------------------------------------------------------------------
-    def ep_context(self, tokens: int, dim: int, experts_total: int, capacity_factor: float = 1.25,
-                   capacity_mode: str | None = None, ffn: int | None = None):
-        key = (tokens, dim, experts_total)
+    def ep_context(self, tokens: int, dim: int, experts_total: int, ffn: int):
+        """The expert-exchange state (``comm.ep.EPPull``) for one problem size, created at first use."""
+        key = (tokens, dim, experts_total, ffn)
         ctx = self._ep.get(key)
         if ctx is None:
-            if self.ep_mode == "pull" and ffn is not None:
-                from .ep import EPPull
-                # a wide group's worst case (every slot of every rank on one rank) is far from anything a trained
-                # router does: beyond four ranks the accepted skew is bounded unless configured otherwise
-                skew = self.ep_max_skew if self.ep_max_skew else (None if self.fsdp.world <= 4 else 4.0)
-                ctx = EPPull(self.fsdp, self.status, self.device, tokens, dim, ffn, experts_total, max_skew=skew)
-            else:
-                ctx = EPContext(self, tokens, dim, experts_total, capacity_factor, capacity_mode or self.capacity_mode)
+            from .ep import EPPull
+            # a wide group's worst case (every slot of every rank on one rank) is far from anything a trained
+            # router does: beyond four ranks the accepted skew is bounded unless configured otherwise
+            skew = self.ep_max_skew if self.ep_max_skew else (None if self.fsdp.world <= 4 else 4.0)
+            ctx = EPPull(self.fsdp, self.status, self.device, tokens, dim, ffn, experts_total, max_skew=skew)
             self._ep[key] = ctx
         return ctx
-
-
-@dataclass
-class Route:
-    cap: int
-    offs: torch.Tensor
-    tile_expert: torch.Tensor
-    meta: torch.Tensor
-    x_perm: torch.Tensor
-    slot_row: torch.Tensor
-    slot_dest: torch.Tensor
-    row_tag: torch.Tensor
-    row_src: torch.Tensor
-    seg_live_end: torch.Tensor
-
-
-class _Landing:
-    """Symmetric landing area for pushed rows plus their per-row tags."""
-
-    def __init__(self, rows, dim, device, group, with_scalar):
-        self.rows = SymmBuffer(rows * dim, torch.bfloat16, device, group, zero=False)
-        self.tag = SymmBuffer(rows, torch.int32, device, group)
-        self.src = SymmBuffer(rows, torch.int32, device, group)
-        self.scalar = SymmBuffer(rows, torch.float32, device, group) if with_scalar else None
-        if native._DEBUG:
-            # checked build: rows nobody wrote are NaN and their tags out of range, so a read of a row that was
-            # never pushed shows up in the loss or in the kernels' range checks instead of passing silently
-            self.rows.tensor.fill_(float("nan"))
-            self.tag.tensor.fill_(-(1 << 30))
-            self.src.tensor.fill_(-(1 << 30))
-            torch.cuda.synchronize(device)
-            dist.barrier(group=group)
-
-
-class EPContext:
-    """Dispatch and return of token rows between the ranks of the expert group."""
-
-    def __init__(self, comm: Comm, tokens: int, dim: int, experts_total: int, capacity_factor: float,
-                 capacity_mode: str = "exact"):
-        g = comm.fsdp
-        self.comm, self.g = comm, g
-        self.tokens, self.dim, self.experts_total = tokens, dim, experts_total
-        self.ep = g.world
-        self.e_local = experts_total // self.ep
-        self.slots = tokens * 2
-        # Landing buffers hold the worst case (every slot of every rank routed here), so a push can
-        # never overflow.  The owned per-call buffers (saved for the backward pass) are sized by
-        # ``capacity_mode``:
-        #   exact  one 16-byte read of the row count per dispatch (the host waits for the plan kernel;
-        #          with millisecond-scale expert GEMMs behind it the queue refills at once); never
-        #          drops, never overflows, least memory.  Default.
-        #   hint   no host wait: rows the same layer needed on its previous call (read back
-        #          asynchronously) times ``capacity_factor``; an abrupt routing change overflows and
-        #          is reported through the status word.
-        #   worst  no host wait, worst-case buffers (``ep`` times the average).
-        if capacity_mode not in ("exact", "hint", "worst"):
-            raise ValueError("capacity_mode must be exact, hint or worst")
-        self.capacity_mode = capacity_mode
-        self.capacity_factor = capacity_factor
-        self.cap = (self.slots * self.ep + self.e_local * 255 + 255) // 256 * 256
-        self._hints = {}
-        dev = comm.device
-        self.counts_all = SymmBuffer(MAX_RANKS * 32, torch.int32, dev, g.group)
-        self.fwd_land = _Landing(self.cap, dim, dev, g.group, with_scalar=False)
-        self.bwd_land = _Landing(self.cap, dim, dev, g.group, with_scalar=True)
-        self.fwd_ret = SymmBuffer(self.slots * dim, torch.bfloat16, dev, g.group, zero=False)
-        self.bwd_ret = SymmBuffer(self.slots * dim, torch.bfloat16, dev, g.group, zero=False)
-        self.ret_scalar = SymmBuffer(self.slots, torch.float32, dev, g.group)
-        self.slot_ids = torch.arange(self.slots, dtype=torch.int32, device=dev)
-        self.null = _null_table()
-        torch.cuda.synchronize(dev)
-        dist.barrier(group=g.group)
-
-    # forward: tokens -> expert owners
-    def _sized(self, needed: int, factor: float | None = None) -> int:
-        factor = self.capacity_factor if factor is None else factor
-        want = int(needed * factor) + (self.e_local * 256 if factor > 1.0 else 0)
-        bucket = self.comm.capacity_bucket
-        return min(self.cap, (want + bucket - 1) // bucket * bucket)
-
-    def _capacity_for(self, key):
-        """Capacity from the layer's previous call, or ``None`` when no readback has
-        arrived yet (the caller then reads the count once, synchronously)."""
-        if self.capacity_mode == "worst":
-            return self.cap
-        hint = self._hints.get(key)
-        if self.capacity_mode == "exact" or hint is None or not hint[1].query():
-            return None
-        return self._sized(int(hint[0][3]))
-
-    def _record_hint(self, key, meta):
-        hint = self._hints.get(key)
-        if hint is None:
-            hint = (torch.zeros(4, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
-            self._hints[key] = hint
-        hint[0].copy_(meta, non_blocking=True)
-        hint[1].record()
-
-    def buffers(self):
-        out = [self.counts_all, self.fwd_ret, self.bwd_ret, self.ret_scalar]
-        for land in (self.fwd_land, self.bwd_land):
-            out += [b for b in (land.rows, land.tag, land.src, land.scalar) if b is not None]
-        return out
-
-    def worst_load(self) -> float:
-        """Rows this rank received in the last call of its busiest layer, relative to a balanced split (from the
-        asynchronous read-backs of the plan kernels; 0 before the first one)."""
-        worst = 0
-        for hint in self._hints.values():
-            if hint[1].query():
-                worst = max(worst, int(hint[0][3]))
-        return worst / self.slots
-
-    def dispatch(self, x, idx, key=None) -> Route:
-        g, dev = self.g, x.device
-        i32 = dict(dtype=torch.int32, device=dev)
-        cap = self._capacity_for(key)
-        cold = cap is None
-        if cold:
-            cap = self.cap
-        slot_row, slot_dest = torch.empty(self.slots, **i32), torch.empty(self.slots, **i32)
-        offs, seg_live_end = torch.empty(self.e_local, **i32), torch.empty(self.e_local, **i32)
-        tile_expert = torch.empty(cap // 128, **i32)
-        meta = torch.zeros(4, **i32)
-        seq = g.next_seq(SIG_EP_COUNTS)
-        native._call("b2_ep_plan", _ptr(idx.contiguous()), _i(self.slots), _i(self.experts_total), _i(self.ep),
-                     _i(g.rank), _i(seq), _i(cap), self.counts_all.table(), g.sig.table(), _i(SIG_EP_COUNTS),
-                     _ptr(slot_row), _ptr(slot_dest), _ptr(offs), _ptr(seg_live_end), _ptr(tile_expert), _ptr(meta),
-                     _ptr(self.comm.status), _stream())
-        self._record_hint(key, meta)
-        if cold:
-            # first call of this layer: one blocking read of the row count sizes the owned buffers
-            cap = self._sized(int(meta.cpu()[3]), 1.0 if self.capacity_mode == "exact" else None)
-        seq = g.next_seq(SIG_EP_FWD_DATA)
-        self._push(x, slot_row, slot_dest, self.slot_ids, None, None, self.slots, 1, self.cap, seq, SIG_EP_FWD_DATA,
-                   self.fwd_land)
-        x_perm = torch.empty(cap, self.dim, dtype=torch.bfloat16, device=dev)
-        row_tag, row_src = torch.empty(cap, **i32), torch.empty(cap, **i32)
-        land = self.fwd_land
-        native._call("b2_ep_consume", _ptr(land.rows.tensor), _ptr(land.tag.tensor), _ptr(land.src.tensor), _ptr(None),
-                     _ptr(tile_expert), _ptr(seg_live_end), _ptr(meta), _ptr(None), self.null, _ptr(x_perm),
-                     _ptr(row_tag), _ptr(row_src), g.my_sig(), _i(self.dim), _i(cap), _i(self.ep), _i(seq),
-                     _i(SIG_EP_FWD_DATA), _ptr(self.comm.status), _stream())
-        return Route(cap, offs, tile_expert, meta, x_perm, slot_row, slot_dest, row_tag, row_src, seg_live_end)
-
-    def _push(self, src, row_of, dest_of, tag_of, scalar_of, live_items, items, shift, dest_cap, seq, slot, land):
-        g = self.g
-        if isinstance(land, _Landing):
-            rows, tag, source = land.rows.table(), land.tag.table(), land.src.table()
-            scalar = land.scalar.table() if land.scalar is not None else self.null
-        else:
-            rows, tag, source, scalar = land.table(), self.null, self.null, self.null
-        native._call("b2_ep_push", _ptr(src), _ptr(row_of), _ptr(dest_of), _ptr(tag_of), _ptr(scalar_of),
-                     _ptr(live_items), _i(items), _i(self.dim), _i(shift), _i(dest_cap), _i(g.rank), _i(self.ep),
-                     _i(seq), _i(slot), rows, tag, source, scalar, g.sig.table(), _ptr(g.counter[2:]), _stream())
-
-    def _wait(self, slot, seq):
-        native._call("b2_ep_wait", self.g.my_sig(), _i(slot), _i(self.ep), _i(seq), _ptr(self.comm.status), _stream())
-
-    # forward: expert outputs -> token owners, weighted sum
-    def combine(self, route: Route, y_perm, weights, tokens):
-        seq = self.g.next_seq(SIG_EP_FWD_RET)
-        self._push(y_perm, route.row_tag, route.row_src, None, None, route.meta[1:2], route.cap, 0, self.slots, seq,
-                   SIG_EP_FWD_RET, self.fwd_ret)
-        self._wait(SIG_EP_FWD_RET, seq)
-        ret = self.fwd_ret.tensor.view(self.slots, self.dim)
-        return native.moe_combine(ret, self.slot_ids, weights, tokens)
-
-    # backward of combine: d(out) rows -> expert owners, scaled by the routing weight there
-    def combine_backward(self, route: Route, dout, y_perm, weights):
-        g = self.g
-        seq = g.next_seq(SIG_EP_BWD_DATA)
-        self._push(dout, route.slot_row, route.slot_dest, self.slot_ids, weights.reshape(-1), None, self.slots, 1,
-                   self.cap, seq, SIG_EP_BWD_DATA, self.bwd_land)
-        dy_perm = torch.empty(route.cap, self.dim, dtype=torch.bfloat16, device=dout.device)
-        land = self.bwd_land
-        native._call("b2_ep_consume", _ptr(land.rows.tensor), _ptr(land.tag.tensor), _ptr(land.src.tensor),
-                     _ptr(land.scalar.tensor), _ptr(route.tile_expert), _ptr(route.seg_live_end), _ptr(route.meta),
-                     _ptr(y_perm), self.ret_scalar.table(), _ptr(dy_perm), _ptr(None), _ptr(None), g.my_sig(),
-                     _i(self.dim), _i(route.cap), _i(self.ep), _i(seq), _i(SIG_EP_BWD_DATA), _ptr(self.comm.status),
-                     _stream())
-        return dy_perm
-
-    # backward of dispatch: d(x_perm) rows -> token owners, summed over the two slots
-    def dispatch_backward(self, route: Route, dx_perm, tokens):
-        seq = self.g.next_seq(SIG_EP_BWD_RET)
-        self._push(dx_perm, route.row_tag, route.row_src, None, None, route.meta[1:2], route.cap, 0, self.slots, seq,
-                   SIG_EP_BWD_RET, self.bwd_ret)
-        self._wait(SIG_EP_BWD_RET, seq)
-        ret = self.bwd_ret.tensor.view(self.slots, self.dim)
-        dx = native.moe_combine(ret, self.slot_ids, None, tokens)
-        dweights = self.ret_scalar.tensor.view(tokens, 2).clone()
-        return dx, dweights
 
 
 def make_comm(mesh, device, multicast: bool = False, wait_seconds: float | None = None) -> Comm:

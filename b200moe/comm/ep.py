@@ -192,9 +192,10 @@ class EPPull:
         """Rows the layer ``key`` needed at its previous call if that read-back has arrived, else a balanced share
         with a quarter of head room.  A guide for what to keep, never a limit."""
         hint = self._hints.get(key)
+        # multiples of 2048 rows: a handful of distinct tensor sizes, which the caching allocator can reuse
         if hint is not None and hint[1].query() and int(hint[0][3]) > 0:
-            return min(self.cap, _align(int(int(hint[0][3]) * 1.1)))
-        return min(self.cap, _align(int(self.slots * 1.25)))
+            return min(self.cap, (int(int(hint[0][3]) * 1.1) + 2047) // 2048 * 2048)
+        return min(self.cap, (int(self.slots * 1.25) + 2047) // 2048 * 2048)
 
     def worst_load(self) -> float:
         worst = 0

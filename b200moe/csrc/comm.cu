@@ -2,11 +2,6 @@
 // "peers" is a table of device pointers to the same symmetric allocation on each
 // rank of a group; kernels load and store through those pointers directly.
 //
-//   * expert-parallel dispatch/return: a one-CTA plan kernel that exchanges the
-//     per-expert counts through peer stores (no size all-to-all, no host sync),
-//     a push kernel that writes token rows straight into the destination rank's
-//     landing buffer, and consume kernels that wait for the senders' flags and
-//     finish the local part (zero padding, scaling, routing-weight gradients);
 //   * FSDP end of step: reduce-scatter of the fp32 gradients by peer loads,
 //     fused with the AdamW update of the owned shard and the all-gather of the
 //     new bf16 weights by peer stores — one kernel;
@@ -42,262 +37,6 @@ __device__ __forceinline__ bool block_wait_all(const int* my_sig, int slot, int 
 struct alignas(16) vec16 {
   uint32_t v[4];
 };
-
-// ------------------------------------------------------------------ EP plan with count exchange
-constexpr int PLAN_THREADS = 1024;
-constexpr int ALIGN_ROWS = 256;   // segment padding; tile tables are per 128-row unit
-constexpr int TILE_ROWS = 128;
-constexpr int MAX_EXPERTS = 32;
-
-struct EpPlanArgs {
-  const long long* idx;   // [slots] global expert of each slot
-  int slots, experts_total, ep, rank, seq, capacity_rows;
-  Peers counts_all;       // int32 [MAX_RANKS][MAX_EXPERTS] on each rank: [src][expert]
-  Peers sig;
-  int sig_slot;
-  int* slot_row;          // [slots] landing row at the destination rank
-  int* slot_dest;         // [slots] destination rank
-  int* offs;              // [E_local] padded cumulative segment ends (this rank as expert owner)
-  int* seg_live_end;      // [E_local] first padding row of each segment
-  int* tile_expert;       // [capacity_rows / 128]
-  int* meta;              // {live tiles, live rows, overflow, rows needed}
-  int* status;
-};
-
-__global__ void __launch_bounds__(PLAN_THREADS) ep_plan_kernel(const EpPlanArgs a) {
-  extern __shared__ uint8_t plan_smem[];
-  uint32_t* local = reinterpret_cast<uint32_t*>(plan_smem);   // [E][PLAN_THREADS]
-  __shared__ int warp_tot[32];
-  __shared__ int my_count[MAX_EXPERTS];
-  __shared__ int all_counts[MAX_RANKS][MAX_EXPERTS];
-  __shared__ int base_row[MAX_EXPERTS];                        // landing row of my first slot of expert e
-  const int E = a.experts_total, e_local = E / a.ep;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int per = (a.slots + PLAN_THREADS - 1) / PLAN_THREADS;
-  const int s0 = min(a.slots, tid * per), s1 = min(a.slots, s0 + per);
-  for (int e = 0; e < E; ++e) local[e * PLAN_THREADS + tid] = 0;
-  for (int s = s0; s < s1; ++s) local[min(max(static_cast<int>(a.idx[s]), 0), E - 1) * PLAN_THREADS + tid] += 1;
-  __syncthreads();
-  for (int e = 0; e < E; ++e) {
-    const int mine = local[e * PLAN_THREADS + tid];
-    int inc = mine;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int up = __shfl_up_sync(0xffffffffu, inc, o);
-      if (lane >= o) inc += up;
-    }
-    if (lane == 31) warp_tot[warp] = inc;
-    __syncthreads();
-    if (warp == 0) {
-      const int t = warp_tot[lane];
-      int winc = t;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int up = __shfl_up_sync(0xffffffffu, winc, o);
-        if (lane >= o) winc += up;
-      }
-      warp_tot[lane] = winc - t;
-      if (lane == 31) my_count[e] = winc;
-    }
-    __syncthreads();
-    local[e * PLAN_THREADS + tid] = static_cast<uint32_t>(inc - mine + warp_tot[warp]);
-    __syncthreads();
-  }
-  // publish my counts in every rank's table, then the flag
-  if (tid < E) {
-    for (int p = 0; p < a.ep; ++p)
-      static_cast<int*>(a.counts_all.ptr[p])[a.rank * MAX_EXPERTS + tid] = my_count[tid];
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (tid == 0) signal_all(a.sig, a.sig_slot, a.rank, a.ep, a.seq);
-  const int* my_sig = static_cast<const int*>(a.sig.ptr[a.rank]);
-  if (!block_wait_all(my_sig, a.sig_slot, a.ep, a.seq, a.status, 101)) {
-    // a peer's counts never came: plan nothing (no tiles, no rows, every slot unsent) instead of using stale counts
-    if (tid == 0) {
-      a.meta[0] = 0; a.meta[1] = 0; a.meta[2] = 1; a.meta[3] = 0;
-    }
-    if (tid < e_local) {
-      a.offs[tid] = 0;
-      a.seg_live_end[tid] = 0;
-    }
-    for (int s = s0; s < s1; ++s) {
-      a.slot_row[s] = -1;
-      a.slot_dest[s] = -1;
-    }
-    return;
-  }
-  if (tid < a.ep * E) {
-    const int src = tid / E, e = tid - src * E;
-    all_counts[src][e] = ld_acquire_sys(static_cast<const int*>(a.counts_all.ptr[a.rank]) + src * MAX_EXPERTS + e);
-  }
-  __syncthreads();
-  if (tid == 0) {
-    for (int d = 0; d < a.ep; ++d) {
-      int row = 0, tile = 0;
-      for (int j = 0; j < e_local; ++j) {
-        const int e = d * e_local + j;
-        int total = 0, before_me = 0;
-        for (int src = 0; src < a.ep; ++src) {
-          if (src < a.rank) before_me += all_counts[src][e];
-          total += all_counts[src][e];
-        }
-        base_row[e] = row + before_me;
-        const int padded = (total + ALIGN_ROWS - 1) / ALIGN_ROWS * ALIGN_ROWS;
-        if (d == a.rank) {
-          a.seg_live_end[j] = row + total;
-          if (row + padded <= a.capacity_rows)
-            for (int t = 0; t < padded / TILE_ROWS; ++t) a.tile_expert[tile++] = j;
-          a.offs[j] = row + padded;
-        }
-        row += padded;
-      }
-      if (d == a.rank) {
-        const bool overflow = row > a.capacity_rows;
-        a.meta[0] = overflow ? 0 : tile;
-        a.meta[1] = overflow ? 0 : row;
-        a.meta[2] = overflow ? 1 : 0;
-        a.meta[3] = row;                       // rows this call needed (capacity hint for the host)
-        if (overflow) atomicExch(a.status, 102);
-      }
-    }
-  }
-  __syncthreads();
-  for (int s = s0; s < s1; ++s) {
-    const int e = min(max(static_cast<int>(a.idx[s]), 0), E - 1);
-    const int pos = local[e * PLAN_THREADS + tid];
-    local[e * PLAN_THREADS + tid] = static_cast<uint32_t>(pos + 1);
-    a.slot_row[s] = base_row[e] + pos;
-    a.slot_dest[s] = e / e_local;
-  }
-}
-
-// ------------------------------------------------------------------ push rows to their destination
-struct EpPushArgs {
-  const __nv_bfloat16* src;   // [rows_src, D]
-  const int* row_of;          // [items] landing row at the destination
-  const int* dest_of;         // [items] destination rank
-  const int* tag_of;          // [items] int tag stored beside the row (source slot), or null
-  const float* scalar_of;     // [items] float stored beside the row (routing weight), or null
-  const int* live_items;      // device scalar: number of items (null = items)
-  int items, D, src_shift;    // source row of item i = i >> src_shift (1: slots -> tokens, 0: rows)
-  int dest_capacity, rank, n, seq, sig_slot;
-  Peers land, land_tag, land_src, land_scalar, sig;
-  unsigned int* counter;      // self-resetting block counter
-};
-
-__global__ void __launch_bounds__(256) ep_push_kernel(const EpPushArgs a) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int items = a.live_items ? min(a.items, *a.live_items) : a.items;
-  for (int i = blockIdx.x * 8 + warp; i < items; i += gridDim.x * 8) {
-    const int dest = a.dest_of[i];
-    const int row = a.row_of[i];
-    if (dest < 0 || row < 0 || row >= a.dest_capacity) continue;   // padding rows / overflow are not sent
-    if (!dbg_in_range(dest, 0, a.n, 401)) continue;
-    const __nv_bfloat16* src = a.src + static_cast<size_t>(i >> a.src_shift) * a.D;
-    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.land.ptr[dest]) + static_cast<size_t>(row) * a.D;
-    // four 16-byte loads in flight per lane before the (possibly remote) stores
-    int c = lane * 8;
-    for (; c + 768 < a.D; c += 1024) {
-      const vec16 v0 = *reinterpret_cast<const vec16*>(src + c);
-      const vec16 v1 = *reinterpret_cast<const vec16*>(src + c + 256);
-      const vec16 v2 = *reinterpret_cast<const vec16*>(src + c + 512);
-      const vec16 v3 = *reinterpret_cast<const vec16*>(src + c + 768);
-      *reinterpret_cast<vec16*>(dst + c) = v0;
-      *reinterpret_cast<vec16*>(dst + c + 256) = v1;
-      *reinterpret_cast<vec16*>(dst + c + 512) = v2;
-      *reinterpret_cast<vec16*>(dst + c + 768) = v3;
-    }
-    for (; c < a.D; c += 256) *reinterpret_cast<vec16*>(dst + c) = *reinterpret_cast<const vec16*>(src + c);
-    if (lane == 0) {
-      if (a.tag_of) static_cast<int*>(a.land_tag.ptr[dest])[row] = a.tag_of[i];
-      if (a.land_src.ptr[0]) static_cast<int*>(a.land_src.ptr[dest])[row] = a.rank;
-      if (a.scalar_of) static_cast<float*>(a.land_scalar.ptr[dest])[row] = a.scalar_of[i];
-    }
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int old = atomicInc(a.counter, gridDim.x - 1);
-    if (old == gridDim.x - 1) {
-      __threadfence_system();
-      signal_all(a.sig, a.sig_slot, a.rank, a.n, a.seq);
-    }
-  }
-}
-
-// ------------------------------------------------------------------ expert side: take landed rows
-struct EpConsumeArgs {
-  const __nv_bfloat16* land;   // [capacity, D] local landing buffer
-  const int* land_tag;
-  const int* land_src;
-  const float* land_scalar;    // null in forward
-  const int* tile_expert;
-  const int* seg_live_end;
-  const int* meta;
-  const __nv_bfloat16* y_perm; // backward: saved expert outputs for the routing-weight gradient
-  Peers ret_scalar;            // backward: float [slots] at each source rank
-  __nv_bfloat16* out;          // [capacity, D] owned buffer
-  int* row_tag;                // forward: saved source slot per row (-1 padding)
-  int* row_src;                // forward: saved source rank per row (-1 padding)
-  const int* my_sig;
-  int D, capacity, n, seq, sig_slot;
-  int* status;
-};
-
-__global__ void __launch_bounds__(256) ep_consume_kernel(const EpConsumeArgs a) {
-  if (!block_wait_all(a.my_sig, a.sig_slot, a.n, a.seq, a.status, 103)) return;   // rows of a peer are missing
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int live_rows = min(a.meta[1], a.capacity);
-  for (int r = blockIdx.x * 8 + warp; r < live_rows; r += gridDim.x * 8) {
-    const int expert = a.tile_expert[r / TILE_ROWS];
-    if (!dbg_in_range(expert, 0, MAX_EXPERTS, 403)) continue;
-    const bool live = r < a.seg_live_end[expert];
-    __nv_bfloat16* dst = a.out + static_cast<size_t>(r) * a.D;
-    if (!live) {
-      for (int c = lane * 8; c < a.D; c += 256) *reinterpret_cast<vec16*>(dst + c) = vec16{{0, 0, 0, 0}};
-      if (lane == 0 && a.row_tag) {
-        a.row_tag[r] = -1;
-        a.row_src[r] = -1;
-      }
-      continue;
-    }
-    const __nv_bfloat16* src = a.land + static_cast<size_t>(r) * a.D;
-    if (!a.land_scalar) {
-      for (int c = lane * 8; c < a.D; c += 256) *reinterpret_cast<vec16*>(dst + c) = *reinterpret_cast<const vec16*>(src + c);
-      if (lane == 0) {
-        a.row_tag[r] = a.land_tag[r];
-        a.row_src[r] = a.land_src[r];
-      }
-      continue;
-    }
-    if (!dbg_in_range(a.land_src[r], 0, a.n, 402) || !dbg_in_range(a.land_tag[r], 0, 1 << 30, 404)) continue;
-    const float w = a.land_scalar[r];
-    float dot = 0.f;
-    for (int c = lane * 8; c < a.D; c += 256) {
-      const vec16 in = *reinterpret_cast<const vec16*>(src + c);
-      const vec16 yv = *reinterpret_cast<const vec16*>(a.y_perm + static_cast<size_t>(r) * a.D + c);
-      vec16 o;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in.v[i]));
-        const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yv.v[i]));
-        dot += f.x * g.x + f.y * g.y;
-        const __nv_bfloat162 s = __floats2bfloat162_rn(f.x * w, f.y * w);
-        o.v[i] = *reinterpret_cast<const uint32_t*>(&s);
-      }
-      *reinterpret_cast<vec16*>(dst + c) = o;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    if (lane == 0) static_cast<float*>(a.ret_scalar.ptr[a.land_src[r]])[a.land_tag[r]] = dot;
-  }
-}
-
-// One block: wait for every peer's flag in ``sig_slot`` (placed before a kernel that reads landed data).
-__global__ void ep_wait_kernel(const int* my_sig, int sig_slot, int n, int seq, int* status) {
-  block_wait_all(my_sig, sig_slot, n, seq, status, 104);   // on failure the status word tells the host
-}
 
 // ------------------------------------------------------------------ replica all-reduce
 struct ArArgs {
@@ -459,15 +198,41 @@ __global__ void __launch_bounds__(512) fsdp_step_kernel(const FsdpArgs a) {
     if (((full_base | ent.shard_off | ent.shard_numel) & 7) == 0) {
       for (long long i = tid * 8; i < ent.shard_numel; i += nthreads * 8) {
         const long long si = ent.shard_off + i;
-        float g[8];
+        // every load of this iteration is issued before the first use: the peers' gradient vectors (NVLink), the
+        // local master weights and the two moments are all in flight together
+        float4 glo[MAX_RANKS], ghi[MAX_RANKS];
+        float pv[8], mv[8], vv[8], g[8];
+        if (a.do_reduce) {
+#pragma unroll
+          for (int p = 0; p < MAX_RANKS; ++p) {
+            if (p < a.n) {
+              const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(a.full_g.ptr[p]) + full_base + i);
+              glo[p] = __ldcg(src);
+              ghi[p] = __ldcg(src + 1);
+            }
+          }
+        } else {
+          const float4* sg = reinterpret_cast<const float4*>(a.shard_grad + si);
+          glo[0] = sg[0];
+          ghi[0] = sg[1];
+        }
+        float4* pm = reinterpret_cast<float4*>(a.master + si);
+        float4* mm = reinterpret_cast<float4*>(a.m + si);
+        float4* vm = reinterpret_cast<float4*>(a.v + si);
+        if (a.do_update) {
+          *reinterpret_cast<float4*>(pv) = pm[0]; *reinterpret_cast<float4*>(pv + 4) = pm[1];
+          *reinterpret_cast<float4*>(mv) = mm[0]; *reinterpret_cast<float4*>(mv + 4) = mm[1];
+          *reinterpret_cast<float4*>(vv) = vm[0]; *reinterpret_cast<float4*>(vv + 4) = vm[1];
+        }
         if (a.do_reduce) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) g[j] = 0.f;
-          for (int p = 0; p < a.n; ++p) {
-            const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(a.full_g.ptr[p]) + full_base + i);
-            const float4 lo = src[0], hi = src[1];
-            g[0] += lo.x; g[1] += lo.y; g[2] += lo.z; g[3] += lo.w;
-            g[4] += hi.x; g[5] += hi.y; g[6] += hi.z; g[7] += hi.w;
+#pragma unroll
+          for (int p = 0; p < MAX_RANKS; ++p) {
+            if (p < a.n) {
+              g[0] += glo[p].x; g[1] += glo[p].y; g[2] += glo[p].z; g[3] += glo[p].w;
+              g[4] += ghi[p].x; g[5] += ghi[p].y; g[6] += ghi[p].z; g[7] += ghi[p].w;
+            }
           }
 #pragma unroll
           for (int j = 0; j < 8; ++j) g[j] *= inv;
@@ -475,18 +240,10 @@ __global__ void __launch_bounds__(512) fsdp_step_kernel(const FsdpArgs a) {
           sg[0] = make_float4(g[0], g[1], g[2], g[3]);
           sg[1] = make_float4(g[4], g[5], g[6], g[7]);
         } else {
-          const float4* sg = reinterpret_cast<const float4*>(a.shard_grad + si);
-          const float4 lo = sg[0], hi = sg[1];
-          g[0] = lo.x; g[1] = lo.y; g[2] = lo.z; g[3] = lo.w; g[4] = hi.x; g[5] = hi.y; g[6] = hi.z; g[7] = hi.w;
+          g[0] = glo[0].x; g[1] = glo[0].y; g[2] = glo[0].z; g[3] = glo[0].w;
+          g[4] = ghi[0].x; g[5] = ghi[0].y; g[6] = ghi[0].z; g[7] = ghi[0].w;
         }
         if (a.do_update) {
-          float4* pm = reinterpret_cast<float4*>(a.master + si);
-          float4* mm = reinterpret_cast<float4*>(a.m + si);
-          float4* vm = reinterpret_cast<float4*>(a.v + si);
-          float pv[8], mv[8], vv[8];
-          *reinterpret_cast<float4*>(pv) = pm[0]; *reinterpret_cast<float4*>(pv + 4) = pm[1];
-          *reinterpret_cast<float4*>(mv) = mm[0]; *reinterpret_cast<float4*>(mv + 4) = mm[1];
-          *reinterpret_cast<float4*>(vv) = vm[0]; *reinterpret_cast<float4*>(vv + 4) = vm[1];
 #pragma unroll
           for (int j = 0; j < 8; ++j) pv[j] = adamw_one(a, pv[j], g[j], mv[j], vv[j]);
           pm[0] = *reinterpret_cast<float4*>(pv); pm[1] = *reinterpret_cast<float4*>(pv + 4);
@@ -613,70 +370,12 @@ int b2_comm_set_wait_ns(long long ns) {
 }
 
 int b2_comm_max_ranks() { return MAX_RANKS; }
-int b2_comm_max_experts() { return MAX_EXPERTS; }
 
 // Pointer tables are passed as arrays of MAX_RANKS device addresses (unused entries 0).
 static Peers table(const unsigned long long* p) {
   Peers t{};
   for (int i = 0; i < MAX_RANKS; ++i) t.ptr[i] = p ? reinterpret_cast<void*>(p[i]) : nullptr;
   return t;
-}
-
-int b2_ep_plan(const long long* idx, int slots, int experts_total, int ep, int rank, int seq, int capacity_rows,
-               const unsigned long long* counts_all, const unsigned long long* sig, int sig_slot, int* slot_row,
-               int* slot_dest, int* offs, int* seg_live_end, int* tile_expert, int* meta, int* status,
-               cudaStream_t s) {
-  if (experts_total > MAX_EXPERTS || ep > MAX_RANKS || experts_total % ep || ep * experts_total > PLAN_THREADS)
-    return -10;
-  EpPlanArgs a{};
-  a.idx = idx; a.slots = slots; a.experts_total = experts_total; a.ep = ep; a.rank = rank; a.seq = seq;
-  a.capacity_rows = capacity_rows; a.counts_all = table(counts_all); a.sig = table(sig); a.sig_slot = sig_slot;
-  a.slot_row = slot_row; a.slot_dest = slot_dest; a.offs = offs; a.seg_live_end = seg_live_end;
-  a.tile_expert = tile_expert; a.meta = meta; a.status = status;
-  const size_t smem = static_cast<size_t>(experts_total) * PLAN_THREADS * 4;
-  static bool set = false;
-  if (!set) {
-    cudaFuncSetAttribute(ep_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    set = true;
-  }
-  ep_plan_kernel<<<1, PLAN_THREADS, smem, s>>>(a);
-  return launched();
-}
-
-int b2_ep_push(const void* src, const int* row_of, const int* dest_of, const int* tag_of, const float* scalar_of,
-               const int* live_items, int items, int D, int src_shift, int dest_capacity, int rank, int n, int seq,
-               int sig_slot, const unsigned long long* land, const unsigned long long* land_tag,
-               const unsigned long long* land_src, const unsigned long long* land_scalar,
-               const unsigned long long* sig, unsigned int* counter, cudaStream_t s) {
-  if (D % 8) return -10;
-  EpPushArgs a{};
-  a.src = static_cast<const __nv_bfloat16*>(src); a.row_of = row_of; a.dest_of = dest_of; a.tag_of = tag_of;
-  a.scalar_of = scalar_of; a.live_items = live_items; a.items = items; a.D = D; a.src_shift = src_shift;
-  a.dest_capacity = dest_capacity; a.rank = rank; a.n = n; a.seq = seq; a.sig_slot = sig_slot;
-  a.land = table(land); a.land_tag = table(land_tag); a.land_src = table(land_src);
-  a.land_scalar = table(land_scalar); a.sig = table(sig); a.counter = counter;
-  ep_push_kernel<<<device_sms() * 8, 256, 0, s>>>(a);
-  return launched();
-}
-
-int b2_ep_consume(const void* land, const int* land_tag, const int* land_src, const float* land_scalar,
-                  const int* tile_expert, const int* seg_live_end, const int* meta, const void* y_perm,
-                  const unsigned long long* ret_scalar, void* out, int* row_tag, int* row_src, const int* my_sig,
-                  int D, int capacity, int n, int seq, int sig_slot, int* status, cudaStream_t s) {
-  if (D % 8) return -10;
-  EpConsumeArgs a{};
-  a.land = static_cast<const __nv_bfloat16*>(land); a.land_tag = land_tag; a.land_src = land_src;
-  a.land_scalar = land_scalar; a.tile_expert = tile_expert; a.seg_live_end = seg_live_end; a.meta = meta;
-  a.y_perm = static_cast<const __nv_bfloat16*>(y_perm); a.ret_scalar = table(ret_scalar);
-  a.out = static_cast<__nv_bfloat16*>(out); a.row_tag = row_tag; a.row_src = row_src; a.my_sig = my_sig; a.D = D;
-  a.capacity = capacity; a.n = n; a.seq = seq; a.sig_slot = sig_slot; a.status = status;
-  ep_consume_kernel<<<device_sms() * 4, 256, 0, s>>>(a);
-  return launched();
-}
-
-int b2_ep_wait(const int* my_sig, int sig_slot, int n, int seq, int* status, cudaStream_t s) {
-  ep_wait_kernel<<<1, 32, 0, s>>>(my_sig, sig_slot, n, seq, status);
-  return launched();
 }
 
 // kind: 0 one-shot (result in ``out``), 1 two-shot in place, 2 NVLS in place (needs ``mc``).

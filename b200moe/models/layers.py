@@ -264,8 +264,8 @@ class MoELayerMulti(nn.Module):
         experts_total = self.world_size * self.num_expert_per_node
         ep_ctx = None
         if self.comm is not None and self.world_size > 1 and flat.is_cuda:
-            ep_ctx = self.comm.ep_context(flat.shape[0], flat.shape[1], experts_total, ffn=self.experts.dff)
-        if ep_ctx is not None and hasattr(ep_ctx, "acquire") and ops.use_native(flat, "moe"):
+            ep_ctx = self.comm.ep_context(flat.shape[0], flat.shape[1], experts_total, self.experts.dff)
+        if ep_ctx is not None and ops.use_native(flat, "moe"):
             # exchange fused with the expert GEMMs: the router reads the staged copy of the input that the other
             # ranks pull their rows from
             from ..ops.moe_fused import moe_ffn_pull
@@ -283,7 +283,7 @@ class MoELayerMulti(nn.Module):
             weights, idx = ops.router_top2(logits)
             out = ops.moe_ffn(flat, weights, idx, self.experts.w1, self.experts.w2, self.experts.w3,
                               group=self.dp_group if self.world_size > 1 else None,
-                              recompute=self.recompute, ep_ctx=ep_ctx, key=id(self), budget=self.budget)
+                              recompute=self.recompute, budget=self.budget)
         out = out.view(shape).to(in_dtype)
         if return_aux_loss:
             from ..ops.moe import aux_loss_from

@@ -247,15 +247,14 @@ def aux_loss_from(logits, idx, num_experts_total: int, k: int, group=None):
 
 
 def moe_ffn(x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor, w1, w2, w3, *,
-            group=None, recompute: bool = False, ep_ctx=None, key=None, budget=None) -> torch.Tensor:
+            group=None, recompute: bool = False, budget=None) -> torch.Tensor:
     """Dispatch ``x [T, D]`` to its top-2 experts, run them, combine with the
     renormalised weights.  ``w1, w3: [E_local, d_ff, D]``, ``w2: [E_local, D, d_ff]``."""
     tokens, k = idx.shape
     ep = 1 if group is None else dist.get_world_size(group)
-    if _use_native(x, "moe") and (ep == 1 or ep_ctx is not None):
+    if _use_native(x, "moe") and ep == 1:
         from .moe_fused import moe_ffn_fused
-        return moe_ffn_fused(x, weights, idx, w1, w2, w3, ep_ctx=ep_ctx if ep > 1 else None, recompute=recompute,
-                             key=key, budget=budget)
+        return moe_ffn_fused(x, weights, idx, w1, w2, w3, recompute=recompute, budget=budget)
     plan = build_plan(idx, w1.shape[0] * ep, group)
     sent = x[plan.order // k]
     received = sent if ep == 1 else _AllToAllRows.apply(sent, plan.send_splits, plan.recv_splits, group)

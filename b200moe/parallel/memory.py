@@ -25,11 +25,23 @@ __all__ = ["ActivationBudget", "stage_activation_budget", "fixed_bytes_per_block
 
 
 class ActivationBudget:
-    def __init__(self, total_bytes: int, max_live_calls: int = 0, routed_bytes_per_call: int = 0):
+    def __init__(self, total_bytes: int, max_live_calls: int = 0, routed_bytes_per_call: int = 0,
+                 fixed_bytes_per_call: int = 0, floor_bytes: int = 0, probe=None, cold_floor_bytes: int = 0,
+                 cold_calls: int = 0):
+        """``probe``: optional callable returning the bytes the device can still hand out right now (free HBM plus
+        what the allocator holds unused).  The plan above is arithmetic; the probe is the cross-check against what
+        really happened: the optional tensors of a call are kept only if, after them, the device still has room for
+        the fixed-size activations of the calls to come (``fixed_bytes_per_call`` each) plus ``floor_bytes``.  During
+        the first ``cold_calls`` calls ``cold_floor_bytes`` more are held back: the expert workspaces and the
+        backward pass's transients do not exist yet and are about to be allocated."""
         self.total = int(total_bytes)
         self.max_live_calls = int(max_live_calls)
         # bytes of routing-dependent tensors a call saves whatever happens (its share of a balanced split)
         self.routed_bytes_per_call = int(routed_bytes_per_call)
+        self.fixed_bytes_per_call = int(fixed_bytes_per_call)
+        self.floor_bytes = int(floor_bytes)
+        self.cold_floor_bytes, self.cold_calls = int(cold_floor_bytes), int(cold_calls)
+        self.probe = probe
         self.used = 0
         self.live_calls = 0
         self.granted = 0
@@ -47,6 +59,11 @@ class ActivationBudget:
         still_to_come = max(0, self.max_live_calls - self.live_calls)
         reserve = still_to_come * self.routed_bytes_per_call
         keep = self.used + routed_bytes + optional_bytes + reserve <= self.total
+        if keep and self.probe is not None:
+            ahead = still_to_come * (self.fixed_bytes_per_call + self.routed_bytes_per_call) + self.floor_bytes
+            if self.granted + self.refused < self.cold_calls:
+                ahead += self.cold_floor_bytes
+            keep = self.probe() - routed_bytes - optional_bytes >= ahead
         self.used += routed_bytes + (optional_bytes if keep else 0)
         if keep:
             self.granted += 1
@@ -113,6 +130,7 @@ def stage_activation_budget(*, tokens_per_microbatch: int, d_model: int, d_ff: i
     in_flight = max(1, min(pp - stage, microbatches))
     shape = _StageShape(tokens_per_microbatch, d_model, d_ff, num_heads, experts_total, ep, blocks, in_flight, vocab,
                         stage == pp - 1)
+    free_bytes_given = free_bytes
     if free_bytes is None:
         free, _total = torch.cuda.mem_get_info(device)
         cached = torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
@@ -123,5 +141,13 @@ def stage_activation_budget(*, tokens_per_microbatch: int, d_model: int, d_ff: i
     if routed_row_bytes is None:
         routed_row_bytes = d_model * 2 * 2
     balanced_rows = tokens_per_microbatch * 2
+    probe = None
+    if free_bytes_given is None:
+        def probe():
+            free_now, _ = torch.cuda.mem_get_info(device)
+            return free_now + torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
+    per_block = fixed_bytes_per_block(tokens_per_microbatch, d_model, num_heads, experts_total)
     return ActivationBudget(max(total, 0), max_live_calls=in_flight * blocks,
-                            routed_bytes_per_call=balanced_rows * routed_row_bytes)
+                            routed_bytes_per_call=balanced_rows * routed_row_bytes, fixed_bytes_per_call=per_block,
+                            floor_bytes=int(margin_bytes), probe=probe, cold_floor_bytes=_workspace_bytes(shape),
+                            cold_calls=2 * in_flight * blocks)

@@ -101,7 +101,7 @@ def build_model(config: dict, mesh, device, fsdp_group, ddp_group, compute_dtype
             vocab=data_cfg["vocab_size"], device=device,
             margin_bytes=int(float(train_cfg.get("activation_margin_gib", 6.0)) * 2 ** 30),
             # with the exchange fused into the expert GEMMs a call keeps no routing-dependent tensor but gate/up
-            routed_row_bytes=0 if (comm is not None and fsdp > 1 and comm.ep_mode == "pull") else None)
+            routed_row_bytes=0 if (comm is not None and fsdp > 1) else None)
         for layer in model.layers:
             layer.ffn.budget = budget
         wrapped.activation_budget = budget

@@ -91,7 +91,7 @@ def main():
         dout = torch.randn(T, D, device=device).bfloat16()
         from b200moe.comm import ep as EP
         from b200moe.ops.moe_fused import moe_ffn_pull
-        epc = comm.ep_context(T, D, E, ffn=Fd)
+        epc = comm.ep_context(T, D, E, Fd)
 
         def block(fused):
             xs, lg = x.clone().requires_grad_(True), logits.clone().requires_grad_(True)

@@ -108,8 +108,7 @@ def _moe_ep(rank, world, port, out_dir):
                   (torch.randn(e_local, Fd, D, device=device) * 0.06).bfloat16(),
                   (torch.randn(e_local, D, Fd, device=device) * 0.06).bfloat16())
     dout = torch.randn(T, D, device=device).bfloat16()
-    epc = comm.ep_context(T, D, E_total, ffn=Fd)
-    assert hasattr(epc, "acquire")
+    epc = comm.ep_context(T, D, E_total, Fd)
     for case in ("unbalanced", "all_to_rank0"):
         logits = torch.randn(T, E_total, device=device)
         if case == "unbalanced":
@@ -141,6 +140,8 @@ def _moe_ep(rank, world, port, out_dir):
 def _train_parity(rank, world, port, out_dir, pp, ddp=1, skew=False):
     """A few training steps: fused peer-memory backend against the NCCL backend.  ``skew``: every token of every
     rank is routed to the two first experts (both on shard rank 0), the worst case for the expert buffers."""
+    import warnings
+
     import torch
     from b200moe.comm import make_comm
     from b200moe.ops import native
@@ -182,12 +183,23 @@ def _train_parity(rank, world, port, out_dir, pp, ddp=1, skew=False):
         ids = torch.randint(0, 2048, (4, 257), device=device)
         run = []
         before = native.launch_count()
-        for _ in range(3):
+        for step in range(3):
             x = ids[:, :-1] if mesh.stage == 0 else None
             y = ids[:, 1:] if mesh.stage == pp - 1 else None
-            loss = pipelined_train_overlap(model, opt, x, y, [4, 256, 512], 2, mesh.stage, cross_entropy,
-                                           dtype=torch.bfloat16, device=device, pp_group=mesh.group("pp"),
-                                           dp_group=mesh.group("data"))
+            # third step of the fused backend: nothing inside a step may make the host wait for the device
+            watch = backend == "fused" and gather == "step" and step == 2
+            with warnings.catch_warnings(record=True) as seen:
+                warnings.simplefilter("always")
+                if watch:
+                    torch.cuda.set_sync_debug_mode(1)
+                try:
+                    loss = pipelined_train_overlap(model, opt, x, y, [4, 256, 512], 2, mesh.stage, cross_entropy,
+                                                   dtype=torch.bfloat16, device=device, pp_group=mesh.group("pp"),
+                                                   dp_group=mesh.group("data"))
+                finally:
+                    torch.cuda.set_sync_debug_mode(0)
+            syncs = [str(w.message) for w in seen if "synchroniz" in str(w.message).lower()]
+            assert not (watch and syncs), syncs
             run.append(float(loss))
         losses[variant] = run
         weights[variant] = model.flat.master.clone()

@@ -32,15 +32,21 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def test_wait_kernel_gives_up_and_reports_its_code(native):
+def test_combine_kernel_gives_up_and_reports_its_code(native):
+    """The source side of the expert exchange waiting for an owner that never delivers."""
     pad = torch.zeros(32 * MAX_RANKS, dtype=torch.int32, device="cuda")       # nobody ever signals
     status = native.status_word()
+    tokens, D = 64, 128
+    ret = torch.ones(2 * tokens, D, dtype=torch.bfloat16, device="cuda")
+    out = torch.full((tokens, D), 7.0, dtype=torch.bfloat16, device="cuda")
     t0 = time.perf_counter()
-    native._call("b2_ep_wait", ctypes.c_void_p(pad.data_ptr()), ctypes.c_int(2), ctypes.c_int(2), ctypes.c_int(1),
-                 ctypes.c_void_p(status.data_ptr()), _stream())
+    native._call("b2_ep_combine", ctypes.c_void_p(ret.data_ptr()), ctypes.c_void_p(0), ctypes.c_void_p(out.data_ptr()),
+                 ctypes.c_void_p(0), ctypes.c_int(tokens), ctypes.c_int(D), ctypes.c_void_p(pad.data_ptr()),
+                 ctypes.c_int(18), ctypes.c_int(2), ctypes.c_int(1), ctypes.c_void_p(status.data_ptr()), _stream())
     torch.cuda.synchronize()
     assert time.perf_counter() - t0 < 1.0
     assert int(status.item()) == 104
+    assert float(out.float().min()) == 7.0              # the output was left alone
     with pytest.raises(RuntimeError, match="104"):
         native.check_status()
     native.clear_status()

@@ -30,6 +30,21 @@ def test_budget_keeps_optional_tensors_only_while_they_fit_beside_the_calls_to_c
     assert budget.used == 0 and budget.live_calls == 0
 
 
+def test_budget_cross_checks_its_plan_against_what_the_device_really_has_left():
+    room = {"bytes": 1000}
+    budget = ActivationBudget(total_bytes=10_000, max_live_calls=3, fixed_bytes_per_call=100, floor_bytes=50,
+                              probe=lambda: room["bytes"], cold_floor_bytes=400, cold_calls=1)
+    # first call (cold): 1000 - 300 optional must cover 2 calls x 100 + floor 50 + cold 400 = 650 -> kept
+    assert budget.enter(0, 300) is True
+    room["bytes"] = 500
+    # second call (warm): 500 - 300 = 200 >= 1 x 100 + 50 -> kept;  with 420 optional it would not be
+    assert budget.enter(0, 420) is False
+    assert budget.enter(0, 300) is True
+    budget = ActivationBudget(total_bytes=10_000, max_live_calls=3, fixed_bytes_per_call=100, floor_bytes=50,
+                              probe=lambda: 900, cold_floor_bytes=400, cold_calls=1)
+    assert budget.enter(0, 300) is False        # the plan says yes, the cold device says no: 600 < 650
+
+
 def test_stage_budget_shrinks_with_the_microbatches_a_stage_keeps_alive():
     common = dict(tokens_per_microbatch=16384, d_model=4096, d_ff=14336, num_heads=32, experts_total=8, ep=2,
                   blocks=8, pp=4, microbatches=32, vocab=32000, free_bytes=95 << 30)
