@@ -760,7 +760,8 @@ int b2_rmsnorm_fwd(const void* x, const void* delta, const float* w, void* sum_o
 }
 
 // dw_partial: fp32 [parts, D] scratch with parts = b2_rmsnorm_bwd_parts(rows); dw: fp32 [D] (overwritten).
-int b2_rmsnorm_bwd_parts(int rows) { return min(rows, sm_count_ew() * 6); }
+// two CTAs are resident per SM (registers): one wave, and as few partial rows as possible for the column sum
+int b2_rmsnorm_bwd_parts(int rows) { return min(rows, sm_count_ew() * 2); }
 int b2_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* residual, void* dx,
                    float* dw_partial, float* dw, int rows, int D, cudaStream_t s) {
   if (D % 8 || D > NORM_THREADS * 8 * NORM_MAX_CHUNKS) return -10;

@@ -8,13 +8,15 @@ neighbour exchange is one batched send+recv; the loss of a microbatch is divided
 by the microbatch count; the value returned is the mean loss on the last stage
 and ``0.0`` elsewhere (or a metrics dict).
 
-Differences in mechanism: transfers are issued asynchronously and only the
-stream that consumes a received tensor waits for it, so the host runs ahead and
-the copy overlaps compute already queued; on the last stage the loss comes from
-the fused LM-head/cross-entropy op when the model offers ``loss()`` and the
-caller passed this framework's ``cross_entropy``; after ``optimizer.step()`` the
-wrapper refreshes its gathered weights (``after_optimizer_step``) or runs its
-fused reduce-scatter/AdamW/all-gather kernel (``fused_optimizer_step``).
+Differences in mechanism: the host never blocks on a transfer (with NCCL,
+``work.wait()`` orders the compute stream after the exchange, it does not stop
+the host), so the host runs ahead of the device; the exchange itself is ordered
+on the compute stream like the reference's, it is not overlapped with compute.
+On the last stage the loss comes from the chunked LM-head/cross-entropy op when
+the model offers ``loss()`` and the caller passed this framework's
+``cross_entropy``; after ``optimizer.step()`` the wrapper refreshes its gathered
+weights (``after_optimizer_step``) or runs its fused reduce-scatter/AdamW/
+all-gather kernel (``fused_optimizer_step``).
 """
 from __future__ import annotations
 
@@ -50,7 +52,7 @@ def router_loss_metrics(task_loss, auxiliary, coefficient, pp_group, dp_group):
 
 
 class _Link:
-    """Batched send/recv with one neighbour stage; completion is awaited lazily."""
+    """Batched send/recv with one neighbour stage; the compute stream waits for it."""
 
     def __init__(self, ranks, stage, pp_group, spec, dtype, device):
         self.ranks, self.stage, self.group = ranks, stage, pp_group

@@ -85,6 +85,10 @@ def main():
     x = rnd(T, D)
     wqkv, wo = rnd(6144, D, scale=0.02), rnd(D, D, scale=0.02)
     gemm_case("gemm_nt qkv 16384x6144x4096", 2 * T * 6144 * D, lambda: native.gemm_nt(x, wqkv), lambda: x @ wqkv.t())
+    from b200moe.ops import functional as Fn
+    cos, sin = Fn.rope_tables(10000.0, 128, 8192, device="cuda")
+    gemm_case("gemm_nt qkv + RoPE in the epilogue 16384x6144x4096", 2 * T * 6144 * D,
+              lambda: native.gemm_nt_rope(x, wqkv, cos, sin, 5120, 8192))
     gemm_case("gemm_nt out 16384x4096x4096", 2 * T * D * D, lambda: native.gemm_nt(x, wo), lambda: x @ wo.t())
     hk, wk = rnd(T, Fd, scale=0.1), rnd(D, Fd, scale=0.02)
     gemm_case("gemm_nt K=14336 16384x4096x14336", 2 * T * D * Fd, lambda: native.gemm_nt(hk, wk))
@@ -142,7 +146,9 @@ def main():
     bw_case("swiglu_bwd 32768x14336", 6 * R * Fd * 2, lambda: native.swiglu_bwd(h, gate, up))
     logits = rnd(T, 32000)
     tgt = torch.randint(0, 32000, (T,), device="cuda")
-    bw_case("cross_entropy fwd+bwd 16384x32000", 3 * T * 32000 * 2, lambda: native.cross_entropy_fwd_bwd_(logits, tgt))
+    ce_loss = torch.zeros((), device="cuda")
+    bw_case("cross_entropy fwd+bwd 16384x32000 (row in registers)", 2 * T * 32000 * 2,
+            lambda: native.cross_entropy_scaled_(logits, tgt, ce_loss, 1.0 / T, 1.0 / T))
     n = 1 << 28
     p, g, m, v = (torch.zeros(n, device="cuda", dtype=torch.bfloat16) for _ in range(4))
     bw_case("adamw bf16 x4 256Mi", 7 * n * 2, lambda: native.adamw_(p, g, m, v, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1e-3))

@@ -401,6 +401,35 @@ def test_attention_forward_backward(native, B, S, Hq, Hkv):
     native.check_status()
 
 
+def test_attention_at_the_training_shape_against_fp32_one_kv_group_at_a_time(native):
+    """Sequence 8192 with 32 query and 8 key/value heads: the fp32 statement is evaluated per key/value head (four
+    query heads, a 4 x 8192 x 8192 score block) so that it fits beside the kernels' tensors."""
+    torch.manual_seed(4)
+    B, S, Hq, Hkv, hd = 1, 8192, 32, 8, 128
+    ratio, total = Hq // Hkv, Hq + 2 * Hkv
+    qkv = _rand(B, S, total, hd)
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    dout = _rand(B, S, Hq, hd)
+    out, lse, _, _ = native.attention_fwd(q, k, v)
+    dq, dk, dv = native.attention_bwd(dout, q, k, v, out, lse)
+    native.check_status()
+    mask = torch.triu(torch.ones(S, S, dtype=torch.bool, device="cuda"), 1)
+    for g in range(Hkv):
+        heads = slice(g * ratio, (g + 1) * ratio)
+        qf = q[0, :, heads].detach().float().transpose(0, 1).requires_grad_(True)       # [4, S, hd]
+        kf = k[0, :, g].detach().float().requires_grad_(True)                           # [S, hd]
+        vf = v[0, :, g].detach().float().requires_grad_(True)
+        scores = (qf @ kf.t()) / math.sqrt(hd)
+        scores = scores.masked_fill(mask, float("-inf"))
+        ref = torch.softmax(scores, -1) @ vf                                             # [4, S, hd]
+        ref.backward(dout[0, :, heads].float().transpose(0, 1))
+        assert _rel(out[0, :, heads].transpose(0, 1), ref) < 1e-2, g
+        assert _rel(lse[0, heads], torch.logsumexp(scores.detach(), -1)) < 1e-3, g
+        assert _rel(dq[0, :, heads].transpose(0, 1), qf.grad) < 2e-2, g
+        assert _rel(dk[0, :, g], kf.grad) < 2e-2 and _rel(dv[0, :, g], vf.grad) < 2e-2, g
+        del scores, ref, qf, kf, vf
+
+
 @pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 256, 2, 2), (2, 512, 4, 1)])
 def test_attention_non_causal(native, B, S, Hq, Hkv):
     """Every query sees every key (the form of the reference's own flash kernel): forward and backward."""
