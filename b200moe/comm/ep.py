@@ -225,17 +225,15 @@ class EPPull:
                     split_row):
         g = self.g
         save_src, save_tag, save_w = save if save is not None else (None, None, None)
-        rc = native.require().b2_ep_gather_gemm(
+        # (return code -20: the device cannot keep one CTA per SM resident, which the cooperative launch needs)
+        native._call(
+            "b2_ep_gather_gemm",
             _i(mode), _ptr(a_buf), _ptr(w), _ptr(w_b), _i(self.cap), _i(N), _i(K), _i(self.e_local),
             _ptr(tile_expert), _ptr(meta), _ptr(seg_live_end), _i(tile_begin), src_table, _i(shift), _ptr(row_src),
             _ptr(row_tag), _ptr(row_w), _ptr(save_src), _ptr(save_tag), _ptr(save_w), _ptr(self.tile_ready),
             _ptr(self.tickets[mode:]), g.sig.table(), _i(self.ep), _i(g.rank), _i(sig_slot), _i(seq), _i(handshake),
             _ptr(d), _ptr(gate_lo), _ptr(up_lo), _ptr(gate_hi), _ptr(up_hi), _i(split_row), _ptr(self.status),
-            _stream())
-        if rc != 0:
-            raise RuntimeError(f"b2_ep_gather_gemm failed with code {rc}"
-                               + (" (the device cannot keep one CTA per SM resident)" if rc == -20 else ""))
-        native.count_launch()
+            _stream(), tag=("gate/up" if mode == 0 else "dh") + (" (re-gather, rebuild)" if gate_hi is not None else ""))
 
     def combine(self, ret, sig_slot, seq, with_scalars: bool):
         out = torch.empty(self.tokens, self.dim, dtype=torch.bfloat16, device=self.device)

@@ -150,8 +150,41 @@ def set_nvtx(enabled: bool) -> None:
     _nvtx = bool(enabled)
 
 
-def _call(name, *args, n: int = 1):
+_timed = None      # list of (label, start event, end event) while launch timing is on
+
+
+def start_launch_timing() -> None:
+    """Bracket every launch of this library with a pair of CUDA events on its stream (``launch_times`` reads them).
+    For per-kernel time tables of a whole step; it adds two event records per launch, so timed regions of a
+    benchmark leave it off."""
+    global _timed
+    _timed = []
+
+
+def launch_times() -> dict:
+    """Stops launch timing and returns ``{label: (launches, total ms)}``; synchronises the device."""
+    global _timed
+    records, _timed = _timed or [], None
+    torch.cuda.synchronize()
+    table: dict = {}
+    for label, begin, end in records:
+        count, total = table.get(label, (0, 0.0))
+        table[label] = (count + 1, total + begin.elapsed_time(end))
+    return table
+
+
+def _call(name, *args, n: int = 1, tag: str = ""):
     global _launches
+    if _timed is not None:
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        rc = getattr(require(), name)(*args)
+        end.record()
+        _timed.append((f"{name} {tag}".strip(), begin, end))
+        if rc != 0:
+            raise RuntimeError(f"{name} failed with code {rc}")
+        _launches += n
+        return
     if _nvtx:
         torch.cuda.nvtx.range_push(name)
         try:
@@ -197,7 +230,7 @@ def gemm_nt(x, w, out_dtype=None, tile_expert=None, num_m_tiles=None, num_expert
     _call("b2_gemm_nt", _p(_bf16(x)), _p(_bf16(w)), _p(out), _I(M), _I(N), _I(K), _L(x.stride(0)), _L(K), _L(N),
           _I(num_experts), _p(tile_expert), _p(num_m_tiles), _I(int(align256)),
           _I(0 if out_dtype == torch.bfloat16 else 4),
-          _p(status_word(x.device)), _stream())
+          _p(status_word(x.device)), _stream(), tag=f"{'grouped ' if tile_expert is not None else ''}N={N} K={K}")
     return out
 
 
@@ -232,7 +265,7 @@ def gemm_nn(dy, w, w2=None, tile_expert=None, num_m_tiles=None, num_experts: int
     assert dy.stride(-1) == 1 and w.is_contiguous() and out.stride(-1) == 1 and out.shape == (M, N)
     _call("b2_gemm_nn", _p(_bf16(dy)), _p(_bf16(w)), _p(w2), _p(_bf16(out)), _I(M), _I(N), _I(K), _I(k_split),
           _L(dy.stride(0)), _L(N), _L(out.stride(0)), _I(num_experts), _p(tile_expert), _p(num_m_tiles), _I(int(align256)),
-          _p(status_word(dy.device)), _stream())
+          _p(status_word(dy.device)), _stream(), tag=f"{'grouped ' if tile_expert is not None else ''}N={N} K={K}")
     return out
 
 
@@ -261,7 +294,8 @@ def gemm_tn(dy, x, out=None, accumulate: bool = False, out_dtype=None, expert_of
     assert dy.stride(-1) == 1 and x.stride(-1) == 1 and out.is_contiguous()
     _call("b2_gemm_tn", _p(_bf16(dy)), _p(_bf16(x)), _p(out), _I(M), _I(N), _I(R), _L(dy.stride(0)), _L(x.stride(0)),
           _L(N), _I(num_experts), _p(expert_offsets), _I(kind), _F(1.0 if accumulate else 0.0),
-          _p(status_word(dy.device)), _stream())
+          _p(status_word(dy.device)), _stream(),
+          tag=f"{'grouped ' if expert_offsets is not None else ''}{M}x{N} {'fp32' if kind == 1 else 'bf16'}")
     return out if want is None or want == out.dtype else out.to(want)
 
 

@@ -65,6 +65,9 @@ def parse_args():
     p.add_argument("--recompute", default=None, choices=["none", "swiglu", "block"])
     p.add_argument("--backend", default=None, choices=["fused", "nccl"])
     p.add_argument("--layout", default=None, choices=sorted(NAMED), help="a named 8-GPU configuration")
+    p.add_argument("--kernel-times", default=None, metavar="FILE",
+                   help="after the measurement, run one more step with a CUDA-event pair around every launch of this "
+                        "library and write rank 0's per-kernel totals to FILE (JSON)")
     return p.parse_args()
 
 
@@ -316,6 +319,21 @@ def bench_b200moe(args):
 
         device_ms, e2e_ms, clocks, launches, last = measure(step, args, device, rank, native.launch_count)
         native.check_status()      # a device-side wait that ran out is an error
+        if args.kernel_times:
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            native.start_launch_timing()
+            begin.record()
+            step(args.warmup + args.steps)
+            end.record()
+            table = native.launch_times()
+            if rank == 0:
+                step_ms = begin.elapsed_time(end)
+                rows = sorted(((ms, label, count) for label, (count, ms) in table.items()), reverse=True)
+                with open(args.kernel_times, "w") as handle:
+                    json.dump({"step_ms": step_ms, "native_ms": sum(r[0] for r in rows), "n_gpus": args.gpus,
+                               "kernels": [{"launch": label, "launches": count, "ms": round(ms, 3),
+                                            "share": round(ms / step_ms, 4)} for ms, label, count in rows]},
+                              handle, indent=1)
         loss = torch.tensor([float(last) if last is not None else 0.0], device=device)
         dist.all_reduce(loss, op=dist.ReduceOp.MAX)
         # allocator peak, and what the device itself reports as taken (symmetric buffers and library workspaces

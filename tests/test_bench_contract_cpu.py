@@ -17,7 +17,7 @@ import bench  # noqa: E402
 
 def _args(**over):
     base = dict(gpus=1, steps=2, warmup=3, impl="b200moe", layers=None, microbatches=32, batch=None, seq=8192,
-                recompute=None, backend=None, layout=None)
+                recompute=None, backend=None, layout=None, kernel_times=None)
     base.update(over)
     return argparse.Namespace(**base)
 
