@@ -282,7 +282,7 @@ def train(local_rank: int, cluster_rank: int, world_size: int, config: dict):
                             future.set_exception(error)
                         pending.append((iteration, directory, future))
                 if len(chaos):
-                    chaos.trigger()
+                    chaos.trigger(iteration)
     except BaseException:
         # leaving on an error path: stop the watchdog and let go of the peer-mapped buffers first, with no
         # kernel of this rank in flight, so that the peers never see a mapping vanish under a running kernel

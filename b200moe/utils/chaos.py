@@ -80,9 +80,25 @@ def random_cpu_hog(num_workers: int = 4, duration: float = 10, chance: float = 0
     return True
 
 
+# keys of a chaos entry that say WHEN it may fire; everything else is passed to the function
+GATES = ("after_iteration", "first_attempt_only", "rank")
+
+
 def function_register(chaos_function, parameters: dict):
-    def trigger():
-        return chaos_function(**parameters)
+    """Closure around one chaos function.  Optional gates in ``parameters`` (for reproducible fault drills):
+    ``after_iteration``: fire only once the loop has reached that iteration; ``first_attempt_only``: not after an
+    elastic restart (``TORCHELASTIC_RESTART_COUNT`` > 0); ``rank``: only on that global rank."""
+    gates = {k: parameters[k] for k in GATES if k in parameters}
+    kwargs = {k: v for k, v in parameters.items() if k not in GATES}
+
+    def trigger(iteration=None):
+        if "after_iteration" in gates and (iteration is None or iteration < gates["after_iteration"]):
+            return False
+        if gates.get("first_attempt_only") and int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0")) > 0:
+            return False
+        if "rank" in gates and int(os.environ.get("RANK", "0")) != gates["rank"]:
+            return False
+        return chaos_function(**kwargs)
     return trigger
 
 
@@ -117,8 +133,10 @@ class ChaosEnginnerTrigger:
     def __len__(self) -> int:
         return len(self._triggers)
 
-    def trigger(self) -> int:
-        return sum(1 for fire in self._triggers if fire())
+    def trigger(self, iteration=None) -> int:
+        """Fire every enabled function once; ``iteration`` (the number of finished iterations) feeds the
+        ``after_iteration`` gate."""
+        return sum(1 for fire in self._triggers if fire(iteration))
 
 
 ChaosEngineerTrigger = ChaosEnginnerTrigger
