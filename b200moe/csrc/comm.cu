@@ -177,8 +177,9 @@ __device__ __forceinline__ float adamw_one(const FsdpArgs& a, float p, float g, 
   return p - a.a_t * m / (sqrtf(v) + a.eps);
 }
 
-// Gradients cross NVLink as 16-byte fp32 vectors (peer loads), new weights as 16-byte vectors of eight bf16
-// (peer stores); entries whose offsets or sizes are not multiples of eight elements take the scalar loop.
+// Gradients cross NVLink as 16-byte fp32 vectors (peer loads), new weights as 8-byte vectors of four bf16 (peer
+// stores), both lane-contiguous; entries whose offsets or sizes are not multiples of eight elements take the scalar
+// loop.
 __global__ void __launch_bounds__(512) fsdp_step_kernel(const FsdpArgs a) {
   ArArgs bar{};
   bar.sig = a.sig; bar.rank = a.rank; bar.n = a.n; bar.seq = a.seq; bar.counter = a.counter; bar.status = a.status;
@@ -196,70 +197,65 @@ __global__ void __launch_bounds__(512) fsdp_step_kernel(const FsdpArgs a) {
     const long long full_base = ent.full_off + ent.shard_numel * a.rank;
     const bool everyone = !(ent.local_only && !a.push_all);
     if (((full_base | ent.shard_off | ent.shard_numel) & 7) == 0) {
-      for (long long i = tid * 8; i < ent.shard_numel; i += nthreads * 8) {
-        const long long si = ent.shard_off + i;
-        // every load of this iteration is issued before the first use: the peers' gradient vectors (NVLink), the
-        // local master weights and the two moments are all in flight together
-        float4 glo[MAX_RANKS], ghi[MAX_RANKS];
-        float pv[8], mv[8], vv[8], g[8];
-        if (a.do_reduce) {
+      // Unit of work: one float4.  Consecutive lanes take consecutive units, so every warp-wide load is 512
+      // contiguous bytes (whole sectors over NVLink) and every bf16 store 256; each thread handles two units per
+      // iteration, a grid apart, and issues all their loads (peers' gradients, master, both moments) before the
+      // first use.
+      const long long units = ent.shard_numel / 4;
+      for (long long u0 = tid; u0 < units; u0 += 2 * nthreads) {
+        const long long u1 = u0 + nthreads;
+        const bool two = u1 < units;
+        float4 gr[2][MAX_RANKS], pv[2], mv[2], vv[2];
 #pragma unroll
-          for (int p = 0; p < MAX_RANKS; ++p) {
-            if (p < a.n) {
-              const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(a.full_g.ptr[p]) + full_base + i);
-              glo[p] = __ldcg(src);
-              ghi[p] = __ldcg(src + 1);
-            }
-          }
-        } else {
-          const float4* sg = reinterpret_cast<const float4*>(a.shard_grad + si);
-          glo[0] = sg[0];
-          ghi[0] = sg[1];
-        }
-        float4* pm = reinterpret_cast<float4*>(a.master + si);
-        float4* mm = reinterpret_cast<float4*>(a.m + si);
-        float4* vm = reinterpret_cast<float4*>(a.v + si);
-        if (a.do_update) {
-          *reinterpret_cast<float4*>(pv) = pm[0]; *reinterpret_cast<float4*>(pv + 4) = pm[1];
-          *reinterpret_cast<float4*>(mv) = mm[0]; *reinterpret_cast<float4*>(mv + 4) = mm[1];
-          *reinterpret_cast<float4*>(vv) = vm[0]; *reinterpret_cast<float4*>(vv + 4) = vm[1];
-        }
-        if (a.do_reduce) {
+        for (int k = 0; k < 2; ++k) {
+          if (k == 1 && !two) break;
+          const long long i = (k ? u1 : u0) * 4;
+          if (a.do_reduce) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) g[j] = 0.f;
-#pragma unroll
-          for (int p = 0; p < MAX_RANKS; ++p) {
-            if (p < a.n) {
-              g[0] += glo[p].x; g[1] += glo[p].y; g[2] += glo[p].z; g[3] += glo[p].w;
-              g[4] += ghi[p].x; g[5] += ghi[p].y; g[6] += ghi[p].z; g[7] += ghi[p].w;
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) g[j] *= inv;
-          float4* sg = reinterpret_cast<float4*>(a.shard_grad + si);
-          sg[0] = make_float4(g[0], g[1], g[2], g[3]);
-          sg[1] = make_float4(g[4], g[5], g[6], g[7]);
-        } else {
-          g[0] = glo[0].x; g[1] = glo[0].y; g[2] = glo[0].z; g[3] = glo[0].w;
-          g[4] = ghi[0].x; g[5] = ghi[0].y; g[6] = ghi[0].z; g[7] = ghi[0].w;
-        }
-        if (a.do_update) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) pv[j] = adamw_one(a, pv[j], g[j], mv[j], vv[j]);
-          pm[0] = *reinterpret_cast<float4*>(pv); pm[1] = *reinterpret_cast<float4*>(pv + 4);
-          mm[0] = *reinterpret_cast<float4*>(mv); mm[1] = *reinterpret_cast<float4*>(mv + 4);
-          vm[0] = *reinterpret_cast<float4*>(vv); vm[1] = *reinterpret_cast<float4*>(vv + 4);
-          vec16 w;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const __nv_bfloat162 b = __floats2bfloat162_rn(pv[2 * j], pv[2 * j + 1]);
-            w.v[j] = *reinterpret_cast<const uint32_t*>(&b);
-          }
-          if (everyone) {
-            for (int p = 0; p < a.n; ++p)
-              *reinterpret_cast<vec16*>(static_cast<__nv_bfloat16*>(a.full_w.ptr[p]) + full_base + i) = w;
+            for (int p = 0; p < MAX_RANKS; ++p)
+              if (p < a.n)
+                gr[k][p] = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(a.full_g.ptr[p]) + full_base + i));
           } else {
-            *reinterpret_cast<vec16*>(static_cast<__nv_bfloat16*>(a.full_w.ptr[a.rank]) + full_base + i) = w;
+            gr[k][0] = *reinterpret_cast<const float4*>(a.shard_grad + ent.shard_off + i);
+          }
+          if (a.do_update) {
+            pv[k] = *reinterpret_cast<const float4*>(a.master + ent.shard_off + i);
+            mv[k] = *reinterpret_cast<const float4*>(a.m + ent.shard_off + i);
+            vv[k] = *reinterpret_cast<const float4*>(a.v + ent.shard_off + i);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          if (k == 1 && !two) break;
+          const long long i = (k ? u1 : u0) * 4;
+          const long long si = ent.shard_off + i;
+          float4 g = gr[k][0];
+          if (a.do_reduce) {
+#pragma unroll
+            for (int p = 1; p < MAX_RANKS; ++p)
+              if (p < a.n) {
+                g.x += gr[k][p].x; g.y += gr[k][p].y; g.z += gr[k][p].z; g.w += gr[k][p].w;
+              }
+            g.x *= inv; g.y *= inv; g.z *= inv; g.w *= inv;
+            *reinterpret_cast<float4*>(a.shard_grad + si) = g;
+          }
+          if (a.do_update) {
+            float4 pn;
+            pn.x = adamw_one(a, pv[k].x, g.x, mv[k].x, vv[k].x);
+            pn.y = adamw_one(a, pv[k].y, g.y, mv[k].y, vv[k].y);
+            pn.z = adamw_one(a, pv[k].z, g.z, mv[k].z, vv[k].z);
+            pn.w = adamw_one(a, pv[k].w, g.w, mv[k].w, vv[k].w);
+            *reinterpret_cast<float4*>(a.master + si) = pn;
+            *reinterpret_cast<float4*>(a.m + si) = mv[k];
+            *reinterpret_cast<float4*>(a.v + si) = vv[k];
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(pn.x, pn.y), hi = __floats2bfloat162_rn(pn.z, pn.w);
+            const uint2 w = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+            if (everyone) {
+              for (int p = 0; p < a.n; ++p)
+                *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(a.full_w.ptr[p]) + full_base + i) = w;
+            } else {
+              *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(a.full_w.ptr[a.rank]) + full_base + i) = w;
+            }
           }
         }
       }

@@ -44,7 +44,11 @@ template <int MT, int PAIR = 0> struct Cfg {
   static constexpr int NACC = MT == 2 ? 1 : 2;
   static constexpr int TM = PAIR ? 2 : MT;     // 128-row units per output tile
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int PUSH_STAGING = 4 * 32 * 256;   // EPI_PUSH: 32 rows x 128 bf16 columns per epilogue warp
 };
+template <int EPI, int MT, int PAIR = 0> constexpr int smem_bytes() {
+  return Cfg<MT, PAIR>::SMEM + (EPI == 5 /*EPI_PUSH*/ ? Cfg<MT, PAIR>::PUSH_STAGING : 0);
+}
 constexpr int GROUP_M = 8;
 
 enum Epilogue : int {
@@ -381,6 +385,52 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
             }
           }
         }
+      } else if (EPI == EPI_PUSH) {
+        // Rows leave for other GPUs.  A thread owns one row of the accumulator, so storing straight from registers
+        // would put 16 bytes per lane at 32 different rows in every store instruction.  Instead each warp stages
+        // 128 columns of its 32 rows in shared memory (16-byte units XOR-swizzled by row: conflict-free both ways) and
+        // writes them out two rows per instruction, 256 contiguous bytes per row.
+        const long long col_base = static_cast<long long>(t.n_tile) * BN;
+        uint4* stage = reinterpret_cast<uint4*>(smem + STAGES * STAGE_BYTES + 256) + (warp - 2) * (32 * 16);
+        int tag = -1, dest = -1;
+        float w = 1.f;
+        if (row_ok) {
+          tag = p.push_tag[row];
+          dest = p.push_src[row];
+          if (p.push_w) w = p.push_w[row];
+          if (dest < 0 || dest >= p.push_n) tag = -1;          // padding row: nobody waits for it
+        }
+#pragma unroll 1
+        for (int half = 0; half < BN / 128; ++half) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + half * 128 + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              stage[lane * 16 + ((c * 4 + i) ^ (lane & 15))] =
+                  make_uint4(pack_bf16(w * __uint_as_float(v[8 * i]), w * __uint_as_float(v[8 * i + 1])),
+                             pack_bf16(w * __uint_as_float(v[8 * i + 2]), w * __uint_as_float(v[8 * i + 3])),
+                             pack_bf16(w * __uint_as_float(v[8 * i + 4]), w * __uint_as_float(v[8 * i + 5])),
+                             pack_bf16(w * __uint_as_float(v[8 * i + 6]), w * __uint_as_float(v[8 * i + 7])));
+          }
+          __syncwarp();
+          const int unit = lane & 15;
+          const long long col = col_base + half * 128 + unit * 8;
+#pragma unroll 4
+          for (int pair = 0; pair < 16; ++pair) {
+            const int r = pair * 2 + (lane >> 4);
+            const int tag_r = __shfl_sync(0xffffffffu, tag, r);
+            const int dest_r = __shfl_sync(0xffffffffu, dest, r);
+            if (tag_r >= 0 && col < p.N) {
+              const uint4 data = stage[r * 16 + (unit ^ (r & 15))];
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.push_dst.ptr[dest_r]) +
+                                        static_cast<long long>(tag_r) * p.ldd + col) = data;
+            }
+          }
+          __syncwarp();
+        }
       } else {
         const long long col_base = static_cast<long long>(t.n_tile) * BN;
         const long long expert_off = SCHED == SCHED_WGRAD ? t.expert * p.d_expert_stride : 0;
@@ -397,20 +447,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const long long col = col_base + c;
           if (!row_ok || col >= p.N) continue;   // N is a multiple of 32 (checked on the host)
           const long long off = expert_off + row * p.ldd + col;
-          if (EPI == EPI_PUSH) {
-            const int tag = p.push_tag[row];
-            const int dest = p.push_src[row];
-            if (tag < 0 || dest < 0 || dest >= p.push_n) continue;       // padding row: nobody waits for it
-            const float w = p.push_w ? p.push_w[row] : 1.f;
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.push_dst.ptr[dest]) +
-                                                  static_cast<long long>(tag) * p.ldd + col);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              dst[i] = make_uint4(pack_bf16(w * __uint_as_float(v[8 * i]), w * __uint_as_float(v[8 * i + 1])),
-                                  pack_bf16(w * __uint_as_float(v[8 * i + 2]), w * __uint_as_float(v[8 * i + 3])),
-                                  pack_bf16(w * __uint_as_float(v[8 * i + 4]), w * __uint_as_float(v[8 * i + 5])),
-                                  pack_bf16(w * __uint_as_float(v[8 * i + 6]), w * __uint_as_float(v[8 * i + 7])));
-          } else if (EPI == EPI_ROPE) {
+          if (EPI == EPI_ROPE) {
             if (col < p.rope_cols) {
               // 32 consecutive columns of one head: pairs (2j, 2j+1), table entries [pos][(col mod 128)/2 + j]
               const size_t tab = static_cast<size_t>(row % p.rope_seq) * 64 + ((col & 127) >> 1);
@@ -526,11 +563,11 @@ static int launch_mt(const GemmParams& p, int sms, cudaStream_t stream) {
   auto kernel = gemm_tcgen05_kernel<A_MN, B_MN, EPI, SCHED, MT, 0>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MT>::SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<EPI, MT>()) != cudaSuccess)
       return -3;
     configured = true;
   }
-  kernel<<<sms, GEMM_THREADS, Cfg<MT>::SMEM, stream>>>(p);
+  kernel<<<sms, GEMM_THREADS, smem_bytes<EPI, MT>(), stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -544,13 +581,13 @@ static int pairs_resident(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, in
   attr->val.clusterDim.y = 1;
   attr->val.clusterDim.z = 1;
   cfg->blockDim = dim3(GEMM_THREADS);
-  cfg->dynamicSmemBytes = Cfg<1, 1>::SMEM;
+  cfg->dynamicSmemBytes = smem_bytes<EPI, 1, 1>();
   cfg->attrs = attr;
   cfg->numAttrs = 1;
   static int max_pairs = -1;
   if (max_pairs < 0) {
     max_pairs = 0;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1, 1>::SMEM) == cudaSuccess) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<EPI, 1, 1>()) == cudaSuccess) {
       int clusters = 0;
       cfg->gridDim = dim3(sms / 2 * 2);
       if (cudaOccupancyMaxActiveClusters(&clusters, kernel, cfg) == cudaSuccess) max_pairs = clusters;

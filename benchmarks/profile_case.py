@@ -8,7 +8,9 @@ two emulated ranks: the "peer" is a second buffer on this GPU and its ready sign
 launch waits for another), swiglu, moe_down, wgrad, rmsnorm, rmsnorm_bwd, cross_entropy, adamw, swiglu_bwd,
 attention_fwd, attention_bwd, sdpa, and the communication kernels with every peer pointer on this GPU: fsdp_step and
 allreduce (rank 0 of two emulated ranks, the peer's flags preset by the host), ep_gateup (gather + gate/up GEMM +
-SwiGLU over a one-rank expert group) and ep_down (down projection with the return in its epilogue).
+SwiGLU over a one-rank expert group), ep_down (down projection with the return in its epilogue), ep_dh (gather of
+the output gradient + dh GEMM) and ep_swiglu_bwd; gemm_rope (q/k/v projection with RoPE in its epilogue), router
+(skinny GEMM + softmax/top-2), embedding.
 """
 import argparse
 import os
@@ -51,6 +53,21 @@ def build(case):
             state["epoch"] += 1
             return native.ag_gemm_nt(x, w_ptrs, N, [N], world, 0, sig_ptrs, 14, state["epoch"], flags, state["epoch"])
         return launch, 2 * T * N * D
+    if case == "gemm_rope":
+        from b200moe.ops import functional as Fn
+        x, w = rnd(T, D), rnd(6144, D, scale=0.02)
+        cos, sin = Fn.rope_tables(10000.0, 128, 8192, device="cuda")
+        return lambda: native.gemm_nt_rope(x, w, cos, sin, 5120, 8192), 2 * T * 6144 * D
+    if case == "router":
+        x, w = rnd(4 * T, D), rnd(8, D, scale=0.02)
+
+        def route():
+            return native.router_top2_fwd(native.gemm_nt(x, w))
+        return route, 0
+    if case == "embedding":
+        ids = torch.randint(0, 32000, (4 * T,), device="cuda")
+        table = rnd(32000, D)
+        return lambda: native.embedding_fwd(ids, table), 0
     if case == "gemm_nn":
         dy, w = rnd(T, 6144), rnd(6144, D, scale=0.02)
         return lambda: native.gemm_nn(dy, w), 2 * T * 6144 * D
@@ -132,7 +149,7 @@ def build(case):
                          c.c_float(1e-4), c.c_int(1), c.c_int(0), c.c_void_p(counter.data_ptr()),
                          c.c_void_p(status.data_ptr()), c.c_void_p(torch.cuda.current_stream().cuda_stream))
         return launch, 0
-    if case in ("ep_gateup", "ep_down"):
+    if case in ("ep_gateup", "ep_down", "ep_dh", "ep_swiglu_bwd"):
         from b200moe import ops
         from b200moe.comm import ep as EP
         tokens, experts = 4096, 2
@@ -152,13 +169,27 @@ def build(case):
 
         def gateup():
             offs, seg_end, tile_expert, meta, seq = epc.plan(idx, weights, "profile")
-            state.update(tile_expert=tile_expert, meta=meta)
+            state.update(tile_expert=tile_expert, meta=meta, seg_end=seg_end)
             epc.gather_gemm(0, x_ws, w1, w3, 2 * Fd, D, tile_expert, meta, seg_end, 0, epc.pool[slot].table(), 1,
                             epc.land_src.tensor, epc.land_tag.tensor, epc.land_w.tensor, (row_src, row_tag, row_w),
                             EP.SIG_META, seq, 1, h, None, None, None, None, 0)
         if case == "ep_gateup":
             return gateup, 2 * 2 * tokens * 2 * Fd * D
         gateup()
+        if case == "ep_dh":
+            epc.dout.tensor.view(tokens, D).copy_(rnd(tokens, D))
+            dy_ws = epc.ws("dy", D)
+
+            def dh():
+                seq = epc.g.next_seq(EP.SIG_BDATA)
+                epc.gather_gemm(1, dy_ws, w2, None, Fd, D, state["tile_expert"], state["meta"], state["seg_end"], 0,
+                                epc.dout.table(), 1, row_src, row_tag, None, None, EP.SIG_BDATA, seq, 2, h, None,
+                                None, None, None, 0)
+            return dh, 2 * 2 * tokens * D * Fd
+        if case == "ep_swiglu_bwd":
+            gate, up, dgu = rnd(epc.cap, Fd), rnd(epc.cap, Fd), epc.ws("dgu", 2 * Fd)
+            return (lambda: native.ep_swiglu_bwd(h, gate, up, None, None, epc.cap, dgu, state["meta"], row_tag,
+                                                 row_src, row_w, epc.dw_ret.table(), 1)), 0
 
         def down():
             seq = epc.g.next_seq(EP.SIG_RET_F)

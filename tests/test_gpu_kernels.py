@@ -311,7 +311,7 @@ def test_moe_block_matches_torch_path(native, recompute):
 
 
 @pytest.mark.parametrize("keep_rows,recompute", [(None, False), (512, False), (None, True)])
-def test_moe_block_with_fused_exchange_on_a_single_rank_group(native, keep_rows, recompute):
+def test_moe_block_with_fused_exchange_on_a_single_rank_group(native, tile_mode, keep_rows, recompute):
     """The gather+GEMM kernels, the return in the GEMM epilogue and the combine kernel with every pointer local
     (expert group of one rank), against the PyTorch statements of the block."""
     from b200moe import ops
