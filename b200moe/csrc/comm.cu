@@ -177,10 +177,79 @@ __device__ __forceinline__ float adamw_one(const FsdpArgs& a, float p, float g, 
   return p - a.a_t * m / (sqrtf(v) + a.eps);
 }
 
+// One entry of the flat buffers, 16 bytes at a time.  Unit of work: one float4.  Consecutive lanes take
+// consecutive units, so every warp-wide load is 512 contiguous bytes (whole sectors over NVLink) and every bf16 store
+// 256.  A thread handles UNITS units per iteration, a grid apart, and issues all their loads (NR ranks' gradients,
+// master, both moments) before the first use: remote loads take several times as long as local ones, and the bytes
+// in flight per SM are what bounds the kernel.  NR: ranks the registers are laid out for (>= a.n).
+template <int NR, int UNITS>
+__device__ __noinline__ void fsdp_vector_entry(const FsdpArgs& a, const FsdpEntry& ent, long long full_base,
+                                                  bool everyone, float inv, long long tid, long long nthreads) {
+  const long long units = ent.shard_numel / 4;
+  for (long long u0 = tid; u0 < units; u0 += UNITS * nthreads) {
+    float4 gr[UNITS][NR], pv[UNITS], mv[UNITS], vv[UNITS];
+#pragma unroll
+    for (int k = 0; k < UNITS; ++k) {
+      const long long u = u0 + k * nthreads;
+      if (u < units) {
+        const long long i = u * 4;
+        if (a.do_reduce) {
+#pragma unroll
+          for (int p = 0; p < NR; ++p)
+            if (p < a.n)
+              gr[k][p] = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(a.full_g.ptr[p]) + full_base + i));
+        } else {
+          gr[k][0] = *reinterpret_cast<const float4*>(a.shard_grad + ent.shard_off + i);
+        }
+        if (a.do_update) {
+          pv[k] = *reinterpret_cast<const float4*>(a.master + ent.shard_off + i);
+          mv[k] = *reinterpret_cast<const float4*>(a.m + ent.shard_off + i);
+          vv[k] = *reinterpret_cast<const float4*>(a.v + ent.shard_off + i);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < UNITS; ++k) {
+      const long long u = u0 + k * nthreads;
+      if (u >= units) continue;
+      const long long i = u * 4;
+      const long long si = ent.shard_off + i;
+      float4 g = gr[k][0];
+      if (a.do_reduce) {
+#pragma unroll
+        for (int p = 1; p < NR; ++p)
+          if (p < a.n) {
+            g.x += gr[k][p].x; g.y += gr[k][p].y; g.z += gr[k][p].z; g.w += gr[k][p].w;
+          }
+        g.x *= inv; g.y *= inv; g.z *= inv; g.w *= inv;
+        *reinterpret_cast<float4*>(a.shard_grad + si) = g;
+      }
+      if (a.do_update) {
+        float4 pn;
+        pn.x = adamw_one(a, pv[k].x, g.x, mv[k].x, vv[k].x);
+        pn.y = adamw_one(a, pv[k].y, g.y, mv[k].y, vv[k].y);
+        pn.z = adamw_one(a, pv[k].z, g.z, mv[k].z, vv[k].z);
+        pn.w = adamw_one(a, pv[k].w, g.w, mv[k].w, vv[k].w);
+        *reinterpret_cast<float4*>(a.master + si) = pn;
+        *reinterpret_cast<float4*>(a.m + si) = mv[k];
+        *reinterpret_cast<float4*>(a.v + si) = vv[k];
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(pn.x, pn.y), hi = __floats2bfloat162_rn(pn.z, pn.w);
+        const uint2 w = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        if (everyone) {
+          for (int p = 0; p < a.n; ++p)
+            *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(a.full_w.ptr[p]) + full_base + i) = w;
+        } else {
+          *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(a.full_w.ptr[a.rank]) + full_base + i) = w;
+        }
+      }
+    }
+  }
+}
+
 // Gradients cross NVLink as 16-byte fp32 vectors (peer loads), new weights as 8-byte vectors of four bf16 (peer
 // stores), both lane-contiguous; entries whose offsets or sizes are not multiples of eight elements take the scalar
 // loop.
-__global__ void __launch_bounds__(512) fsdp_step_kernel(const FsdpArgs a) {
+__global__ void __launch_bounds__(512, 1) fsdp_step_kernel(const FsdpArgs a) {
   ArArgs bar{};
   bar.sig = a.sig; bar.rank = a.rank; bar.n = a.n; bar.seq = a.seq; bar.counter = a.counter; bar.status = a.status;
   // every rank has finished accumulating its gradients; if one never says so, this rank neither reduces nor
@@ -197,68 +266,9 @@ __global__ void __launch_bounds__(512) fsdp_step_kernel(const FsdpArgs a) {
     const long long full_base = ent.full_off + ent.shard_numel * a.rank;
     const bool everyone = !(ent.local_only && !a.push_all);
     if (((full_base | ent.shard_off | ent.shard_numel) & 7) == 0) {
-      // Unit of work: one float4.  Consecutive lanes take consecutive units, so every warp-wide load is 512
-      // contiguous bytes (whole sectors over NVLink) and every bf16 store 256; each thread handles two units per
-      // iteration, a grid apart, and issues all their loads (peers' gradients, master, both moments) before the
-      // first use.
-      const long long units = ent.shard_numel / 4;
-      for (long long u0 = tid; u0 < units; u0 += 2 * nthreads) {
-        const long long u1 = u0 + nthreads;
-        const bool two = u1 < units;
-        float4 gr[2][MAX_RANKS], pv[2], mv[2], vv[2];
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          if (k == 1 && !two) break;
-          const long long i = (k ? u1 : u0) * 4;
-          if (a.do_reduce) {
-#pragma unroll
-            for (int p = 0; p < MAX_RANKS; ++p)
-              if (p < a.n)
-                gr[k][p] = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(a.full_g.ptr[p]) + full_base + i));
-          } else {
-            gr[k][0] = *reinterpret_cast<const float4*>(a.shard_grad + ent.shard_off + i);
-          }
-          if (a.do_update) {
-            pv[k] = *reinterpret_cast<const float4*>(a.master + ent.shard_off + i);
-            mv[k] = *reinterpret_cast<const float4*>(a.m + ent.shard_off + i);
-            vv[k] = *reinterpret_cast<const float4*>(a.v + ent.shard_off + i);
-          }
-        }
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          if (k == 1 && !two) break;
-          const long long i = (k ? u1 : u0) * 4;
-          const long long si = ent.shard_off + i;
-          float4 g = gr[k][0];
-          if (a.do_reduce) {
-#pragma unroll
-            for (int p = 1; p < MAX_RANKS; ++p)
-              if (p < a.n) {
-                g.x += gr[k][p].x; g.y += gr[k][p].y; g.z += gr[k][p].z; g.w += gr[k][p].w;
-              }
-            g.x *= inv; g.y *= inv; g.z *= inv; g.w *= inv;
-            *reinterpret_cast<float4*>(a.shard_grad + si) = g;
-          }
-          if (a.do_update) {
-            float4 pn;
-            pn.x = adamw_one(a, pv[k].x, g.x, mv[k].x, vv[k].x);
-            pn.y = adamw_one(a, pv[k].y, g.y, mv[k].y, vv[k].y);
-            pn.z = adamw_one(a, pv[k].z, g.z, mv[k].z, vv[k].z);
-            pn.w = adamw_one(a, pv[k].w, g.w, mv[k].w, vv[k].w);
-            *reinterpret_cast<float4*>(a.master + si) = pn;
-            *reinterpret_cast<float4*>(a.m + si) = mv[k];
-            *reinterpret_cast<float4*>(a.v + si) = vv[k];
-            const __nv_bfloat162 lo = __floats2bfloat162_rn(pn.x, pn.y), hi = __floats2bfloat162_rn(pn.z, pn.w);
-            const uint2 w = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
-            if (everyone) {
-              for (int p = 0; p < a.n; ++p)
-                *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(a.full_w.ptr[p]) + full_base + i) = w;
-            } else {
-              *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(a.full_w.ptr[a.rank]) + full_base + i) = w;
-            }
-          }
-        }
-      }
+      if (a.n <= 2) fsdp_vector_entry<2, 3>(a, ent, full_base, everyone, inv, tid, nthreads);
+      else if (a.n <= 4) fsdp_vector_entry<4, 2>(a, ent, full_base, everyone, inv, tid, nthreads);
+      else fsdp_vector_entry<MAX_RANKS, 1>(a, ent, full_base, everyone, inv, tid, nthreads);
       continue;
     }
     for (long long i = tid; i < ent.shard_numel; i += nthreads) {

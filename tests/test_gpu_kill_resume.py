@@ -39,11 +39,14 @@ def _config(folder, kill):
 
 
 def _launch(config_path, port, restarts):
-    env = {**os.environ, "NCCL_NVLS_ENABLE": "0"}
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-           f"--max-restarts={restarts}", "--monitor-interval=1", "--master-addr=127.0.0.1",
-           f"--master-port={port}", os.path.join(ROOT, "distributed_parallel_training_pipelined.py"),
-           "--config-path", str(config_path)]
+    # --standalone: a fresh rendezvous (and a fresh store prefix) for every attempt, so the restarted workers do not
+    # pick up the first attempt's NCCL bootstrap address; loopback for the rendezvous and for NCCL's bootstrap
+    env = {**os.environ, "NCCL_NVLS_ENABLE": "0", "NCCL_SOCKET_IFNAME": "lo"}
+    for key in ("MASTER_ADDR", "MASTER_PORT", "RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(key, None)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr=127.0.0.1", "--nnodes=1",
+           "--nproc-per-node=2", f"--max-restarts={restarts}", "--monitor-interval=1",
+           os.path.join(ROOT, "distributed_parallel_training_pipelined.py"), "--config-path", str(config_path)]
     return subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
 
 
