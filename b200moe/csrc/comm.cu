@@ -183,7 +183,7 @@ __device__ __forceinline__ float adamw_one(const FsdpArgs& a, float p, float g, 
 // master, both moments) before the first use: remote loads take several times as long as local ones, and the bytes
 // in flight per SM are what bounds the kernel.  NR: ranks the registers are laid out for (>= a.n).
 template <int NR, int UNITS>
-__device__ __noinline__ void fsdp_vector_entry(const FsdpArgs& a, const FsdpEntry& ent, long long full_base,
+__device__ __forceinline__ void fsdp_vector_entry(const FsdpArgs& a, const FsdpEntry& ent, long long full_base,
                                                   bool everyone, float inv, long long tid, long long nthreads) {
   const long long units = ent.shard_numel / 4;
   for (long long u0 = tid; u0 < units; u0 += UNITS * nthreads) {
@@ -249,7 +249,10 @@ __device__ __noinline__ void fsdp_vector_entry(const FsdpArgs& a, const FsdpEntr
 // Gradients cross NVLink as 16-byte fp32 vectors (peer loads), new weights as 8-byte vectors of four bf16 (peer
 // stores), both lane-contiguous; entries whose offsets or sizes are not multiples of eight elements take the scalar
 // loop.
-__global__ void __launch_bounds__(512, 1) fsdp_step_kernel(const FsdpArgs a) {
+// NR: ranks the registers are laid out for (2, 4 or MAX_RANKS, >= a.n).  With two ranks the state of two units fits
+// 64 registers, so two CTAs share an SM and twice as many loads are in flight.
+template <int NR>
+__global__ void __launch_bounds__(512, NR <= 2 ? 2 : 1) fsdp_step_kernel(const FsdpArgs a) {
   ArArgs bar{};
   bar.sig = a.sig; bar.rank = a.rank; bar.n = a.n; bar.seq = a.seq; bar.counter = a.counter; bar.status = a.status;
   // every rank has finished accumulating its gradients; if one never says so, this rank neither reduces nor
@@ -266,9 +269,7 @@ __global__ void __launch_bounds__(512, 1) fsdp_step_kernel(const FsdpArgs a) {
     const long long full_base = ent.full_off + ent.shard_numel * a.rank;
     const bool everyone = !(ent.local_only && !a.push_all);
     if (((full_base | ent.shard_off | ent.shard_numel) & 7) == 0) {
-      if (a.n <= 2) fsdp_vector_entry<2, 3>(a, ent, full_base, everyone, inv, tid, nthreads);
-      else if (a.n <= 4) fsdp_vector_entry<4, 2>(a, ent, full_base, everyone, inv, tid, nthreads);
-      else fsdp_vector_entry<MAX_RANKS, 1>(a, ent, full_base, everyone, inv, tid, nthreads);
+      fsdp_vector_entry<NR, 2>(a, ent, full_base, everyone, inv, tid, nthreads);
       continue;
     }
     for (long long i = tid; i < ent.shard_numel; i += nthreads) {
@@ -417,7 +418,9 @@ int b2_fsdp_step(const unsigned long long* full_g, const unsigned long long* ful
   a.do_update = mode == 1 || mode == 2;
   a.push_all = push_all;
   if (mode == 3) fsdp_allgather_kernel<<<device_sms() * 2, 512, 0, s>>>(a);
-  else fsdp_step_kernel<<<device_sms() * 2, 512, 0, s>>>(a);
+  else if (n <= 2) fsdp_step_kernel<2><<<device_sms() * 2, 512, 0, s>>>(a);
+  else if (n <= 4) fsdp_step_kernel<4><<<device_sms() * 2, 512, 0, s>>>(a);
+  else fsdp_step_kernel<MAX_RANKS><<<device_sms() * 2, 512, 0, s>>>(a);
   return launched();
 }
 
