@@ -49,6 +49,23 @@ def resolve_device(config: dict, local_rank: int) -> torch.device:
     return torch.device("cpu")
 
 
+def init_process_group(backend: str, rank: int, world_size: int, timeout, device=None) -> None:
+    """``dist.init_process_group`` from the torchrun environment.  After an elastic restart the workers talk to the
+    same agent-hosted store as the attempt before, which still holds that attempt's keys (for NCCL: the bootstrap
+    address of a process that no longer exists), and a rank that reads before rank 0 has overwritten them connects
+    to nobody.  Restarted attempts therefore rendezvous under a key prefix of their own."""
+    extra = {"device_id": device} if device is not None else {}
+    restart = int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0") or 0)
+    if restart > 0 and os.environ.get("TORCHELASTIC_USE_AGENT_STORE") == "True":
+        base = dist.TCPStore(os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]), world_size, is_master=False,
+                             timeout=timeout)
+        store = dist.PrefixStore(f"/b200moe/attempt_{restart}", base)
+        dist.init_process_group(backend, store=store, rank=rank, world_size=world_size, timeout=timeout, **extra)
+    else:
+        dist.init_process_group(backend, init_method="env://", rank=rank, world_size=world_size, timeout=timeout,
+                                **extra)
+
+
 def build_model(config: dict, mesh, device, fsdp_group, ddp_group, compute_dtype, comm=None):
     """Stage model + sharding wrapper + optimizer from a run configuration."""
     model_cfg, train_cfg, data_cfg = config["model"], config["train"], config["data"]
@@ -122,12 +139,11 @@ def train(local_rank: int, cluster_rank: int, world_size: int, config: dict):
     device = resolve_device(config, local_rank)
     timeout = timedelta(seconds=config.get("recovery", {}).get("collective_timeout_seconds", 180))
     if device.type == "cuda":
-        dist.init_process_group("nccl", init_method="env://", rank=rank, world_size=world_size,
-                                device_id=device, timeout=timeout)
+        init_process_group("nccl", rank, world_size, timeout, device)
         torch.backends.cuda.matmul.allow_tf32 = True
         torch.backends.cudnn.allow_tf32 = True
     else:
-        dist.init_process_group("gloo", init_method="env://", rank=rank, world_size=world_size, timeout=timeout)
+        init_process_group("gloo", rank, world_size, timeout)
     compute_dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
 
     mesh = build_groups(train_cfg, rank, world_size, general["gpu_per_node"], timeout=timeout)
