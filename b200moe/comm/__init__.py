@@ -161,6 +161,11 @@ class Comm:
         self._ep.clear()
         self.fsdp = self.ddp = None
 
+    def new_step(self) -> None:
+        """Called by the sharding wrapper at the start of every training step."""
+        for ctx in self._ep.values():
+            ctx.new_step()
+
     # -- allocation ----------------------------------------------------------------------
     def alloc_flat(self, numel: int, dtype):
         """Symmetric, zero-filled flat buffer over the FSDP group (plain memory

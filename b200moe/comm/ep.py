@@ -166,6 +166,11 @@ class EPPull:
     def release(self, slot: int) -> None:
         self.free.append(slot)
 
+    def new_step(self) -> None:
+        """Start of a training step: no call of the previous step is alive, so every slot is free again (a step that
+        ended in an exception never ran the backward passes that give slots back).  Same order on every rank."""
+        self.free = list(range(len(self.pool) - 1, -1, -1))
+
     def slot_tensor(self, slot: int) -> torch.Tensor:
         return self.pool[slot].tensor.view(self.tokens, self.dim)
 

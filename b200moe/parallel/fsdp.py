@@ -316,6 +316,8 @@ class FSDPWrapperPipelined(nn.Module):
         budget = getattr(self, "activation_budget", None)
         if budget is not None:
             budget.reset()      # start of a step: no activation of the previous one is alive
+        if self.comm is not None and getattr(self, "fused", False):
+            self.comm.new_step()
         self.flat.full_g.zero_()
         for p in self.sharded_params + self.replicated_params:
             p.grad = None
