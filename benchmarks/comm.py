@@ -75,7 +75,8 @@ def main():
     # ---- expert parallel over all ranks
     mesh = build_groups({"fsdp_parallel_num": world, "data_parallel_num": 1, "pipeline_parallel_stages": 1},
                         rank, world, world)
-    comm = make_comm(mesh, device, wait_seconds=5.0)
+    # the NVLS all-reduce needs buffers bound to a multicast address, and the binding is decided at the first rendezvous
+    comm = make_comm(mesh, device, wait_seconds=5.0, multicast=want("allreduce"))
     group = mesh.group("fsdp")
     T, D, Fd, E = args.tokens, 4096, 14336, 8
     e_local = E // world
@@ -230,7 +231,7 @@ def main():
         # ---- replica all-reduce over all ranks
         mesh2 = build_groups({"fsdp_parallel_num": 1, "data_parallel_num": world, "pipeline_parallel_stages": 1},
                              rank, world, world)
-        comm2 = make_comm(mesh2, device)
+        comm2 = make_comm(mesh2, device, multicast=True)
         for n in (1 << 12, 1 << 18, 1 << 22, 1 << 26):
             buf = torch.randn(n, device=device)
             for kind in ("oneshot", "twoshot", "nvls"):

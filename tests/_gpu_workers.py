@@ -46,7 +46,8 @@ def _allreduce(rank, world, port, out_dir):
     device = _setup(rank, world, port)
     mesh = build_groups({"fsdp_parallel_num": 1, "data_parallel_num": world, "pipeline_parallel_stages": 1},
                         rank, world, world)
-    comm = make_comm(mesh, device)
+    # the in-switch reduction needs the staging buffer bound to a multicast address (off by default elsewhere)
+    comm = make_comm(mesh, device, multicast=True)
     kinds = ["oneshot", "twoshot"] + (["nvls"] if comm.ddp is not None else [])
     for n in (1000, 262144, 5_000_000):
         for kind in kinds:
