@@ -64,6 +64,8 @@ def parse_args():
     p.add_argument("--seq", type=int, default=MODEL["seq"])
     p.add_argument("--recompute", default=None, choices=["none", "swiglu", "block"])
     p.add_argument("--backend", default=None, choices=["fused", "nccl"])
+    p.add_argument("--no-e2e", action="store_true",
+                   help="accepted for older command lines: both numbers now come from the one timed pass")
     p.add_argument("--layout", default=None, choices=sorted(NAMED), help="a named 8-GPU configuration")
     p.add_argument("--kernel-times", default=None, metavar="FILE",
                    help="after the measurement, run one more step with a CUDA-event pair around every launch of this "
