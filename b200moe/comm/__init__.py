@@ -16,7 +16,10 @@ and write those buffers through peer pointers:
   per-microbatch all-gathers, implementation/distributed/ddp_modules.py:24-100,
   219-292);
 * ``Comm.allreduce_avg``: replica all-reduce, one-shot / two-shot / NVLS chosen
-  by message size (replaces ddp_modules.py:274-287).
+  by message size (replaces ddp_modules.py:274-287);
+* ``Comm.pp_link`` → ``comm.pp.PeerLink``: the pipeline's stage-to-stage transfers
+  as peer stores into landing rings (replaces the blocking batched send/recv of
+  pipeline/pipelined_train_overlap.py:40-75).
 
 Sequence numbers: every synchronising phase owns a signal slot and a counter
 that all ranks of the group advance in the same order.
@@ -103,8 +106,12 @@ class GroupComm:
 
 
 class Comm:
-    def __init__(self, mesh, device, multicast: bool = False, wait_seconds: float | None = None):
-        """``multicast``: let the symmetric-memory rendezvous bind buffers to an NVSwitch multicast address (only
+    def __init__(self, mesh, device, multicast: bool = False, wait_seconds: float | None = None,
+                 pipeline_link: str | None = None, pipeline_wait_seconds: float = 120.0):
+        """``pipeline_link``: ``"peer"`` moves the pipeline's activations and gradients with this library's
+        peer-store kernels (``pp_link``), ``"nccl"`` with batched NCCL send/recv; ``None`` reads
+        ``B200MOE_PIPELINE_LINK`` and defaults to ``"nccl"``.  ``pipeline_wait_seconds``: budget of a pipeline wait
+        (they span whole stage steps, so it is longer than ``wait_seconds``).  ``multicast``: let the symmetric-memory rendezvous bind buffers to an NVSwitch multicast address (only
         the NVLS all-reduce uses it).  Off by default: a process that dies while bound raises NVLink faults on the
         other ranks' GPUs, and nothing else here needs the binding.  ``wait_seconds``: budget of every cross-GPU
         wait inside the kernels (``native.set_wait_seconds``)."""
@@ -124,6 +131,12 @@ class Comm:
         self.ddp = GroupComm(mesh.group("ddp"), device) if mesh.ddp > 1 else None
         skew = os.environ.get("B200MOE_EP_MAX_SKEW")
         self.ep_max_skew = float(skew) if skew else None
+        chosen = pipeline_link or os.environ.get("B200MOE_PIPELINE_LINK") or "nccl"
+        if chosen not in ("peer", "nccl"):
+            raise ValueError(f"pipeline_link must be 'peer' or 'nccl', got {chosen!r}")
+        self.pipeline_link = chosen
+        self.pipeline_wait_seconds = float(os.environ.get("B200MOE_PIPELINE_WAIT_SECONDS") or pipeline_wait_seconds)
+        self._pp = {}
         self._symm = {}
         self._ep = {}
         self._ar_stage = {}
@@ -139,6 +152,9 @@ class Comm:
                 found.append(g.sig)
         for ctx in self._ep.values():
             found.extend(ctx.buffers())
+        for link in self._pp.values():
+            if link is not None:
+                found.extend(link.buffers())
         return found
 
     def any_multicast(self) -> bool:
@@ -159,6 +175,7 @@ class Comm:
         self._symm.clear()
         self._ar_stage.clear()
         self._ep.clear()
+        self._pp.clear()
         self.fsdp = self.ddp = None
 
     def new_step(self) -> None:
@@ -308,6 +325,30 @@ class Comm:
                 flat[lo:lo + n].copy_(stage.tensor[:n])
         return tensor
 
+    # -- pipeline ---------------------------------------------------------------------------
+    def pp_link(self, group, stage: int, spec, dtype):
+        """The peer-memory link of this stage for microbatches of shape ``spec`` (collective over ``group`` at
+        first use), or ``None`` when the pipeline is to use NCCL: ``pipeline_link="nccl"``, a payload that is not
+        a whole number of 16-byte units, or stages that do not all sit on this host (peer memory is an NVLink
+        domain)."""
+        if self.pipeline_link != "peer" or group is None or dtype is None:
+            return None
+        key = (id(group), tuple(spec), dtype)
+        if key not in self._pp:
+            from .pp import PeerLink
+            import math
+            import socket
+            stages = dist.get_world_size(group)
+            hosts = [None] * stages
+            dist.all_gather_object(hosts, socket.gethostname(), group=group)
+            usable = (stages <= MAX_RANKS and len(set(hosts)) == 1 and dist.get_rank(group) == stage
+                      and (math.prod(spec) * dtype.itemsize) % 16 == 0)
+            votes = [None] * stages
+            dist.all_gather_object(votes, bool(usable), group=group)
+            self._pp[key] = PeerLink.over_group(group, self.device, self.status, spec, dtype,
+                                                self.pipeline_wait_seconds) if all(votes) else None
+        return self._pp[key]
+
     # -- expert parallel --------------------------------------------------------------------
     def ep_context(self, tokens: int, dim: int, experts_total: int, ffn: int):
         """The expert-exchange state (``comm.ep.EPPull``) for one problem size, created at first use."""
@@ -323,5 +364,7 @@ class Comm:
         return ctx
 
 
-def make_comm(mesh, device, multicast: bool = False, wait_seconds: float | None = None) -> Comm:
-    return Comm(mesh, device, multicast=multicast, wait_seconds=wait_seconds)
+def make_comm(mesh, device, multicast: bool = False, wait_seconds: float | None = None,
+              pipeline_link: str | None = None, pipeline_wait_seconds: float = 120.0) -> Comm:
+    return Comm(mesh, device, multicast=multicast, wait_seconds=wait_seconds, pipeline_link=pipeline_link,
+                pipeline_wait_seconds=pipeline_wait_seconds)

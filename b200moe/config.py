@@ -13,6 +13,9 @@ are optional and default to the reference's behaviour:
 ``train.expert_state_dtype``    ``float32`` | ``bfloat16`` AdamW m/v of experts
 ``train.expert_grad_dtype``     ``float32`` | ``bfloat16`` expert grad accumulators
 ``comm.backend``                ``fused`` (peer-memory kernels) | ``nccl``
+``comm.pipeline_link``          ``peer``: a stage stores its activations and gradients into landing rings of
+                                its neighbour (no rendezvous of the two stages) | ``nccl``: batched send/recv
+``recovery.pipeline_wait_seconds``  budget of a stage's wait for its neighbour inside the peer link (default 120)
 ``train.fsdp_gather``           ``step``: the end-of-step kernel pushes every new weight to the peers;
                                 ``first_use``: the attention projections are gathered by the first GEMM
                                 that uses them (all-gather and GEMM in one kernel)
@@ -123,6 +126,8 @@ def validate_config(config: dict, *, check_data: bool = False, check_cuda: bool 
         raise ValueError("train.fsdp_gather must be step or first_use")
     if (config.get("comm") or {}).get("backend", "fused") not in ("fused", "nccl"):
         raise ValueError("comm.backend must be fused or nccl")
+    if (config.get("comm") or {}).get("pipeline_link") not in (None, "peer", "nccl"):
+        raise ValueError("comm.pipeline_link must be peer or nccl")
     if check_data:
         from .utils.data import load_dataset
         tokens = load_dataset(data["train_dataset_path"], vocab_size=data["vocab_size"], validate=True)

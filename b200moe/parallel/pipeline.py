@@ -8,10 +8,16 @@ neighbour exchange is one batched send+recv; the loss of a microbatch is divided
 by the microbatch count; the value returned is the mean loss on the last stage
 and ``0.0`` elsewhere (or a metrics dict).
 
-Differences in mechanism: the host never blocks on a transfer (with NCCL,
-``work.wait()`` orders the compute stream after the exchange, it does not stop
-the host), so the host runs ahead of the device; the exchange itself is ordered
-on the compute stream like the reference's, it is not overlapped with compute.
+Differences in mechanism: the host never blocks on a transfer, so it runs ahead
+of the device.  There are two kinds of link between stages.  The NCCL link is the
+reference's batched ``isend``/``irecv`` (``work.wait()`` orders the compute stream
+after the exchange; a send completes when the neighbour has reached its matching
+receive, which keeps the stages in lock step).  The peer link
+(``comm.pp.PeerLink``, chosen by the wrapper's ``Comm``) stores the payload into
+a landing ring of the neighbour and publishes a message number: a send never
+waits for the neighbour unless its ring is full, a receive is a bounded wait on
+the stream followed by reads of the slot in place, and a slot is handed back
+after the backward pass of its microbatch (``consumed``).
 On the last stage the loss comes from the chunked LM-head/cross-entropy op when
 the model offers ``loss()`` and the caller passed this framework's
 ``cross_entropy``; after ``optimizer.step()`` the wrapper refreshes its gathered
@@ -72,6 +78,20 @@ class _Link:
             work.wait()
         return received
 
+    def consumed(self):
+        """Nothing to hand back: every received tensor is its own allocation."""
+
+
+def _make_link(model, ranks, stage, pp_group, spec, dtype, device):
+    """The peer-memory link when the wrapper's communication layer offers one for this group, else NCCL."""
+    comm = getattr(model, "comm", None)
+    offer = getattr(comm, "pp_link", None)
+    if offer is not None and pp_group is not None and len(ranks) > 1:
+        link = offer(pp_group, stage, spec, dtype)
+        if link is not None:
+            return link
+    return _Link(ranks, stage, pp_group, spec, dtype, device)
+
 
 def _uses_fused_loss(model, loss_fn):
     target = getattr(model, "module", model)
@@ -92,7 +112,7 @@ def pipelined_train_overlap(model, optimizer, x, x_label, x_spec: list[int], spl
     first, last = pipeline_stage_this == 0, pipeline_stage_this == stages - 1
     ranks = dist.get_process_group_ranks(pp_group) if pp_group is not None else []
     mb_size = x_spec[0] // split_num
-    link = _Link(ranks, pipeline_stage_this, pp_group, [mb_size, *x_spec[1:]], dtype, device)
+    link = _make_link(model, ranks, pipeline_stage_this, pp_group, [mb_size, *x_spec[1:]], dtype, device)
     data_chunks = torch.split(x, mb_size) if first else None
     label_chunks = torch.split(x_label, mb_size) if last else None
     fused_loss = last and _uses_fused_loss(model, loss_fn)
@@ -150,6 +170,7 @@ def pipelined_train_overlap(model, optimizer, x, x_label, x_spec: list[int], spl
         else:
             backward_with_router_loss(out, grad, aux, router_aux_loss_coef, split_num)
         model.accumulate_full_gradients()
+        link.consumed()
         return None if first else x_in.grad
 
     warmup = min(stages - pipeline_stage_this - 1, split_num)

@@ -160,8 +160,11 @@ def train(local_rank: int, cluster_rank: int, world_size: int, config: dict):
         from .comm import make_comm
         # comm.multicast (default off): bind the symmetric buffers to an NVSwitch multicast address, which the NVLS
         # all-reduce needs.  A process must not die while bound, so self-kill fault injection is refused with it.
+        # comm.pipeline_link: "peer" (landing rings in peer memory, comm/pp.py) or "nccl" (batched send/recv)
         comm = make_comm(mesh, device, multicast=bool(comm_cfg.get("multicast", False)),
-                         wait_seconds=float(recovery.get("device_wait_seconds", 20.0)))
+                         wait_seconds=float(recovery.get("device_wait_seconds", 20.0)),
+                         pipeline_link=comm_cfg.get("pipeline_link"),
+                         pipeline_wait_seconds=float(recovery.get("pipeline_wait_seconds", 120.0)))
     model, optimizer = build_model(config, mesh, device, fsdp_group, ddp_group, compute_dtype, comm)
 
     run_id = datetime.now().strftime("%Y%m%d%H%M%S%f")

@@ -47,7 +47,9 @@ BASELINE_TOKENS_PER_S = 75076.0
 MODEL = {"d_model": 4096, "d_ff": 14336, "num_head": 32, "experts": 8, "vocab": 32000, "seq": 8192}
 LAYOUT = {1: (1, 1, 8, 64), 2: (1, 2, 8, 128), 4: (2, 2, 8, 128), 8: (4, 2, 8, 128)}  # pp, fsdp, blocks/stage, batch
 # other named configurations: pp, fsdp, ddp, blocks/stage, global batch, microbatches, rope base
-NAMED = {"ddp2": (1, 4, 2, 8, 32, 4, 1e6), "pp2": (2, 4, 1, 16, 64, 16, 1e4)}
+NAMED = {"ddp2": (1, 4, 2, 8, 32, 4, 1e6), "pp2": (2, 4, 1, 16, 64, 16, 1e4),
+         # two stages of the one-GPU workload on two GPUs (16 blocks): isolates what the pipeline itself costs
+         "pp2x1": (2, 1, 1, 8, 64, 32, 1e4)}
 SCHEDULE = {"a_max": 0.01, "a_min": 0.0001, "t_w": 5000, "t_c": 20000}     # the reference's run_config.yaml
 
 
@@ -66,7 +68,10 @@ def parse_args():
     p.add_argument("--backend", default=None, choices=["fused", "nccl"])
     p.add_argument("--no-e2e", action="store_true",
                    help="accepted for older command lines: both numbers now come from the one timed pass")
-    p.add_argument("--layout", default=None, choices=sorted(NAMED), help="a named 8-GPU configuration")
+    p.add_argument("--layout", default=None, choices=sorted(NAMED), help="a named configuration (see NAMED)")
+    p.add_argument("--pipeline-link", default=None, choices=["peer", "nccl"],
+                   help="stage-to-stage transfers: this library's peer-store kernels or batched NCCL send/recv "
+                        "(default: the library's default)")
     p.add_argument("--kernel-times", default=None, metavar="FILE",
                    help="after the measurement, run one more step with a CUDA-event pair around every launch of this "
                         "library and write rank 0's per-kernel totals to FILE (JSON)")
@@ -297,7 +302,7 @@ def bench_b200moe(args):
         comm = None
         if config["comm"]["backend"] == "fused" and native.has("comm"):
             from b200moe.comm import make_comm
-            comm = make_comm(mesh, device)
+            comm = make_comm(mesh, device, pipeline_link=args.pipeline_link)
         state["comm"] = comm
         torch.manual_seed(1234 + mesh.stage)
         model, optimizer = build_model(config, mesh, device, mesh.group("fsdp"), mesh.group("ddp"), torch.bfloat16,
@@ -356,6 +361,8 @@ def bench_b200moe(args):
                                "moe_calls_kept_gate_up": int(kept[0]), "moe_calls_rebuilt_gate_up": int(kept[1]),
                                "ep_max_rows_over_balanced": round(float(load), 3),
                                "comm_backend": "fused" if comm is not None else "nccl",
+                               "pipeline_link": ("none" if mesh.pp == 1 else
+                                                 "nccl" if comm is None or not any(comm._pp.values()) else "peer"),
                                "native_ops": native.available_ops()})
         dist.destroy_process_group()
     except Exception as error:

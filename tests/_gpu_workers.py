@@ -219,6 +219,63 @@ def _train_parity(rank, world, port, out_dir, pp, ddp=1, skew=False):
     native.check_status()
 
 
+def _pipeline_link(rank, world, port, out_dir):
+    """``world`` pipeline stages, eight microbatches per step: the peer-memory link (landing rings in symmetric
+    memory, peer stores, message numbers) against the batched NCCL send/recv.  Same kernels and same data on both
+    sides, so losses and weights must agree to rounding of the atomics in the embedding gradient."""
+    import torch
+    from b200moe.comm import make_comm
+    from b200moe.comm.pp import PeerLink
+    from b200moe.ops import native
+    from b200moe.ops.functional import cross_entropy
+    from b200moe.parallel import pipelined_train_overlap
+    from b200moe.topology import build_groups
+    from b200moe.trainer import build_model
+    device = _setup(rank, world, port)
+    config = {
+        "general": {"device": "gpu"}, "data": {"vocab_size": 2048}, "comm": {"backend": "fused"},
+        "model": {"num_head": 4, "d_model": 512, "d_ff": 1024, "context_len": 256, "num_layers": 2 * world,
+                  "num_expert_per_node": 4},
+        "train": {"fsdp_parallel_num": 1, "data_parallel_num": 1, "pipeline_parallel_stages": world,
+                  "learning_rate": 1e-3, "optimizer": {"beta1": 0.9, "beta2": 0.999, "lambda": 0.01}},
+    }
+    mesh = build_groups(config["train"], rank, world, world)
+    stage = mesh.stage
+    losses, weights = {}, {}
+    for kind in ("nccl", "peer"):
+        comm = make_comm(mesh, device, wait_seconds=5.0, pipeline_link=kind, pipeline_wait_seconds=20.0)
+        torch.manual_seed(77 + stage)
+        model, opt = build_model(config, mesh, device, mesh.group("fsdp"), mesh.group("ddp"), torch.bfloat16, comm)
+        torch.manual_seed(1000)
+        run = []
+        for step in range(3):
+            ids = torch.randint(0, 2048, (16, 257), device=device)
+            loss = pipelined_train_overlap(model, opt, ids[:, :-1] if stage == 0 else None,
+                                           ids[:, 1:] if stage == world - 1 else None, [16, 256, 512], 8, stage,
+                                           cross_entropy, dtype=torch.bfloat16, device=device,
+                                           pp_group=mesh.group("pp"), dp_group=mesh.group("data"))
+            run.append(float(loss))
+        torch.cuda.synchronize()
+        native.check_status()
+        links = [link for link in comm._pp.values() if link is not None]
+        if kind == "peer":
+            assert len(links) == 1 and isinstance(links[0], PeerLink)
+            link = links[0]
+            # three steps of eight microbatches: every ring wrapped several times
+            assert link.done == 24
+            assert link.sent_act == (24 if stage < world - 1 else 0) and link.got_act == (24 if stage > 0 else 0)
+            assert link.sent_grad == (24 if stage > 0 else 0) and link.got_grad == (24 if stage < world - 1 else 0)
+        else:
+            assert not links
+        losses[kind] = run
+        weights[kind] = torch.cat([p.detach().float().reshape(-1) for p in model.parameters()])
+    if stage == world - 1:
+        assert all(l > 0 for l in losses["nccl"])
+        for a, b in zip(losses["nccl"], losses["peer"]):
+            assert abs(a - b) < 2e-3, losses
+    assert _rel(weights["peer"], weights["nccl"]) < 1e-3
+
+
 def _allgather_gemm(rank, world, port, out_dir):
     """All-gather fused with its GEMM against NCCL all_gather + fp32 matmul, over several "steps"."""
     import torch
@@ -262,6 +319,10 @@ def run_moe_ep(rank, world, port, out_dir):
 
 def run_train_parity(rank, world, port, out_dir, pp, ddp=1, skew=False):
     _guarded(_train_parity, rank, world, port, out_dir, pp, ddp, skew)
+
+
+def run_pipeline_link(rank, world, port, out_dir):
+    _guarded(_pipeline_link, rank, world, port, out_dir)
 
 
 def run_allgather_gemm(rank, world, port, out_dir):

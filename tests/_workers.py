@@ -190,3 +190,142 @@ def run_reference_layout(rank, world, port, result_dir, pp, ref_dir):
         raise
     finally:
         dist.destroy_process_group()
+
+
+class HostTransport:
+    """Stand-in for ``b200moe.comm.pp.DeviceTransport`` on CPU ranks: the landing rings and flag words are files
+    mapped by every rank, a send runs at call time (it blocks the rank exactly where the kernel would block the
+    stream), and the ring discipline is checked: a slot that its receiver still uses must never be written."""
+
+    def __init__(self, folder, stage, stages, slot_bytes, act_slots, grad_slots, timeout=60.0):
+        import torch
+        import torch.distributed as dist
+        self.stage, self.stages, self.slot_bytes = stage, stages, slot_bytes
+        self.act_slots, self.grad_slots = act_slots, grad_slots
+        self.timeout = timeout
+        slots = act_slots + grad_slots
+        for name, size in (("data", slot_bytes * slots), ("flags", 4 * 64), ("busy", 4 * slots)):
+            with open(os.path.join(folder, f"{name}_{stage}.bin"), "wb") as f:
+                f.write(b"\0" * size)
+        dist.barrier()
+        self.data = [torch.from_file(os.path.join(folder, f"data_{r}.bin"), shared=True, size=slot_bytes * slots,
+                                     dtype=torch.uint8) for r in range(stages)]
+        self.flags = [torch.from_file(os.path.join(folder, f"flags_{r}.bin"), shared=True, size=64,
+                                      dtype=torch.int32) for r in range(stages)]
+        self.busy = [torch.from_file(os.path.join(folder, f"busy_{r}.bin"), shared=True, size=slots,
+                                     dtype=torch.int32) for r in range(stages)]
+        self.waits_for_room = 0
+        dist.barrier()
+
+    def buffers(self):
+        return []
+
+    def _spin(self, word, seq, what):
+        import time
+        deadline = time.monotonic() + self.timeout
+        while int(word[0]) < seq:
+            if time.monotonic() > deadline:
+                raise TimeoutError(f"stage {self.stage}: {what} {seq} never came")
+            time.sleep(0.0005)
+
+    def slot(self, index, spec, dtype):
+        import math
+        begin = index * self.slot_bytes
+        return self.data[self.stage][begin:begin + math.prod(spec) * dtype.itemsize].view(dtype).view(spec)
+
+    def send(self, payload, peer, slot, flag, ack_word, seq, need_ack):
+        mine = self.flags[self.stage]
+        if need_ack > 0 and int(mine[ack_word]) < need_ack:
+            self.waits_for_room += 1
+            self._spin(mine[ack_word:ack_word + 1], need_ack, "acknowledgement")
+        if int(self.busy[peer][slot]) != 0:
+            raise AssertionError(f"stage {self.stage} overwrites slot {slot} of stage {peer} while message "
+                                 f"{int(self.busy[peer][slot])} is still in use (sending {seq})")
+        raw = payload.contiguous().view(-1).view(torch_uint8())
+        begin = slot * self.slot_bytes
+        self.data[peer][begin:begin + raw.numel()].copy_(raw)
+        self.flags[peer][flag] = seq
+
+    def wait(self, flag, seq):
+        self._spin(self.flags[self.stage][flag:flag + 1], seq, "message")
+        if int(self.flags[self.stage][flag]) != seq:
+            raise AssertionError(f"stage {self.stage}: slot of flag {flag} holds message "
+                                 f"{int(self.flags[self.stage][flag])}, expected {seq}")
+        slot = flag if flag < 16 else self.act_slots + (flag - 16)
+        self.busy[self.stage][slot] = seq
+
+    def ack(self, upstream, downstream, value):
+        if upstream is not None:
+            self.busy[self.stage][(value - 1) % self.act_slots] = 0
+            self.flags[upstream][32] = value
+        if downstream is not None:
+            self.busy[self.stage][self.act_slots + (value - 1) % self.grad_slots] = 0
+            self.flags[downstream][33] = value
+
+
+def torch_uint8():
+    import torch
+    return torch.uint8
+
+
+def run_peer_link_schedule(rank, world, port, result_dir, microbatches, steps, act_slots):
+    """The 1F1B scheduler over ``world`` stages, once with the NCCL-style link (gloo) and once with the peer link
+    over ``HostTransport``: same losses and gradients, no ring overrun, no deadlock."""
+    import torch
+    import torch.distributed as dist
+    _env(rank, world, port)
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from b200moe.comm.pp import GRAD_SLOTS, PeerLink
+        from b200moe.models import TransformerLMPipelined
+        from b200moe.ops.functional import cross_entropy
+        from b200moe.optim import AdamW
+        from b200moe.parallel import FSDPWrapperPipelined, pipelined_train_overlap
+        from b200moe.topology import build_groups
+        mesh = build_groups({"fsdp_parallel_num": 1, "data_parallel_num": 1, "pipeline_parallel_stages": world},
+                            rank, world, world)
+        stage = mesh.stage
+        V, S, D, H, E, FF, B = 128, 16, 32, 4, 2, 48, 2 * microbatches
+        spec = [B // microbatches, S, D]
+        results = {}
+        for kind in ("nccl", "peer"):
+            torch.manual_seed(11 + stage)
+            model = TransformerLMPipelined(V, S, D, 1, H, stage, world, num_expert_per_node=E, d_ff=FF,
+                                           dp_group=mesh.group("fsdp"), moe_compute_dtype=torch.float32)
+            wrapped = FSDPWrapperPipelined(model, mesh.group("fsdp"), None, compute_dtype=torch.float32,
+                                           moe_compute_dtype=torch.float32)
+            transport = None
+            if kind == "peer":
+                folder = os.path.join(result_dir, "rings")
+                os.makedirs(folder, exist_ok=True)
+                transport = HostTransport(folder, stage, world, PeerLink.slot_bytes(spec, torch.float32),
+                                          act_slots, GRAD_SLOTS)
+                link = PeerLink(stage, world, spec, torch.float32, transport, act_slots=act_slots)
+
+                class _Offer:
+                    def pp_link(self, group, stage_, spec_, dtype_):
+                        assert (stage_, list(spec_), dtype_) == (stage, spec, torch.float32)
+                        return link
+                wrapped.comm = _Offer()
+            opt = AdamW(wrapped.parameters(), lr=1e-3, weight_decay=0.0)
+            gen = torch.Generator().manual_seed(5)
+            losses = []
+            for _ in range(steps):
+                data = torch.randint(0, V, (B, S + 1), generator=gen)
+                loss = pipelined_train_overlap(wrapped, opt, data[:, :-1] if stage == 0 else None,
+                                               data[:, 1:] if stage == world - 1 else None, [B, S, D], microbatches,
+                                               stage, cross_entropy, dtype=torch.float32, device=torch.device("cpu"),
+                                               pp_group=mesh.group("pp"), dp_group=mesh.group("data"))
+                losses.append(float(loss))
+            results[kind] = {"losses": losses,
+                             "weights": {k: v.detach().clone() for k, v in wrapped.state_dict().items()},
+                             "waits_for_room": 0 if transport is None else transport.waits_for_room}
+            dist.barrier()
+        torch.save({"stage": stage, **results}, os.path.join(result_dir, f"link_{rank}.pt"))
+    except Exception:
+        with open(os.path.join(result_dir, f"err_{rank}.txt"), "w") as f:
+            f.write(traceback.format_exc())
+        raise
+    finally:
+        dist.destroy_process_group()

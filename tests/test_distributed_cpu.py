@@ -119,3 +119,20 @@ def test_host_failure_then_restart_resumes_from_last_commit(tmp_path, free_port)
     text = (res2 / "out_0.txt").read_text()
     assert f"loaded checkpoint at {committed[-1]} iterations" in text
     assert "FINAL 12" in text
+
+
+@pytest.mark.parametrize("world,microbatches,act_slots", [(4, 8, 4), (2, 6, 2), (3, 7, 2)])
+def test_peer_link_schedule_matches_nccl_link(tmp_path, free_port, world, microbatches, act_slots):
+    """The pipeline's peer-memory link (message numbers, landing rings, acknowledgements) under the real 1F1B
+    scheduler, with a host transport in place of the kernels: bit-identical training to the send/recv link, no slot
+    written while in use, no deadlock — also with the smallest activation ring the schedule allows (``pp − 1`` slots), where senders wait."""
+    _spawn(W.run_peer_link_schedule, world, (world, free_port, str(tmp_path), microbatches, 3, act_slots))
+    outs = [torch.load(tmp_path / f"link_{r}.pt") for r in range(world)]
+    for o in outs:
+        assert o["nccl"]["losses"] == o["peer"]["losses"]
+        for key, value in o["nccl"]["weights"].items():
+            assert torch.equal(value, o["peer"]["weights"][key]), key
+    assert any(o["stage"] == world - 1 and o["peer"]["losses"][0] > 0 for o in outs)
+    if act_slots >= world:
+        # a ring of ``pp`` activation slots never makes a sender wait for room under 1F1B
+        assert all(o["peer"]["waits_for_room"] == 0 or o["stage"] > 0 for o in outs)

@@ -58,3 +58,13 @@ def test_training_steps_fused_vs_nccl_fsdp4_ep4(tmp_path, free_port):
 def test_training_steps_fused_vs_nccl_fsdp2_with_two_replicas(tmp_path, free_port):
     _need(4)
     _run(W.run_train_parity, 4, tmp_path, free_port, 1, 2)
+
+
+def test_pipeline_peer_link_matches_nccl_link_two_stages(tmp_path, free_port):
+    _need(2)
+    _run(W.run_pipeline_link, 2, tmp_path, free_port)
+
+
+def test_pipeline_peer_link_matches_nccl_link_four_stages(tmp_path, free_port):
+    _need(4)
+    _run(W.run_pipeline_link, 4, tmp_path, free_port)

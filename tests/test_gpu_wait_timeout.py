@@ -111,3 +111,63 @@ def test_vectorised_end_of_step_kernel_matches_the_adamw_rule_on_emulated_single
     torch.testing.assert_close(v, want_v, rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(master, want_p, rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(full_w.float(), want_p.bfloat16().float())
+
+
+def _pp_send(native, src, dst, flag, ack, seq, need_ack, wait_s, ticket, status):
+    native._call("b2_pp_send", ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(dst.data_ptr()),
+                 ctypes.c_longlong(src.numel() * src.element_size()), ctypes.c_void_p(flag.data_ptr()),
+                 ctypes.c_void_p(ack.data_ptr()), ctypes.c_int(seq), ctypes.c_int(need_ack),
+                 ctypes.c_longlong(int(wait_s * 1e9)), ctypes.c_void_p(ticket.data_ptr()),
+                 ctypes.c_void_p(status.data_ptr()), _stream())
+
+
+def test_pipeline_link_kernels_deliver_and_give_up(native):
+    """The pipeline's send / wait / acknowledge kernels with this GPU as its own neighbour: a message lands whole and
+    its number is published; a send into a full ring and a wait for a message that nobody sends both return within
+    their budget with their status code, and the send leaves slot and flag alone."""
+    status = native.status_word()
+    ticket = torch.zeros(1, dtype=torch.int32, device="cuda")
+    words = torch.zeros(64, dtype=torch.int32, device="cuda")
+    for numel in (8, 4096 * 33 + 8, 64 * 1024 * 1024 + 24):            # bf16 elements: whole 16-byte units
+        src = torch.randn(numel, device="cuda").bfloat16()
+        dst = torch.zeros(numel + 64, dtype=torch.bfloat16, device="cuda")
+        words.zero_()
+        _pp_send(native, src, dst, words[3:], words[32:], 5, 0, 0.2, ticket, status)
+        native._call("b2_pp_wait", ctypes.c_void_p(words[3:].data_ptr()), ctypes.c_int(5),
+                     ctypes.c_longlong(200_000_000), ctypes.c_void_p(status.data_ptr()), _stream())
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert torch.equal(dst[:numel], src) and float(dst[numel:].float().abs().max()) == 0.0
+        assert int(words[3].item()) == 5 and int(ticket.item()) == 0
+    # acknowledge: both neighbours' words
+    native._call("b2_pp_ack", ctypes.c_void_p(words[32:].data_ptr()), ctypes.c_void_p(words[33:].data_ptr()),
+                 ctypes.c_int(9), _stream())
+    native._call("b2_pp_ack", ctypes.c_void_p(0), ctypes.c_void_p(words[40:].data_ptr()), ctypes.c_int(4), _stream())
+    torch.cuda.synchronize()
+    assert words[32:34].tolist() == [9, 9] and int(words[40].item()) == 4
+    # a send that has room once message 9 is acknowledged goes through; one that needs message 10 gives up
+    src = torch.randn(4096, device="cuda").bfloat16()
+    dst = torch.zeros(4096, dtype=torch.bfloat16, device="cuda")
+    _pp_send(native, src, dst, words[4:], words[32:], 11, 9, 0.2, ticket, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and torch.equal(dst, src) and int(words[4].item()) == 11
+    dst.zero_()
+    t0 = time.perf_counter()
+    _pp_send(native, src, dst, words[5:], words[32:], 12, 10, 0.05, ticket, status)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0
+    assert int(status.item()) == 321
+    assert float(dst.float().abs().max()) == 0.0 and int(words[5].item()) == 0 and int(ticket.item()) == 0
+    native.clear_status()
+    t0 = time.perf_counter()
+    native._call("b2_pp_wait", ctypes.c_void_p(words[6:].data_ptr()), ctypes.c_int(1), ctypes.c_longlong(50_000_000),
+                 ctypes.c_void_p(status.data_ptr()), _stream())
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0
+    assert int(status.item()) == 322
+    with pytest.raises(RuntimeError, match="322"):
+        native.check_status()
+    native.clear_status()
+    # misuse is refused on the host
+    with pytest.raises(RuntimeError, match="-8"):
+        _pp_send(native, src[:4], dst, words[5:], words[32:], 13, 0, 0.05, ticket, status)

@@ -78,7 +78,15 @@ def test_comm_reports_multicast_and_releases_its_buffers():
 
     comm = Comm.__new__(Comm)
     plain, bound = FakeBuffer(0), FakeBuffer(0xdead0000)
-    comm._symm, comm._ar_stage, comm._ep = {1: plain}, {}, {}
+    class FakeLink:
+        def __init__(self, *buffers):
+            self.held = list(buffers)
+
+        def buffers(self):
+            return self.held
+
+    ring = FakeBuffer(0)
+    comm._symm, comm._ar_stage, comm._ep, comm._pp = {1: plain}, {}, {}, {"link": FakeLink(ring), "none": None}
     comm.fsdp = comm.ddp = None
     comm.device = torch.device("cpu")
     assert comm.any_multicast() is False
@@ -86,6 +94,7 @@ def test_comm_reports_multicast_and_releases_its_buffers():
     assert comm.any_multicast() is True
     comm.release()
     assert comm.any_multicast() is False and bound.tensor is None and bound.handle is None and not comm._symm
+    assert ring.tensor is None and ring.handle is None and not comm._pp
 
 
 def test_watchdog_runs_the_release_hook_before_it_ends_the_process():
