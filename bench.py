@@ -278,7 +278,7 @@ def bench_b200moe(args):
         from b200moe.utils.data import BatchStager
         from b200moe.utils.schedule import learning_rate_schedule_wrapper
         cfg = run_config(args)
-        single = args.gpus == 1
+        single = cfg["fsdp"] == 1          # all 8 experts of every block on this GPU
         config = {
             "general": {"device": "gpu", "n_workers": world, "gpu_per_node": world, "info_src": 0},
             "data": {"vocab_size": MODEL["vocab"], "mock_data": True, "seed": 42},
