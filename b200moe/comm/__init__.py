@@ -109,10 +109,10 @@ class Comm:
     def __init__(self, mesh, device, multicast: bool = False, wait_seconds: float | None = None,
                  pipeline_link: str | None = None, pipeline_wait_seconds: float = 120.0):
         """``pipeline_link``: ``"peer"`` moves the pipeline's activations and gradients with this library's
-        peer-store kernels (``pp_link``), ``"nccl"`` with batched NCCL send/recv; ``None`` reads
-        ``B200MOE_PIPELINE_LINK`` and defaults to ``"nccl"``.  ``pipeline_wait_seconds``: budget of a pipeline wait
-        (they span whole stage steps, so it is longer than ``wait_seconds``).  ``multicast``: let the symmetric-memory rendezvous bind buffers to an NVSwitch multicast address (only
-        the NVLS all-reduce uses it).  Off by default: a process that dies while bound raises NVLink faults on the
+        peer-store kernels (``pp_link``), ``"nccl"`` with batched NCCL send/recv (the default);
+        ``B200MOE_PIPELINE_LINK`` overrides it.  ``pipeline_wait_seconds``: budget of a pipeline wait
+        (they span whole stage steps, so it is longer than ``wait_seconds``).  ``multicast``: let the
+        symmetric-memory rendezvous bind buffers to an NVSwitch multicast address (only the NVLS all-reduce uses it).  Off by default: a process that dies while bound raises NVLink faults on the
         other ranks' GPUs, and nothing else here needs the binding.  ``wait_seconds``: budget of every cross-GPU
         wait inside the kernels (``native.set_wait_seconds``)."""
         import os
@@ -131,7 +131,7 @@ class Comm:
         self.ddp = GroupComm(mesh.group("ddp"), device) if mesh.ddp > 1 else None
         skew = os.environ.get("B200MOE_EP_MAX_SKEW")
         self.ep_max_skew = float(skew) if skew else None
-        chosen = pipeline_link or os.environ.get("B200MOE_PIPELINE_LINK") or "nccl"
+        chosen = os.environ.get("B200MOE_PIPELINE_LINK") or pipeline_link or "nccl"
         if chosen not in ("peer", "nccl"):
             raise ValueError(f"pipeline_link must be 'peer' or 'nccl', got {chosen!r}")
         self.pipeline_link = chosen

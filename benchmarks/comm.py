@@ -30,7 +30,7 @@ sys.path.insert(0, ROOT)
 NVLINK_GBS = 770.0
 
 
-def timed(fn, iters=5, warmup=2):
+def timed(fn, iters=5, warmup=3):
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -112,7 +112,7 @@ def main():
         emit(case="moe block fwd+bwd, exchange fused with the expert GEMMs", ms=round(ms, 3),
              tflops_per_gpu=round(flops / ms / 1e9, 1), max_rows_over_balanced=round(epc.worst_load(), 3))
         if not args.skip_nccl:
-            ms_nccl = timed(lambda: block(False), iters=2, warmup=1)
+            ms_nccl = timed(lambda: block(False), iters=2, warmup=3)
             emit(case="moe block fwd+bwd, NCCL all-to-all + library grouped GEMM", ms=round(ms_nccl, 3),
                  tflops_per_gpu=round(flops / ms_nccl / 1e9, 1))
         # the two fused kernels alone, on one fixed routing
