@@ -51,7 +51,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--skip-nccl", action="store_true")
     ap.add_argument("--tokens", type=int, default=16384)
-    ap.add_argument("--only", default="", help="comma-separated subset of: moe, fsdp, aggemm, allreduce")
+    ap.add_argument("--only", default="", help="comma-separated subset of: moe, fsdp, aggemm, allreduce, pp")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -158,6 +158,39 @@ def main():
              tflops=round(2 * rows_here * D * Fd / ms_return / 1e9, 1),
              frac_of_roofline=round(max(ms_down, link_ms) / ms_return, 3))
         epc.release(slot)
+        native.check_status()
+    if want("pp") and world > 1:
+        # ---- pipeline link: every rank stores one microbatch (2 x 8192 tokens, 128 MiB) into the landing ring of its
+        # right neighbour and waits for the one from its left neighbour, so every GPU sends and receives at once
+        from b200moe.comm.pp import DeviceTransport, PeerLink
+        spec = [2, 8192, D]
+        slot_bytes = PeerLink.slot_bytes(spec, torch.bfloat16)
+        transport = DeviceTransport(group, device, comm.status, slot_bytes, 2, 5.0)
+        payload = torch.randn(spec, device=device).bfloat16()
+        state = {"n": 0}
+
+        def hop():
+            state["n"] += 1
+            n = state["n"]
+            slot = (n - 1) % 2
+            # bandwidth only: nothing reads the slots, so no acknowledgements (need_ack = 0); a neighbour that runs
+            # ahead overwrites a slot and raises its message number, which the wait accepts
+            transport.send(payload, (rank + 1) % world, slot, slot, 32, n, 0)
+            transport.wait(slot, n)
+        ms = timed(hop, iters=20)
+        nbytes = payload.numel() * 2
+        emit(case="pipeline link: 128 MiB to the right neighbour + wait for the left one", ms=round(ms, 4),
+             gbs_per_direction=round(nbytes / ms / 1e6, 1), frac_of_nvlink=round(nbytes / ms / 1e6 / NVLINK_GBS, 3))
+        if not args.skip_nccl:
+            recv = torch.empty_like(payload)
+
+            def nccl_hop():
+                ops_ = [dist.P2POp(dist.isend, payload, (rank + 1) % world), dist.P2POp(dist.irecv, recv, (rank - 1) % world)]
+                for work in dist.batch_isend_irecv(ops_):
+                    work.wait()
+            ms_nccl = timed(nccl_hop, iters=20)
+            emit(case="NCCL batched isend/irecv, same ring", ms=round(ms_nccl, 4),
+                 gbs_per_direction=round(nbytes / ms_nccl / 1e6, 1))
         native.check_status()
     if want("fsdp") and world > 1:
         # ---- end of step: reduce-scatter + AdamW + all-gather of one stage's dense weights in one kernel
