@@ -2,6 +2,8 @@
 import random
 
 import pytest
+import os
+
 import yaml
 
 import modal_wrapper
@@ -247,3 +249,52 @@ def test_allgather_gemm_schedule_on_the_host():
     for bad in (([100], 3), ([0], 2), ([256 * 200], 2)):
         with pytest.raises(ValueError):
             native.ag_gemm_plan(bad[0], bad[1], 0)
+
+
+def test_modal_launcher_nodes_rendezvous_and_profiler(tmp_path, monkeypatch):
+    for name in ("MASTER_ADDR", "MASTER_PORT", "NCCL_HOSTID"):
+        monkeypatch.delenv(name, raising=False)
+    two_nodes = {"general": {"n_workers": 16, "gpu_per_node": 8}, "recovery": {"max_restarts": 1}}
+    # the reference's builder and its checks
+    with pytest.raises(ValueError, match="MASTER_ADDR"):
+        modal_wrapper._build_torchrun_command("c.json", 1, 16, 8)
+    for bad in (dict(cluster_rank=2), dict(world_size=12), dict(max_restarts=-1), dict(max_restarts=True)):
+        args = {"config_path": "c.json", "cluster_rank": 0, "world_size": 16, "gpu_per_node": 8, **bad}
+        with pytest.raises(ValueError):
+            modal_wrapper._build_torchrun_command(**args)
+    cmd = modal_wrapper.torchrun_command(two_nodes, "c.yaml", 1, "fd00::7", 29511, "job")
+    assert "--nnodes=2" in cmd and "--node-rank=1" in cmd and "--rdzv-endpoint=[fd00::7]:29511" in cmd
+    assert "--rdzv-id=job" in cmd and "MASTER_ADDR" not in os.environ
+    # one node of two: rendezvous on the first container, one host id per node, IPv6 sockets for an IPv6 cluster
+    calls = []
+
+    def runner(command, check, env, cwd):
+        with open(command[command.index("--config-path") + 1], encoding="utf-8") as handle:
+            seen = yaml.safe_load(handle)
+        calls.append((command, env, seen))
+    modal_wrapper.run_node(two_nodes, 1, ["fd00::7", "fd00::8"], "cl9", runner=runner)
+    command, env, seen = calls[-1]
+    assert seen == two_nodes and "--master-addr=fd00::7" in command and "--max-restarts=1" in command
+    assert env["NCCL_HOSTID"] == "cl9-node-1" and env["NCCL_SOCKET_FAMILY"] == "AF_INET6" and "--rdzv-id=cl9" in command
+    with pytest.raises(ValueError, match="addresses"):
+        modal_wrapper.run_node(two_nodes, 0, None, runner=runner)
+    # a single node meets itself on loopback whatever the cluster says
+    one = {"general": {"n_workers": 8, "gpu_per_node": 8},
+           "profile": {"enabled": True, "output_dir": str(tmp_path), "nsight_trace": "cuda-sw,nvtx"}}
+    monkeypatch.setattr(modal_wrapper.shutil, "which", lambda name: None)
+    with pytest.raises(RuntimeError, match="nsys"):
+        modal_wrapper.run_node(one, 0, ["10.0.0.5"], runner=runner)
+    monkeypatch.setattr(modal_wrapper.shutil, "which", lambda name: "/opt/nsys")
+    with pytest.raises(RuntimeError, match="did not write"):
+        modal_wrapper.run_node(one, 0, ["10.0.0.5"], runner=runner)
+    committed = []
+
+    def writes_report(command, check, env, cwd):
+        output = [c for c in command if c.startswith("--output=")][0].split("=", 1)[1]
+        open(output + ".nsys-rep", "w").close()
+        calls.append((command, env, None))
+    modal_wrapper.run_node(one, 0, ["10.0.0.5"], runner=writes_report, commit_profile=lambda: committed.append(1))
+    command, env, _ = calls[-1]
+    assert command[:2] == ["/opt/nsys", "profile"] and "--kill=none" in command and "--wait=all" in command
+    assert "--master-addr=127.0.0.1" in command and env["MASTER_ADDR"] == "127.0.0.1" and committed == [1]
+    assert command[command.index("--module") + 1] == "distributed_parallel_training_pipelined"
