@@ -324,13 +324,13 @@ class Attention_Simple(nn.Module):
 
 
 class Attention_Flash(nn.Module):
-    """Non-causal flash attention on ``[B, S, hd]`` or ``[B, H, S, hd]`` inputs
-    with the reference's (k, q, v) argument order (layers.py:430-437)."""
+    """Non-causal flash attention on ``[B, S, hd]`` inputs, called as the reference calls it (layers.py:430-437):
+    ``forward(k, q, v, mask)`` hands ``(k, q, v)`` to a function whose first argument holds the queries, so the
+    tensor named ``k`` plays the queries and ``mask`` is not used.  Kept that way so that results match."""
 
     def forward(self, k, q, v, mask=None):
-        squeeze = q.dim() == 3
-        if squeeze:
-            q, k, v = (t.unsqueeze(1) for t in (q, k, v))
-        import torch.nn.functional as F
-        out = F.scaled_dot_product_attention(q, k, v, attn_mask=mask)
-        return out.squeeze(1) if squeeze else out
+        from ..ops.attention import attention
+        squeeze = k.dim() == 3
+        queries, keys, values = ((t.unsqueeze(2) if squeeze else t.transpose(1, 2)) for t in (k, q, v))
+        out = attention(queries, keys, values, causal=False)
+        return out.squeeze(2) if squeeze else out.transpose(1, 2)

@@ -172,6 +172,20 @@ def _stage_optimizer(optimizer, stager: CheckpointStager) -> dict:
     return {"state": staged, "param_groups": copy.deepcopy(state_dict["param_groups"])}
 
 
+def move_model_state(model, stager: CheckpointStager | None = None) -> dict:
+    """Host snapshot of ``model.state_dict()`` (reference train_utils.py:151-161): every tensor is copied to
+    pinned memory without blocking the host; synchronise the stream before reading the copies.  Without a
+    ``stager`` the buffers are fresh, as in the reference; the asynchronous save passes its own and reuses them."""
+    stager = CheckpointStager() if stager is None else stager
+    return {name: stager.stage(("model", name), tensor) for name, tensor in model.state_dict().items()}
+
+
+def move_optimizer_state(optimizer, stager: CheckpointStager | None = None) -> dict:
+    """Host snapshot of ``optimizer.state_dict()`` (reference train_utils.py:163-180): tensors to pinned memory,
+    everything else and the parameter groups copied."""
+    return _stage_optimizer(optimizer, CheckpointStager() if stager is None else stager)
+
+
 def _rng_bundle(data_rng) -> dict:
     return {
         "data": copy.deepcopy(data_rng.bit_generator.state),
@@ -203,10 +217,8 @@ def save_checkpoint_async_dist(model, optimizer, iteration: int, checkpoint_path
     """Stage on the host, then write in the background; returns the ``Future``."""
     stager = stager or _DEFAULT_STAGER
     stager.wait()
-    model_state = {name: stager.stage(("model", name), tensor)
-                   for name, tensor in model.state_dict().items()}
-    checkpoint = {"model.state_dict": model_state,
-                  "optimizer.state_dict": _stage_optimizer(optimizer, stager),
+    checkpoint = {"model.state_dict": move_model_state(model, stager),
+                  "optimizer.state_dict": move_optimizer_state(optimizer, stager),
                   "iteration": iteration}
     if data_rng is not None:
         checkpoint["rng"] = _rng_bundle(data_rng)

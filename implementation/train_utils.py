@@ -1,5 +1,6 @@
-from b200moe.utils.checkpoint import (load_checkpoint, load_checkpoint_async_dist, save_checkpoint,  # noqa: F401
-                                      save_checkpoint_async_dist)
+from b200moe.utils.checkpoint import (_load_legacy_optimizer, _write_checkpoint, load_checkpoint,  # noqa: F401
+                                      load_checkpoint_async_dist, move_model_state, move_optimizer_state,
+                                      save_checkpoint, save_checkpoint_async_dist)
 from b200moe.utils.data import get_batch, load_dataset  # noqa: F401
 
 

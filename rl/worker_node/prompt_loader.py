@@ -1,59 +1,94 @@
-"""Sample prompts from a Postgres table (reference rl/worker_node/prompt_loader.py:23-98).
+"""Prompt sources for the RL worker node (reference rl/worker_node/prompt_loader.py:15-98).
 
-Connection settings come from a YAML file (see ``configs/data_source.example.yaml``).
-``psycopg`` is imported when a connection is first needed; a connection factory can
-be injected for tests.
+``DatabasePromptLoader`` reads its connection settings and the SQL that fetches a
+prompt from a YAML file in the reference's format (``configs/data_source.example.yaml``):
+
+    database:      {host, dbname, user, password, [port, sslmode, connect_timeout, ...]}
+    prompt_query:  SELECT ... LIMIT 1
+
+Every key of ``database`` goes into the connection string as it is.  A sampled
+prompt is the first row of the query as a dict keyed by column name, or ``None``
+when the query returns nothing.  ``psycopg`` is imported when a connection is
+first needed; a connection factory can be injected for tests.
 """
 from __future__ import annotations
 
 from pathlib import Path
+from typing import Any
 
 import yaml
 
+DEFAULT_CONFIG_PATH = Path(__file__).resolve().parents[2] / "configs" / "data_source.yaml"
+_REQUIRED_DB_KEYS = ("host", "dbname", "user", "password")
 
-class DatabasePromptLoader:
-    REQUIRED = ("host", "port", "dbname", "user")
 
-    def __init__(self, config_path, connect=None):
-        with Path(config_path).open(encoding="utf-8") as handle:
-            config = yaml.safe_load(handle) or {}
-        source = config.get("data_source") or {}
-        missing = [k for k in self.REQUIRED if k not in source]
-        if missing:
-            raise ValueError(f"data_source is missing keys: {missing}")
-        self.source = source
-        self.table = source.get("table", "prompts")
-        self.dataset = source.get("dataset")
-        if not self.table.replace("_", "").isalnum():
-            raise ValueError("table name must be alphanumeric")
+class PromptLoader:
+    """Interface of a prompt source: ``samplePrompt()`` returns one prompt as a dict, or ``None``."""
+
+    def samplePrompt(self) -> dict[str, Any] | None:
+        return None
+
+
+def read_data_source(config_path) -> dict[str, Any]:
+    """Load and check a data-source file; returns ``{"database": {...}, "prompt_query": "..."}``."""
+    path = Path(config_path)
+    if not path.is_file():
+        raise FileNotFoundError(f"data source config not found: {path} (copy configs/data_source.example.yaml to "
+                                "configs/data_source.yaml and fill in the credentials)")
+    with path.open(encoding="utf-8") as handle:
+        config = yaml.safe_load(handle)
+    if not isinstance(config, dict):
+        raise TypeError(f"invalid data source config: {path}")
+    database = config.get("database")
+    if not isinstance(database, dict):
+        raise TypeError("the config must hold a 'database' mapping")
+    missing = [key for key in _REQUIRED_DB_KEYS if key not in database]
+    if missing:
+        raise ValueError(f"'database' is missing required keys: {missing}")
+    query = config.get("prompt_query")
+    if not isinstance(query, str) or not query.strip():
+        raise ValueError("the config must hold a non-empty 'prompt_query' SQL string")
+    return config
+
+
+class DatabasePromptLoader(PromptLoader):
+    """Prompts from a PostgreSQL database; one lazily opened, autocommitting connection that is reopened if it
+    was closed under us."""
+
+    def __init__(self, config_path=DEFAULT_CONFIG_PATH, connect=None):
+        self._config = read_data_source(config_path)
+        self._conninfo = self._build_conninfo(self._config["database"])
+        self._prompt_query = self._config["prompt_query"]
         self._connect = connect
-        self._connection = None
+        self._conn = None
 
-    def _conn(self):
-        if self._connection is None:
+    @staticmethod
+    def _build_conninfo(database: dict[str, Any]) -> str:
+        return " ".join(f"{key}={value}" for key, value in database.items())
+
+    def _get_connection(self):
+        if self._conn is None or getattr(self._conn, "closed", False):
             if self._connect is None:
                 import psycopg
-                self._connect = psycopg.connect
-            keys = ("host", "port", "dbname", "user", "password")
-            self._connection = self._connect(**{k: self.source[k] for k in keys if k in self.source})
-        return self._connection
+                from psycopg.rows import dict_row
+                self._conn = psycopg.connect(self._conninfo, autocommit=True, row_factory=dict_row)
+            else:
+                self._conn = self._connect(self._conninfo)
+        return self._conn
 
-    def samplePrompt(self):
-        """One random row as ``{"id", "prompt", "metadata"}`` or ``None`` if the table is empty."""
-        query = f"SELECT id, prompt, metadata FROM {self.table}"
-        params = ()
-        if self.dataset:
-            query += " WHERE dataset = %s"
-            params = (self.dataset,)
-        query += " ORDER BY random() LIMIT 1"
-        with self._conn().cursor() as cursor:
-            cursor.execute(query, params)
+    def samplePrompt(self) -> dict[str, Any] | None:
+        with self._get_connection().cursor() as cursor:
+            cursor.execute(self._prompt_query)
             row = cursor.fetchone()
-        if row is None:
-            return None
-        return {"id": row[0], "prompt": row[1], "metadata": row[2]}
+        return None if row is None else dict(row)
 
-    def close(self):
-        if self._connection is not None:
-            self._connection.close()
-            self._connection = None
+    def close(self) -> None:
+        if self._conn is not None and not getattr(self._conn, "closed", False):
+            self._conn.close()
+        self._conn = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()

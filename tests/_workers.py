@@ -329,3 +329,56 @@ def run_peer_link_schedule(rank, world, port, result_dir, microbatches, steps, a
         raise
     finally:
         dist.destroy_process_group()
+
+
+def run_weight_hooks(rank, world, port, result_dir):
+    """Two row-sharded linear modules in sequence with the gather / prefetch / free hooks of
+    ``b200moe.parallel.hooks`` against the same modules holding full weights."""
+    import collections
+    import torch
+    import torch.distributed as dist
+    _env(rank, world, port)
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from implementation.distributed import ddp_modules as H
+        torch.manual_seed(3)
+        full = [torch.nn.Linear(8, 12, bias=False), torch.nn.Linear(12, 6, bias=False)]
+        x = torch.randn(5, 8)
+        want = full[1](full[0](x))
+        want.sum().backward()
+        sharded = [torch.nn.Linear(8, 12, bias=False), torch.nn.Linear(12, 6, bias=False)]
+        for whole, part in zip(full, sharded):
+            rows = whole.weight.shape[0] // world
+            part.weight.data = whole.weight.data[rank * rows:(rank + 1) * rows].clone()
+        first, second = sharded
+        works, works_back = collections.deque(), collections.deque()
+        # forward: the first module gathers itself and prefetches the second, which only waits for its prefetch
+        first.register_forward_pre_hook(H.sync_weight_wrapper(torch.float32, None))
+        first.register_forward_pre_hook(H.async_weight_wrapper_next(second, works, torch.float32, None))
+        second.register_forward_pre_hook(H.wait_prefetched_weight(works))
+        # backward: mirrored, the second module gathers itself and prefetches the first
+        second.register_full_backward_pre_hook(H.sync_weight_wrapper_backward(torch.float32, None))
+        second.register_full_backward_pre_hook(H.async_weight_wrapper_backward_next(first, works_back, torch.float32, None))
+        first.register_full_backward_pre_hook(H.wait_prefetched_weight_backward(works_back))
+        for module in sharded:
+            module.register_forward_hook(H.free_weight)
+            module.register_full_backward_hook(H.free_weight_backward)
+        xs = x.clone().requires_grad_(True)
+        got = second(first(xs))
+        assert torch.allclose(got, want, atol=1e-6)
+        assert first.weight.shape[0] == 12 // world and second.weight.shape[0] == 6 // world     # shards are back
+        got.sum().backward()
+        assert not works and not works_back
+        assert first.weight.shape[0] == 12 // world and first.weight.data_original is None
+        for whole, part in zip(full, sharded):
+            assert part.weight.grad.shape == whole.weight.shape
+            assert torch.allclose(part.weight.grad, whole.weight.grad, atol=1e-6)
+        with open(os.path.join(result_dir, f"hooks_ok_{rank}"), "w") as f:
+            f.write("ok")
+    except Exception:
+        with open(os.path.join(result_dir, f"err_{rank}.txt"), "w") as f:
+            f.write(traceback.format_exc())
+        raise
+    finally:
+        dist.destroy_process_group()

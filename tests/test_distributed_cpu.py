@@ -136,3 +136,8 @@ def test_peer_link_schedule_matches_nccl_link(tmp_path, free_port, world, microb
     if act_slots >= world:
         # a ring of ``pp`` activation slots never makes a sender wait for room under 1F1B
         assert all(o["peer"]["waits_for_room"] == 0 or o["stage"] > 0 for o in outs)
+
+
+def test_gather_and_free_hooks_on_hand_sharded_modules(tmp_path, free_port):
+    _spawn(W.run_weight_hooks, 2, (2, free_port, str(tmp_path)))
+    assert all((tmp_path / f"hooks_ok_{r}").exists() for r in range(2))

@@ -1,17 +1,16 @@
 """Launchers, tools, chaos hooks and the side car, all on CPU with fakes."""
+import os
 import random
 
 import pytest
-import os
-
 import yaml
 
 import modal_wrapper
 import run_experiment
 from b200moe.utils import chaos
 from b200moe.utils.metrics import MetricsSink, flops_per_token, mfu
-from rl.worker_node.prompt_loader import DatabasePromptLoader
-from rl.worker_node.start_vllm import build_command, start_server
+from rl.worker_node.prompt_loader import DatabasePromptLoader, PromptLoader, read_data_source
+from rl.worker_node.start_vllm import build_command, find_vllm_servers, kill_existing_vllm_server, start_server
 
 
 def test_flops_per_token_matches_published_figure():
@@ -97,18 +96,19 @@ def test_prompt_loader_with_fake_connection(tmp_path):
         def __enter__(self):
             return self
 
-        def __exit__(self, *a):
+        def __exit__(self, *exc):
             return False
 
-        def execute(self, query, params):
-            self.seen.append((query, params))
+        def execute(self, query):
+            self.seen.append(query)
 
         def fetchone(self):
             return self.rows.pop(0) if self.rows else None
 
     class Conn:
-        def __init__(self, **kw):
-            self.kw, self.cur = kw, Cursor([(7, "hello", {"a": 1})])
+        def __init__(self, conninfo):
+            self.conninfo, self.closed = conninfo, False
+            self.cur = Cursor([{"id": 7, "prompt_text": "hello", "priority": 2}])
 
         def cursor(self):
             return self.cur
@@ -116,27 +116,57 @@ def test_prompt_loader_with_fake_connection(tmp_path):
         def close(self):
             self.closed = True
 
+    good = {"database": {"host": "h", "port": 1, "dbname": "d", "user": "u", "password": "p", "sslmode": "prefer"},
+            "prompt_query": "SELECT id, prompt_text, priority FROM prompts LIMIT 1;"}
     path = tmp_path / "ds.yaml"
-    path.write_text(yaml.safe_dump({"data_source": {"host": "h", "port": 1, "dbname": "d", "user": "u",
-                                                    "dataset": "gsm"}}))
+    path.write_text(yaml.safe_dump(good, sort_keys=False))
     made = []
-    loader = DatabasePromptLoader(path, connect=lambda **kw: made.append(Conn(**kw)) or made[-1])
-    assert loader.samplePrompt() == {"id": 7, "prompt": "hello", "metadata": {"a": 1}}
-    assert "WHERE dataset = %s" in made[0].cur.seen[0][0] and made[0].cur.seen[0][1] == ("gsm",)
-    assert loader.samplePrompt() is None
-    loader.close()
-    path.write_text(yaml.safe_dump({"data_source": {"host": "h"}}))
-    with pytest.raises(ValueError, match="missing"):
-        DatabasePromptLoader(path)
+    with DatabasePromptLoader(path, connect=lambda info: made.append(Conn(info)) or made[-1]) as loader:
+        assert isinstance(loader, PromptLoader) and PromptLoader().samplePrompt() is None
+        assert loader.samplePrompt() == {"id": 7, "prompt_text": "hello", "priority": 2}
+        assert made[0].conninfo == "host=h port=1 dbname=d user=u password=p sslmode=prefer"
+        assert made[0].cur.seen == [good["prompt_query"]]
+        assert loader.samplePrompt() is None
+        made[0].closed = True                              # the server dropped us: the next call reconnects
+        assert loader.samplePrompt() == {"id": 7, "prompt_text": "hello", "priority": 2} and len(made) == 2
+    assert made[1].closed
+    for broken, error in (({**good, "database": {"host": "h"}}, ValueError), ({**good, "prompt_query": " "}, ValueError),
+                          ({"prompt_query": "x"}, TypeError), (["not", "a", "mapping"], TypeError)):
+        path.write_text(yaml.safe_dump(broken))
+        with pytest.raises(error):
+            DatabasePromptLoader(path)
+    with pytest.raises(FileNotFoundError):
+        DatabasePromptLoader(tmp_path / "absent.yaml")
+    # the example file of this repository is a valid data source
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    example = read_data_source(os.path.join(root, "configs", "data_source.example.yaml"))
+    assert "prompt_text" in example["prompt_query"]
 
 
-def test_vllm_launcher_pins_gpu():
+def test_vllm_launcher_pins_gpu_and_ends_only_the_servers_on_its_port():
     calls = []
-    start_server("m", gpu=3, port=9000, popen=lambda cmd, env: calls.append((cmd, env)) or "proc")
-    cmd, env = calls[0]
-    assert cmd[:3] == ["vllm", "serve", "m"] and "--weight-transfer-config" in cmd
-    assert env["CUDA_VISIBLE_DEVICES"] == "3"
+    start_server("m", "0.0.0.0", 9000, 3, seed=5, load_format="dummy", logging_level="DEBUG",
+                 popen=lambda cmd, env, start_new_session: calls.append((cmd, env, start_new_session)) or "proc")
+    cmd, env, own_session = calls[0]
+    assert cmd[:3] == ["vllm", "serve", "m"] and own_session is True
+    for flag, value in (("--host", "0.0.0.0"), ("--port", "9000"), ("--seed", "5"), ("--load-format", "dummy"),
+                        ("--tensor-parallel-size", "1"), ("--gpu-memory-utilization", "0.9"),
+                        ("--weight-transfer-config", '{"backend": "nccl"}')):
+        assert cmd[cmd.index(flag) + 1] == value
+    assert "--enable-prefix-caching" in cmd
+    assert (env["CUDA_VISIBLE_DEVICES"], env["VLLM_SERVER_DEV_MODE"], env["VLLM_LOGGING_LEVEL"]) == ("3", "1", "DEBUG")
     assert "--max-model-len" in build_command("m", max_model_len=128)
+    table = [(11, ["/usr/bin/python", "/opt/bin/vllm", "serve", "m", "--port", "9000"]),
+             (12, ["vllm", "serve", "m", "--port", "9001"]),
+             (13, ["vllm", "serve", "m", "--host", "x", "--port=9000"]),
+             (14, ["grep", "vllm serve m --port 9000"]),
+             (os.getpid(), ["vllm", "serve", "m", "--port", "9000"])]
+    assert find_vllm_servers(9000, table) == [11, 13]
+    sent, naps = [], []
+    assert kill_existing_vllm_server(9000, table, send=lambda pid, sig: sent.append((pid, int(sig))),
+                                     sleep=naps.append) == [11, 13]
+    assert sent == [(11, 15), (13, 15), (11, 9), (13, 9)] and naps == [2.0]
+    assert kill_existing_vllm_server(7, table, send=lambda *a: sent.append(a), sleep=naps.append) == [] and len(sent) == 4
 
 
 def test_helm_values_hold_a_valid_run_config():
