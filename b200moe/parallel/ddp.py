@@ -23,9 +23,10 @@ def _world():
     return 0, 1
 
 
-def sync_grad(works: list, group=None):
+def sync_grad(works: list, FSDP_communication_group=None):
     def hook(param):
-        works.append(dist.all_reduce(param.grad.data, op=dist.ReduceOp.AVG, async_op=True, group=group))
+        works.append(dist.all_reduce(param.grad.data, op=dist.ReduceOp.AVG, async_op=True,
+                                     group=FSDP_communication_group))
     return hook
 
 

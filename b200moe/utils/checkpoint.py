@@ -212,7 +212,7 @@ def _write_checkpoint(checkpoint: dict, destination) -> None:
             os.unlink(temporary)
 
 
-def save_checkpoint_async_dist(model, optimizer, iteration: int, checkpoint_path, data_rng=None,
+def save_checkpoint_async_dist(model, optimizer, iteration: int, checkpoint_dir, data_rng=None,
                                stager: CheckpointStager | None = None) -> Future:
     """Stage on the host, then write in the background; returns the ``Future``."""
     stager = stager or _DEFAULT_STAGER
@@ -226,17 +226,17 @@ def save_checkpoint_async_dist(model, optimizer, iteration: int, checkpoint_path
         torch.cuda.synchronize()
     pool = ThreadPoolExecutor(max_workers=1)
     try:
-        future = pool.submit(_write_checkpoint, checkpoint, checkpoint_path)
+        future = pool.submit(_write_checkpoint, checkpoint, checkpoint_dir)
     finally:
         pool.shutdown(wait=False)
     stager._busy = future
     return future
 
 
-def _load_legacy_optimizer(saved: dict, optimizer) -> None:
+def _load_legacy_optimizer(saved_state: dict, optimizer) -> None:
     """Accept the old layout: a bare ``{index: state}`` mapping without groups."""
     params = [p for group in optimizer.param_groups for p in group["params"]]
-    values = list(saved.values())
+    values = list(saved_state.values())
     if len(values) != len(params):
         raise ValueError("Checkpoint optimizer state invalid, failed to load")
     groups, base = [], 0

@@ -14,25 +14,72 @@ import torch
 from b200moe.ops.attention import attention, flash_attention_forward  # noqa: F401
 
 
-def _attend(q, k, v, causal):
-    """``[B, S, hd]`` single-head attention, differentiable."""
-    return attention(q.unsqueeze(2), k.unsqueeze(2), v.unsqueeze(2), causal=bool(causal)).squeeze(2)
+def _native_ok(q, k, scale=None) -> bool:
+    """bf16, head_dim 128, equal lengths that are multiples of 128, on a GPU, scale 1/√d: the tcgen05 kernels."""
+    if not (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and q.shape[-2] % 128 == 0
+            and k.shape[-2] == q.shape[-2] and q.dim() == 3):
+        return False
+    if scale is not None and abs(scale * math.sqrt(k.shape[-1]) - 1.0) > 1e-6:
+        return False
+    from b200moe.ops import use_native
+    return use_native(q, "attention")
 
 
-class FlashAttentionFunc:
-    """``FlashAttentionFunc.apply(q, k, v, is_causal=False)``: the first argument holds the queries, as in the
-    reference's ``forward(ctx, q, k, v, is_causal)``.  (The reference's PyTorch variant accepts ``is_causal`` and
-    ignores it, :13-37; this one applies the mask.)  Differentiation goes through the attention op itself."""
+def _visible(q, k, causal):
+    """Boolean ``[Sq, Sk]`` mask of the keys a query may see, or ``None``."""
+    if not causal:
+        return None
+    return torch.arange(q.shape[-2], device=q.device)[:, None] >= torch.arange(k.shape[-2], device=q.device)[None, :]
+
+
+def _forward_values(q, k, v, causal, scale=None):
+    """Attention output and log-sum-exp of the scaled scores for ``[B, S, hd]`` tensors, no graph."""
+    with torch.no_grad():
+        if _native_ok(q, k, scale):
+            from b200moe.ops import native
+            out, lse, _, _ = native.attention_fwd(q.unsqueeze(2).contiguous(), k.unsqueeze(2).contiguous(),
+                                                  v.unsqueeze(2).contiguous(), None, None, causal=bool(causal))
+            return out.squeeze(2), lse.squeeze(1)
+        scale = 1.0 / math.sqrt(k.shape[-1]) if scale is None else scale
+        s = torch.einsum("...qd,...kd->...qk", q.float(), k.float()) * scale
+        visible = _visible(q, k, causal)
+        if visible is not None:
+            s = s.masked_fill(~visible, float("-inf"))
+        lse = torch.logsumexp(s, dim=-1)
+        out = torch.einsum("...qk,...kv->...qv", torch.exp(s - lse.unsqueeze(-1)), v.float())
+        return out.to(v.dtype), lse
+
+
+class FlashAttentionFunc(torch.autograd.Function):
+    """``FlashAttentionFunc.apply(q, k, v, is_causal=False)`` on ``[B, S, hd]`` tensors: the first argument holds the
+    queries, as in the reference's ``forward(ctx, q, k, v, is_causal)``.  (The reference's PyTorch variant accepts
+    ``is_causal`` and ignores it, :13-37; this one applies the mask.)  Saves q, k, v, the output and the
+    log-sum-exp; the backward pass runs the flash backward kernels where the forward ran the flash kernel, else
+    ``attention_pytorch``."""
 
     @staticmethod
-    def apply(q, k, v, is_causal=False):
-        return _attend(q, k, v, is_causal)
+    def forward(ctx, q, k, v, is_causal=False):
+        out, lse = _forward_values(q, k, v, is_causal)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.is_causal = bool(is_causal)
+        return out
 
-    def __call__(self, *args, **kwargs):          # the reference's layer writes ``FlashAttentionTritonFunc().apply``
-        return self.apply(*args, **kwargs)
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, l = ctx.saved_tensors
+        if _native_ok(q, k):
+            from b200moe.ops import native
+            dq, dk, dv = native.attention_bwd(do.unsqueeze(2).contiguous(), q.unsqueeze(2).contiguous(),
+                                              k.unsqueeze(2).contiguous(), v.unsqueeze(2).contiguous(),
+                                              o.unsqueeze(2).contiguous(), l.unsqueeze(1).contiguous(),
+                                              causal=ctx.is_causal)
+            return dq.squeeze(2), dk.squeeze(2), dv.squeeze(2), None
+        visible = _visible(q, k, ctx.is_causal)
+        return attention_pytorch(q, k, v, o, do, l, None if visible is None else visible.unsqueeze(0))
 
 
-FlashAttentionTritonFunc = FlashAttentionFunc
+class FlashAttentionTritonFunc(FlashAttentionFunc):
+    """Same function under the name of the reference's Triton variant (:60-98), which honours ``is_causal``."""
 
 
 def _scores(q, k, l, mask):
@@ -73,27 +120,9 @@ class _ForwardLauncher:
             is_causal = bool(layout[20])
         is_causal = bool(named.get("is_causal", is_causal))
         scale = named.get("scale", layout[16] if len(layout) > 16 else 1.0 / math.sqrt(K.shape[-1]))
-        q4, k4, v4 = (t.unsqueeze(2) for t in (Q, K, V))
-        native_ok = (Q.is_cuda and Q.dtype == torch.bfloat16 and Q.shape[-1] == 128 and Q.shape[-2] % 128 == 0
-                     and K.shape[-2] == Q.shape[-2] and abs(scale * math.sqrt(K.shape[-1]) - 1.0) < 1e-6)
-        if native_ok:
-            from b200moe.ops import native, use_native
-            if use_native(q4, "attention"):
-                with torch.no_grad():
-                    out, lse, _, _ = native.attention_fwd(q4.contiguous(), k4.contiguous(), v4.contiguous(), None,
-                                                          None, causal=is_causal)
-                O.copy_(out.squeeze(2))
-                L.copy_(lse.squeeze(1))
-                return
-        with torch.no_grad():
-            s = torch.einsum("...qd,...kd->...qk", Q.float(), K.float()) * scale
-            if is_causal:
-                nq, nk = Q.shape[-2], K.shape[-2]
-                allowed = torch.arange(nq, device=Q.device)[:, None] >= torch.arange(nk, device=Q.device)[None, :]
-                s = s.masked_fill(~allowed, float("-inf"))
-            lse = torch.logsumexp(s, dim=-1)
-            O.copy_(torch.einsum("...qk,...kv->...qv", torch.exp(s - lse.unsqueeze(-1)), V.float()))
-            L.copy_(lse)
+        out, lse = _forward_values(Q, K, V, is_causal, scale)
+        O.copy_(out)
+        L.copy_(lse)
 
 
 attention_forward = _ForwardLauncher()

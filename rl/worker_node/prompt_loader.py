@@ -62,6 +62,8 @@ class DatabasePromptLoader(PromptLoader):
         self._connect = connect
         self._conn = None
 
+    _load_config = staticmethod(read_data_source)
+
     @staticmethod
     def _build_conninfo(database: dict[str, Any]) -> str:
         return " ".join(f"{key}={value}" for key, value in database.items())

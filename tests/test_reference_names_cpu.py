@@ -48,10 +48,13 @@ def test_attention_functions_take_queries_first_and_match_the_formula():
         visible = torch.arange(S)[:, None] >= torch.arange(S)[None, :] if causal else torch.ones(S, S, dtype=torch.bool)
         scores = (q @ k.transpose(-1, -2) / math.sqrt(D)).masked_fill(~visible, float("-inf"))
         want = torch.softmax(scores, -1) @ v
-        for function in (FlashAttentionFunc, FlashAttentionTritonFunc()):
-            assert torch.allclose(function.apply(q, k, v, causal), want, atol=1e-5)
         grad_out = torch.randn_like(want)
         want_grads = torch.autograd.grad(want, (q, k, v), grad_out, retain_graph=True)
+        for function in (FlashAttentionFunc, FlashAttentionTritonFunc):
+            got_out = function.apply(q, k, v, causal)
+            assert torch.allclose(got_out, want, atol=1e-5)
+            for a, b in zip(torch.autograd.grad(got_out, (q, k, v), grad_out), want_grads):
+                assert torch.allclose(a, b, atol=1e-5)
         lse = torch.logsumexp(scores, -1).detach()
         got = attention_pytorch(q.detach(), k.detach(), v.detach(), want.detach(), grad_out, lse,
                                 visible.float().unsqueeze(0))
