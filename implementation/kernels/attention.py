@@ -69,10 +69,8 @@ class FlashAttentionFunc(torch.autograd.Function):
         q, k, v, o, l = ctx.saved_tensors
         if _native_ok(q, k):
             from b200moe.ops import native
-            dq, dk, dv = native.attention_bwd(do.unsqueeze(2).contiguous(), q.unsqueeze(2).contiguous(),
-                                              k.unsqueeze(2).contiguous(), v.unsqueeze(2).contiguous(),
-                                              o.unsqueeze(2).contiguous(), l.unsqueeze(1).contiguous(),
-                                              causal=ctx.is_causal)
+            four = [t.unsqueeze(2).contiguous() for t in (do.to(torch.bfloat16), q, k, v, o)]
+            dq, dk, dv = native.attention_bwd(*four, l.unsqueeze(1).contiguous(), causal=ctx.is_causal)
             return dq.squeeze(2), dk.squeeze(2), dv.squeeze(2), None
         visible = _visible(q, k, ctx.is_causal)
         return attention_pytorch(q, k, v, o, do, l, None if visible is None else visible.unsqueeze(0))

@@ -467,6 +467,36 @@ def test_flash_attention_forward_entry(native):
     native.check_status()
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_reference_named_attention_functions_run_the_flash_kernels(native, causal):
+    """``FlashAttentionTritonFunc.apply(q, k, v, is_causal)`` and the ``attention_forward[grid](...)`` launch of the
+    reference's module, on bf16 ``[B, S, 128]`` tensors: forward and backward against an fp32 formula."""
+    from implementation.kernels.attention import FlashAttentionTritonFunc, attention_forward
+    torch.manual_seed(9)
+    B, S, hd = 3, 256, 128
+    q, k, v = (_rand(B, S, hd).requires_grad_(True) for _ in range(3))
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    scores = qf @ kf.transpose(-1, -2) / math.sqrt(hd)
+    if causal:
+        scores = scores.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool, device="cuda"), 1), float("-inf"))
+    ref = torch.softmax(scores, -1) @ vf
+    before = native.launch_count()
+    out = FlashAttentionTritonFunc.apply(q, k, v, causal)
+    assert native.launch_count() > before and out.shape == (B, S, hd) and out.dtype == torch.bfloat16
+    assert _rel(out, ref) < 2e-2
+    dout = _rand(B, S, hd)
+    before = native.launch_count()
+    out.backward(dout)
+    assert native.launch_count() > before
+    ref.backward(dout.float())
+    assert _rel(q.grad, qf.grad) < 3e-2 and _rel(k.grad, kf.grad) < 3e-2 and _rel(v.grad, vf.grad) < 3e-2
+    filled, lse = torch.empty(B, S, hd, device="cuda", dtype=torch.bfloat16), torch.empty(B, S, device="cuda")
+    attention_forward[(S // 16, B)](q.detach(), k.detach(), v.detach(), filled, lse, *([0] * 14), S, S,
+                                    1 / math.sqrt(hd), hd, 16, 16, causal)
+    assert _rel(filled, ref) < 2e-2 and _rel(lse, torch.logsumexp(scores.detach(), -1)) < 1e-3
+    native.check_status()
+
+
 def test_fused_qkv_attention_with_rope(native):
     from b200moe.ops import functional as Fn
     from b200moe.ops.attention import fused_qkv_attention
