@@ -21,6 +21,7 @@
 //   and accumulates dQ += dS K in TMEM.
 // Every barrier wait is bounded; a wait that runs out sets the status word.
 #include "ptx.cuh"
+#include "tensormap.cuh"
 
 namespace b2 {
 
@@ -769,33 +770,21 @@ __global__ void __launch_bounds__(ATTN_BWD_THREADS, 1) attn_bwd_dq_kernel(const 
 }
 
 // ================================================================= host
-typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeFn attn_encode() {
-  static EncodeFn fn = nullptr;
-  if (!fn) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult res;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) == cudaSuccess &&
-        res == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeFn>(sym);
-  }
-  return fn;
-}
 // [tokens, heads*128] bf16 with token pitch ``pitch`` elements; box = [128 tokens, 64 columns].
+static int g_last_encode_result = 0;     // CUresult of the last tensor-map encode that failed (diagnostics)
+
 static int attn_map(CUtensorMap* map, const void* base, long long tokens, int heads, long long pitch) {
-  EncodeFn fn = attn_encode();
+  EncodeTiledFn fn = encode_fn();      // binds this thread's context first (tensormap.cuh)
   if (!fn) return -1;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(heads) * HD, static_cast<cuuint64_t>(tokens)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch) * 2};
   cuuint32_t box[2] = {64, 128};
   cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
-             ? 0
-             : -2;
+  const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) g_last_encode_result = static_cast<int>(rc);
+  return rc == CUDA_SUCCESS ? 0 : -2;
 }
 
 constexpr int FWD_SMEM = 5 * TILE_BYTES + 1024 + 6 * TQ * 4 + 512;
@@ -806,6 +795,9 @@ constexpr int BWD_SMEM = 6 * TILE_BYTES + 1024 + 512;
 using namespace b2;
 
 extern "C" {
+
+// After an entry point returned -11 (a tensor map could not be encoded): the driver's result code of that encode.
+int b2_attention_last_encode_result() { return g_last_encode_result; }
 
 // q: [B,S,Hq,128], k, v: [B,S,Hkv,128] bf16 with token pitches (elements); out [B,S,Hq,128] contiguous; lse [B,Hq,S].
 int b2_attention_fwd_ex(const void* q, const void* k, const void* v, long long q_pitch, long long k_pitch,
@@ -863,9 +855,13 @@ int b2_attention_bwd_rope(const void* dout, const void* q, const void* k, const 
   if (S % 128 || Hq % Hkv) return -10;
   AttnParams p{};
   const long long tokens = static_cast<long long>(B) * S;
-  if (attn_map(&p.map_q, q, tokens, Hq, q_pitch) || attn_map(&p.map_k, k, tokens, Hkv, k_pitch) ||
-      attn_map(&p.map_v, v, tokens, Hkv, v_pitch) || attn_map(&p.map_do, dout, tokens, Hq, static_cast<long long>(Hq) * HD))
-    return -11;
+  // -11 / -12 / -13 / -14: the tensor map of q / k / v / dout could not be encoded (base not 16-byte aligned, pitch
+  // not a multiple of 8 elements, ...); b2_attention_last_encode_result() has the driver's code
+  if (q_pitch % 8 || k_pitch % 8 || v_pitch % 8) return -10;
+  if (attn_map(&p.map_q, q, tokens, Hq, q_pitch)) return -11;
+  if (attn_map(&p.map_k, k, tokens, Hkv, k_pitch)) return -12;
+  if (attn_map(&p.map_v, v, tokens, Hkv, v_pitch)) return -13;
+  if (attn_map(&p.map_do, dout, tokens, Hq, static_cast<long long>(Hq) * HD)) return -14;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal != 0;
   p.lse = const_cast<float*>(lse); p.delta = delta; p.dq = static_cast<__nv_bfloat16*>(dq);

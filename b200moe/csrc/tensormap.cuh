@@ -10,7 +10,20 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// A host thread that has made no CUDA runtime call yet has no current context (PyTorch's autograd worker thread on
+// device 0 is one: it never needs to switch devices), and the driver entry point then answers
+// CUDA_ERROR_INVALID_CONTEXT (201).  ``cudaFree(nullptr)`` binds the primary context of the current device; once per
+// thread.
+static inline void bind_primary_context() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 static inline EncodeTiledFn encode_fn() {
+  bind_primary_context();
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* sym = nullptr;

@@ -194,8 +194,18 @@ def _call(name, *args, n: int = 1, tag: str = ""):
     else:
         rc = getattr(require(), name)(*args)
     if rc != 0:
-        raise RuntimeError(f"{name} failed with code {rc}")
+        raise RuntimeError(f"{name} failed with code {rc}{_failure_detail(name, rc)}")
     _launches += n
+
+
+def _failure_detail(name: str, rc: int) -> str:
+    """What else is known about a refused launch (the attention entry points keep the driver's result of a
+    tensor-map encode that failed)."""
+    if name.startswith("b2_attention") and -14 <= rc <= -11:
+        reader = getattr(_lib, "b2_attention_last_encode_result", None)
+        if reader is not None:
+            return f" (tensor map {('q', 'k', 'v', 'dout')[-11 - rc]}: driver result {reader()})"
+    return ""
 
 
 _I, _L, _F = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
