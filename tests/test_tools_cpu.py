@@ -328,3 +328,21 @@ def test_modal_launcher_nodes_rendezvous_and_profiler(tmp_path, monkeypatch):
     assert command[:2] == ["/opt/nsys", "profile"] and "--kill=none" in command and "--wait=all" in command
     assert "--master-addr=127.0.0.1" in command and env["MASTER_ADDR"] == "127.0.0.1" and committed == [1]
     assert command[command.index("--module") + 1] == "distributed_parallel_training_pipelined"
+
+
+def test_packaging_lists_every_importable_top_level_name():
+    """``pip install .`` must carry the package, the reference's import names and entry modules, the run
+    configuration, the SQL of the side car and the CUDA sources."""
+    import tomllib
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with open(os.path.join(root, "pyproject.toml"), "rb") as handle:
+        meta = tomllib.load(handle)
+    tool = meta["tool"]["setuptools"]
+    for module in tool["py-modules"]:
+        assert os.path.isfile(os.path.join(root, module + ".py")), module
+    patterns = tool["packages"]["find"]["include"]
+    for package in ("b200moe", "implementation", "pipeline", "configs", "rl"):
+        assert os.path.isfile(os.path.join(root, package, "__init__.py")), package
+        assert any(p.rstrip("*") == package for p in patterns), package
+    assert "csrc/*.cu" in tool["package-data"]["b200moe"] and "*.yaml" in tool["package-data"]["configs"]
+    assert meta["project"]["name"] == "b200moe" and any(d.startswith("torch") for d in meta["project"]["dependencies"])
