@@ -292,6 +292,58 @@ class MoELayerMulti(nn.Module):
         return out
 
 
+    # ---- the reference's two-step form of the same computation (layers.py:140-213) ------------------------------
+    # ``forward`` above does not go through these: it hands routing, exchange and experts to one op.  They are kept,
+    # with the reference's arguments and return values, for code that drives the steps itself, and they double as a
+    # plain-PyTorch statement of what the fused path computes (tests compare the two).
+    def _dispatch_tokens(self, x, logits, probs, expert_idx, return_aux_loss):
+        """Sort the ``tokens × k`` assignments by global expert, send every row to the rank that owns its expert and
+        order what arrives by local expert.  ``x [tokens, d]``, ``probs``/``expert_idx [tokens, k]``.  Returns
+        ``(expert_input, cumulative_rows_per_local_expert int32, expert_split_sizes, recv_splits, assignment_order,
+        renormalised probs, aux_loss)``."""
+        probs = probs / probs.sum(dim=-1, keepdim=True)
+        experts_total = self.world_size * self.num_expert_per_node
+        group = self.dp_group if self.world_size > 1 else None
+        aux_loss = None
+        if return_aux_loss:
+            from ..ops.moe import aux_loss_from
+            aux_loss = aux_loss_from(logits, expert_idx, experts_total, self.k, group)
+        flat_idx = expert_idx.reshape(-1)
+        assignment_order = torch.argsort(flat_idx, stable=True)          # grouped by expert, token order inside
+        split_sizes = torch.bincount(flat_idx, minlength=experts_total).tolist()
+        sent = x[assignment_order // self.k]
+        if self.world_size == 1:
+            received, recv_splits = sent, split_sizes
+        else:
+            received, recv_splits = TensorExchange.apply(sent, split_sizes, self.dp_group)
+        # arrivals are ordered (source rank, local expert); the grouped GEMM wants (local expert, source rank)
+        chunks = torch.split(received, recv_splits, dim=0)
+        per_expert = [chunks[e::self.num_expert_per_node] for e in range(self.num_expert_per_node)]
+        expert_input = torch.cat([c for group_ in per_expert for c in group_], dim=0)
+        expert_split_sizes = [c.shape[0] for group_ in per_expert for c in group_]
+        rows = torch.tensor([sum(c.shape[0] for c in group_) for group_ in per_expert], device=x.device,
+                            dtype=torch.int32)
+        return (expert_input, rows.cumsum(dim=0, dtype=torch.int32), expert_split_sizes, recv_splits,
+                assignment_order, probs, aux_loss)
+
+    def _combine_tokens(self, expert_outputs, expert_split_sizes, recv_splits, assignment_order, probs, batch_size,
+                        context_len, input_dtype):
+        """Inverse of ``_dispatch_tokens`` for the experts' outputs: back to (source rank, local expert) order, home
+        over the exchange, into assignment order, weighted sum of each token's ``k`` rows."""
+        pieces = torch.split(expert_outputs, expert_split_sizes)
+        by_rank = [pieces[e * self.world_size + r] for r in range(self.world_size)
+                   for e in range(self.num_expert_per_node)]
+        sent = torch.cat(by_rank, dim=0)
+        if self.world_size == 1:
+            returned = sent
+        else:
+            returned, _ = TensorExchange.apply(sent, recv_splits, self.dp_group)
+        rows = torch.empty_like(returned)
+        rows[assignment_order] = returned
+        mixed = (rows.view(-1, self.k, rows.shape[-1]) * probs.unsqueeze(-1)).sum(dim=1)
+        return mixed.view(batch_size, context_len, -1).to(input_dtype)
+
+
 class TransformerLayer(nn.Module):
     """Pre-norm block: ``x += attn(ln1(x)); x += moe(ln2(x))`` (reference
     layers.py:336-356)."""

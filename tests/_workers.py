@@ -382,3 +382,49 @@ def run_weight_hooks(rank, world, port, result_dir):
         raise
     finally:
         dist.destroy_process_group()
+
+
+def run_moe_two_step(rank, world, port, result_dir):
+    """``MoELayerMulti._dispatch_tokens`` → grouped experts → ``_combine_tokens`` over ``world`` gloo ranks against
+    the layer's own forward pass, values and gradients."""
+    import torch
+    import torch.distributed as dist
+    _env(rank, world, port)
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from b200moe import ops
+        from b200moe.models.layers import MoELayerMulti
+        torch.manual_seed(5)
+        layer = MoELayerMulti(32, 48, num_expert_per_node=2, dtype=torch.float32, dp_group=dist.group.WORLD)
+        torch.manual_seed(100 + rank)
+        for p in layer.experts.parameters():
+            p.data.normal_(0, 0.2)                        # every rank owns different experts
+        x = torch.randn(3, 8, 32)
+        x1 = x.clone().requires_grad_(True)
+        want, want_aux = layer(x1, return_aux_loss=True)
+        (want.sum() + want_aux).backward()
+        want_grads = [x1.grad.clone()] + [p.grad.clone() for p in layer.parameters()]
+        layer.zero_grad()
+        x2 = x.clone().requires_grad_(True)
+        flat = x2.reshape(-1, 32)
+        logits = layer.router(flat)
+        weights, idx = ops.router_top2(logits)
+        (expert_input, offsets, expert_splits, recv_splits, order, probs, aux) = layer._dispatch_tokens(
+            flat, logits, weights, idx, True)
+        assert int(offsets[-1]) == expert_input.shape[0] and len(expert_splits) == 2 * world
+        got = layer._combine_tokens(layer.experts(expert_input, offsets), expert_splits, recv_splits, order, probs,
+                                    3, 8, x.dtype)
+        assert torch.allclose(got, want, atol=1e-5) and torch.allclose(aux, want_aux, atol=1e-6)
+        (got.sum() + aux).backward()
+        got_grads = [x2.grad] + [p.grad for p in layer.parameters()]
+        for a, b in zip(got_grads, want_grads):
+            assert torch.allclose(a, b, atol=1e-4), (a - b).abs().max()
+        with open(os.path.join(result_dir, f"two_step_ok_{rank}"), "w") as f:
+            f.write("ok")
+    except Exception:
+        with open(os.path.join(result_dir, f"err_{rank}.txt"), "w") as f:
+            f.write(traceback.format_exc())
+        raise
+    finally:
+        dist.destroy_process_group()

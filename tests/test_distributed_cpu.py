@@ -141,3 +141,9 @@ def test_peer_link_schedule_matches_nccl_link(tmp_path, free_port, world, microb
 def test_gather_and_free_hooks_on_hand_sharded_modules(tmp_path, free_port):
     _spawn(W.run_weight_hooks, 2, (2, free_port, str(tmp_path)))
     assert all((tmp_path / f"hooks_ok_{r}").exists() for r in range(2))
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_two_step_dispatch_and_combine_match_the_layer(tmp_path, free_port, world):
+    _spawn(W.run_moe_two_step, world, (world, free_port, str(tmp_path)))
+    assert all((tmp_path / f"two_step_ok_{r}").exists() for r in range(world))
