@@ -93,9 +93,9 @@ class EmbeddingLayer(nn.Module):
         self.weight = nn.Parameter(_trunc_normal((num_embeddings, embedding_dim), 1.0, device))
         self.compute_weight = None
 
-    def forward(self, ids):
+    def forward(self, x):
         weight = self.compute_weight if self.compute_weight is not None else self.weight
-        return ops.embedding(ids, weight)
+        return ops.embedding(x, weight)
 
 
 class RMSNormLayer(nn.Module):

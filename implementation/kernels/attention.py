@@ -104,21 +104,29 @@ def attention_pytorch(q, k, v, o, do, l, mask):
 
 
 class _ForwardLauncher:
-    """Stands where the reference has a ``@triton.jit`` kernel: ``attention_forward[grid](Q, K, V, O, L, <14 strides>,
-    n_queries, n_keys, scale, D, q_tile, k_tile, is_causal)`` writes the attention output into ``O`` and the
-    log-sum-exp of the scaled scores into ``L``.  Grid, strides and tile sizes are accepted and not needed: the
-    tensors carry their own layout and the kernel picks its tiles."""
+    """Stands where the reference has a ``@triton.jit`` kernel: ``attention_forward[grid](Q_ptr, K_ptr, V_ptr, O_ptr,
+    L_ptr, <14 strides>, N_QUERIES, N_KEYS, scale, D, Q_TILE_SIZE, K_TILE_SIZE, is_causal)``, positionally or by those
+    names, writes the attention output into ``O_ptr`` and the log-sum-exp of the scaled scores into ``L_ptr`` (both
+    tensors, as in a Triton launch).  Grid, strides and tile sizes are accepted and not needed: the tensors carry
+    their own layout and the kernel picks its tiles."""
+
+    PARAMETERS = ("Q_ptr", "K_ptr", "V_ptr", "O_ptr", "L_ptr",
+                  "stride_qb", "stride_qq", "stride_qd", "stride_kb", "stride_kk", "stride_kd",
+                  "stride_vb", "stride_vk", "stride_vd", "stride_ob", "stride_oq", "stride_od",
+                  "stride_lb", "stride_lq", "N_QUERIES", "N_KEYS", "scale", "D", "Q_TILE_SIZE", "K_TILE_SIZE",
+                  "is_causal")
 
     def __getitem__(self, grid):
         return self
 
-    def __call__(self, Q, K, V, O, L, *layout, is_causal=False, **named):
-        # positional tail of the reference's launch: 14 strides, n_queries, n_keys, scale, D, q_tile, k_tile, is_causal
-        if len(layout) > 20:
-            is_causal = bool(layout[20])
-        is_causal = bool(named.get("is_causal", is_causal))
-        scale = named.get("scale", layout[16] if len(layout) > 16 else 1.0 / math.sqrt(K.shape[-1]))
-        out, lse = _forward_values(Q, K, V, is_causal, scale)
+    def __call__(self, *args, **named):
+        unknown = set(named) - set(self.PARAMETERS)
+        if unknown or len(args) > len(self.PARAMETERS):
+            raise TypeError(f"attention_forward: unexpected arguments {sorted(unknown) or len(args)}")
+        given = dict(zip(self.PARAMETERS, args))
+        given.update(named)
+        Q, K, V, O, L = (given[name] for name in self.PARAMETERS[:5])
+        out, lse = _forward_values(Q, K, V, bool(given.get("is_causal", False)), given.get("scale"))
         O.copy_(out)
         L.copy_(lse)
 

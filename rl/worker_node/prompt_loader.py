@@ -65,8 +65,8 @@ class DatabasePromptLoader(PromptLoader):
     _load_config = staticmethod(read_data_source)
 
     @staticmethod
-    def _build_conninfo(database: dict[str, Any]) -> str:
-        return " ".join(f"{key}={value}" for key, value in database.items())
+    def _build_conninfo(db_config: dict[str, Any]) -> str:
+        return " ".join(f"{key}={value}" for key, value in db_config.items())
 
     def _get_connection(self):
         if self._conn is None or getattr(self._conn, "closed", False):

@@ -37,6 +37,55 @@ def test_public_names_of_the_reference_exist_here(relative):
     assert not missing, f"{relative}: {missing}"
 
 
+def _argument_names(node):
+    return [a.arg for a in node.args.args] + [a.arg for a in node.args.kwonlyargs]
+
+
+def _accepts(callable_, wanted):
+    """Names of ``wanted`` that ``callable_`` cannot take by keyword."""
+    import inspect
+    try:
+        have = inspect.signature(callable_).parameters
+    except (TypeError, ValueError):
+        return []
+    if any(p.kind in (p.VAR_KEYWORD, p.VAR_POSITIONAL) for p in have.values()):
+        return []
+    if getattr(callable_, "PARAMETERS", None):
+        have = set(have) | set(callable_.PARAMETERS)
+    return [name for name in wanted if name not in have]
+
+
+@pytest.mark.parametrize("relative", _reference_modules())
+def test_methods_and_argument_names_of_the_reference_exist_here(relative):
+    """Every method of a reference class exists on the class here, and every function or method takes the
+    reference's argument names (so calls by keyword keep working)."""
+    with open(os.path.join(REFERENCE, relative), encoding="utf-8") as handle:
+        tree = ast.parse(handle.read())
+    module_name = relative[:-3].replace(os.sep, ".")
+    module = importlib.import_module(module_name[:-9] if module_name.endswith(".__init__") else module_name)
+    problems = []
+    for node in tree.body:
+        here = getattr(module, node.name, None) if isinstance(node, (ast.FunctionDef, ast.ClassDef)) else None
+        if here is None:
+            continue
+        if isinstance(node, ast.FunctionDef):
+            target = getattr(here, "__call__", here) if getattr(here, "PARAMETERS", None) else here
+            missing = _accepts(target, _argument_names(node)) if not getattr(here, "PARAMETERS", None) else \
+                [n for n in _argument_names(node) if n not in here.PARAMETERS]
+            if missing:
+                problems.append(f"{node.name}: no argument {missing}")
+            continue
+        for method in (n for n in node.body if isinstance(n, ast.FunctionDef)):
+            if not hasattr(here, method.name):
+                problems.append(f"{node.name}.{method.name}: missing")
+                continue
+            wanted = [n for n in _argument_names(method) if n not in ("self", "cls", "ctx")]
+            missing = _accepts(getattr(here, method.name), wanted)
+            if missing:
+                problems.append(f"{node.name}.{method.name}: no argument {missing}")
+    assert not problems, f"{relative}: {problems}"
+
+
 def test_attention_functions_take_queries_first_and_match_the_formula():
     from implementation.kernels.attention import (FlashAttentionFunc, FlashAttentionTritonFunc, attention_forward,
                                                   attention_pytorch)
