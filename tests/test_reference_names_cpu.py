@@ -8,7 +8,10 @@ import os
 import pytest
 import torch
 
-REFERENCE = os.environ.get("B200MOE_REFERENCE_TREE", "/root/reference")
+# the reference's source tree: a checkout named by B200MOE_REFERENCE_TREE (covers the side car under rl/ as well),
+# else the copy installed for the benchmark's reference arm; without either the walk is skipped
+_HERE = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REFERENCE = os.environ.get("B200MOE_REFERENCE_TREE") or os.path.join(_HERE, "baseline", "_ref")
 NOT_CARRIED: dict = {}     # per reference file: names deliberately absent here (none)
 
 
@@ -17,7 +20,8 @@ def _reference_modules():
         return []
     found = []
     for folder, dirs, files in os.walk(REFERENCE):
-        dirs[:] = [d for d in dirs if not d.startswith(".") and d not in ("tests", "__pycache__", "kubernetes")]
+        dirs[:] = [d for d in dirs if not d.startswith(".") and d not in ("tests", "__pycache__", "kubernetes")
+                   and not d.endswith(".dist-info")]
         for name in files:
             if name.endswith(".py"):
                 found.append(os.path.relpath(os.path.join(folder, name), REFERENCE))
