@@ -170,16 +170,35 @@ def test_vllm_launcher_pins_gpu_and_ends_only_the_servers_on_its_port():
 
 
 def test_helm_values_hold_a_valid_run_config():
-    import os
+    """The chart's values use the reference chart's keys, its run configuration passes this framework's checks with
+    the topology the helper derives, and every ``.Values.*`` path a template reads exists in values.yaml."""
+    import re
     from b200moe import config as cfg
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    with open(os.path.join(root, "kubernetes", "chart", "values.yaml")) as f:
+    chart = os.path.join(root, "kubernetes", "chart")
+    with open(os.path.join(chart, "values.yaml")) as f:
         values = yaml.safe_load(f)
-    run = values["config"]
-    run["general"]["n_workers"] = values["nodes"] * values["gpusPerNode"]
+    for key in ("image", "numNodes", "gpusPerNode", "runtimeRef", "resourcesPerNode", "memlock", "failurePolicy",
+                "sharedMemory", "ncclDebug", "runConfig"):
+        assert key in values, key
+    assert set(values["runtimeRef"]) == {"name", "kind", "apiGroup"} and set(values["memlock"]) == {"enabled", "createRuntime"}
+    run = values["runConfig"]
+    run["general"]["n_workers"] = values["numNodes"] * values["gpusPerNode"]
     run["general"]["gpu_per_node"] = values["gpusPerNode"]
-    run["train"].setdefault("validation_interval", 1)
     cfg.validate_config(run)
+    for name in os.listdir(os.path.join(chart, "templates")):
+        with open(os.path.join(chart, "templates", name)) as f:
+            text = f.read()
+        assert text.count("{{") == text.count("}}"), name
+        actions = re.findall(r"\{\{-?\s*(.*?)\s*-?\}\}", re.sub(r"\{\{-?\s*/\*.*?\*/\s*-?\}\}", "", text, flags=re.S),
+                             flags=re.S)
+        opened = sum(1 for a in actions if re.match(r"(if|range|with|define)\b", a))
+        assert opened == sum(1 for a in actions if re.match(r"end\b", a)), name
+        for path in set(re.findall(r"\.Values\.([A-Za-z_.]+)", text)):
+            node = values
+            for part in path.rstrip(".").split("."):
+                assert isinstance(node, dict) and part in node, f"{name}: .Values.{path}"
+                node = node[part]
 
 
 def test_checked_build_compiles_and_exports_its_readers():
